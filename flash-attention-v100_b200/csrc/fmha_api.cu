@@ -1,0 +1,360 @@
+// C-ABI launch layer of the B200 attention library (declared in include/fmha_b200.h).
+//
+// Replaces the host launchers of the reference (kernel/fused_mha_kernel.cu:891-916): validate
+// plain-pointer parameters, build the TMA tensor maps, raise the dynamic shared-memory limit,
+// launch, and return a status.  Nothing here allocates device memory or synchronises.
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include <cmath>
+#include <cstdint>
+#include <cstring>
+
+#include "../../include/fmha_b200.h"
+#include "aux_kernels.cuh"
+#include "bwd_kernel.cuh"
+#include "fwd_kernel.cuh"
+
+namespace {
+
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                   const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                   const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn get_encode_fn() {
+  // resolved once; the pointer is process-wide and immutable afterwards
+  static EncodeTiledFn fn = []() -> EncodeTiledFn {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) !=
+            cudaSuccess ||
+        qres != cudaDriverEntryPointSuccess)
+      return nullptr;
+    return reinterpret_cast<EncodeTiledFn>(ptr);
+  }();
+  return fn;
+}
+
+// fp16 (Z, N, H, D) tensor with element strides -> 4-D map (D, N, H, Z), box 64 x 128 x 1 x 1,
+// 128-byte swizzle, zero fill outside the tensor
+int make_tensor_map(CUtensorMap* map, const void* base, int Z, int N, int H, int D,
+                    const FmhaStrides& s) {
+  EncodeTiledFn encode = get_encode_fn();
+  if (encode == nullptr) return FMHA_ERR_NO_DEVICE;
+  // a stride of a size-1 dimension is never used for addressing; make it well-formed
+  const int64_t row = (N > 1) ? s.row : (int64_t)H * D;
+  const int64_t head = (H > 1) ? s.head : (int64_t)D;
+  const int64_t batch = (Z > 1) ? s.batch : row * N;
+  const cuuint64_t dims[4] = {(cuuint64_t)D, (cuuint64_t)N, (cuuint64_t)H, (cuuint64_t)Z};
+  const cuuint64_t strides[3] = {(cuuint64_t)row * 2, (cuuint64_t)head * 2, (cuuint64_t)batch * 2};
+  const cuuint32_t box[4] = {64, 128, 1, 1};
+  const cuuint32_t estr[4] = {1, 1, 1, 1};
+  const CUresult r = encode(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4, const_cast<void*>(base), dims,
+                            strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                            CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? FMHA_OK : FMHA_ERR_TENSOR_MAP;
+}
+
+bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+int check_strides(const FmhaStrides& s, int N, int H, int Z) {
+  if ((N > 1 && (s.row % 8 != 0 || s.row <= 0)) || (H > 1 && (s.head % 8 != 0 || s.head <= 0)) ||
+      (Z > 1 && (s.batch % 8 != 0 || s.batch <= 0)))
+    return FMHA_ERR_BAD_STRIDE;
+  return FMHA_OK;
+}
+
+int check_common(int batch, int heads, int seqlen_q, int seqlen_k, int head_dim, float scale) {
+  if (head_dim != 64 && head_dim != 128) return FMHA_ERR_BAD_HEAD_DIM;
+  if (batch <= 0 || heads <= 0 || seqlen_q <= 0 || seqlen_k <= 0) return FMHA_ERR_BAD_SHAPE;
+  if (!std::isfinite(scale) || scale == 0.f) return FMHA_ERR_BAD_SHAPE;
+  if ((long long)batch * heads * ((seqlen_q + 127) / 128 + 1) >= (1ll << 31) ||
+      (long long)batch * heads * ((seqlen_k + 127) / 128 + 1) >= (1ll << 31))
+    return FMHA_ERR_TOO_LARGE;
+  return FMHA_OK;
+}
+
+fmha::Strides3 to3(const FmhaStrides& s) { return fmha::Strides3{s.batch, s.row, s.head}; }
+
+int round_up_128(int x) { return (x + 127) / 128 * 128; }
+
+struct BwdWorkspace {
+  float* dq_accum;
+  float* lse2;
+  float* delta;
+  size_t bytes;
+};
+
+BwdWorkspace carve_workspace(void* ws, int Z, int H, int Nq, int D) {
+  BwdWorkspace w;
+  const size_t dq_bytes = (size_t)Z * Nq * H * D * sizeof(float);  // multiple of 256
+  const size_t stat_bytes = (size_t)Z * H * round_up_128(Nq) * sizeof(float);
+  char* base = static_cast<char*>(ws);
+  w.dq_accum = reinterpret_cast<float*>(base);
+  w.lse2 = reinterpret_cast<float*>(base + dq_bytes);
+  w.delta = reinterpret_cast<float*>(base + dq_bytes + stat_bytes);
+  w.bytes = dq_bytes + 2 * stat_bytes;
+  return w;
+}
+
+template <int D>
+int launch_fwd(const FmhaFwdParams* p, cudaStream_t stream) {
+  using T = fmha::FwdTraits<D>;
+  CUtensorMap tq, tk, tv, to;
+  int rc;
+  if ((rc = make_tensor_map(&tq, p->q, p->batch, p->seqlen_q, p->heads, D, p->q_strides))) return rc;
+  if ((rc = make_tensor_map(&tk, p->k, p->batch, p->seqlen_k, p->heads, D, p->k_strides))) return rc;
+  if ((rc = make_tensor_map(&tv, p->v, p->batch, p->seqlen_k, p->heads, D, p->v_strides))) return rc;
+  if ((rc = make_tensor_map(&to, p->o, p->batch, p->seqlen_q, p->heads, D, p->o_strides))) return rc;
+  fmha::FwdKernelParams kp;
+  kp.lse = p->lse;
+  kp.heads = p->heads;
+  kp.seqlen_q = p->seqlen_q;
+  kp.seqlen_k = p->seqlen_k;
+  kp.num_q_blocks = (p->seqlen_q + 255) / 256;
+  kp.scale_log2 = p->scale * 1.4426950408889634f;
+  kp.causal = p->causal ? 1 : 0;
+  kp.causal_shift = p->causal_shift;
+  kp.status = p->status;
+  auto kernel = fmha::fmha_fwd_kernel<D>;
+  if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, T::kSmemBytes) !=
+      cudaSuccess)
+    return FMHA_ERR_LAUNCH;
+  const unsigned grid = (unsigned)((long long)kp.num_q_blocks * p->heads * p->batch);
+  kernel<<<grid, T::kThreads, T::kSmemBytes, stream>>>(tq, tk, tv, to, kp);
+  return cudaGetLastError() == cudaSuccess ? FMHA_OK : FMHA_ERR_LAUNCH;
+}
+
+template <int D>
+int launch_bwd(const FmhaBwdParams* p, const BwdWorkspace& w, cudaStream_t stream) {
+  using T = fmha::BwdTraits<D>;
+  const int Z = p->batch, H = p->heads, Nq = p->seqlen_q, Nk = p->seqlen_k;
+  const int Nq_pad = round_up_128(Nq);
+
+  if (!(p->flags & FMHA_BWD_KEEP_WORKSPACE)) {
+    const long long rows = (long long)Z * H * Nq_pad;
+    constexpr int rows_per_block = 256 / (D / 8);
+    const unsigned grid = (unsigned)((rows + rows_per_block - 1) / rows_per_block);
+    fmha::fmha_bwd_preprocess_kernel<D><<<grid, 256, 0, stream>>>(
+        static_cast<const __half*>(p->o), to3(p->o_strides), static_cast<const __half*>(p->dout),
+        to3(p->dout_strides), p->lse, w.dq_accum, w.lse2, w.delta, H, Nq, Nq_pad, rows);
+    if (cudaGetLastError() != cudaSuccess) return FMHA_ERR_LAUNCH;
+  }
+
+  {
+    CUtensorMap tq, tk, tv, tdo, tdk, tdv;
+    int rc;
+    if ((rc = make_tensor_map(&tq, p->q, Z, Nq, H, D, p->q_strides))) return rc;
+    if ((rc = make_tensor_map(&tk, p->k, Z, Nk, H, D, p->k_strides))) return rc;
+    if ((rc = make_tensor_map(&tv, p->v, Z, Nk, H, D, p->v_strides))) return rc;
+    if ((rc = make_tensor_map(&tdo, p->dout, Z, Nq, H, D, p->dout_strides))) return rc;
+    // with fp32 accumulation the fp16 outputs are not touched: any valid map will do
+    const bool acc_k = p->dk_accum != nullptr, acc_v = p->dv_accum != nullptr;
+    if ((rc = make_tensor_map(&tdk, acc_k ? p->k : p->dk, Z, Nk, H, D,
+                              acc_k ? p->k_strides : p->dk_strides)))
+      return rc;
+    if ((rc = make_tensor_map(&tdv, acc_v ? p->v : p->dv, Z, Nk, H, D,
+                              acc_v ? p->v_strides : p->dv_strides)))
+      return rc;
+    fmha::BwdKernelParams kp;
+    kp.dq_accum = w.dq_accum;
+    kp.lse2 = w.lse2;
+    kp.delta = w.delta;
+    kp.dk_accum = p->dk_accum;
+    kp.dv_accum = p->dv_accum;
+    kp.heads = H;
+    kp.seqlen_q = Nq;
+    kp.seqlen_k = Nk;
+    kp.seqlen_q_pad = Nq_pad;
+    kp.num_kv_blocks = (Nk + 127) / 128;
+    kp.scale = p->scale;
+    kp.scale_log2 = p->scale * 1.4426950408889634f;
+    kp.causal = p->causal ? 1 : 0;
+    kp.causal_shift = p->causal_shift;
+    kp.status = p->status;
+    auto kernel = fmha::fmha_bwd_kernel<D>;
+    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, T::kSmemBytes) !=
+        cudaSuccess)
+      return FMHA_ERR_LAUNCH;
+    const unsigned grid = (unsigned)((long long)kp.num_kv_blocks * H * Z);
+    kernel<<<grid, T::kThreads, T::kSmemBytes, stream>>>(tq, tk, tv, tdo, tdk, tdv, kp);
+    if (cudaGetLastError() != cudaSuccess) return FMHA_ERR_LAUNCH;
+  }
+
+  if (!(p->flags & FMHA_BWD_SKIP_DQ_CONVERT)) {
+    const long long rows = (long long)Z * Nq * H;
+    constexpr int rows_per_block = 256 / (D / 8);
+    const unsigned grid = (unsigned)((rows + rows_per_block - 1) / rows_per_block);
+    fmha::fmha_bwd_convert_dq_kernel<D><<<grid, 256, 0, stream>>>(
+        w.dq_accum, static_cast<__half*>(p->dq), to3(p->dq_strides), H, Nq, p->scale, rows);
+    if (cudaGetLastError() != cudaSuccess) return FMHA_ERR_LAUNCH;
+  }
+  return FMHA_OK;
+}
+
+FmhaStrides dense_strides(int n, int head, int k) {
+  FmhaStrides s;
+  s.head = k;
+  s.row = (int64_t)head * k;
+  s.batch = (int64_t)n * head * k;
+  return s;
+}
+
+}  // namespace
+
+extern "C" {
+
+int fmha_fwd(const FmhaFwdParams* p, void* stream) {
+  if (p == nullptr || p->q == nullptr || p->k == nullptr || p->v == nullptr || p->o == nullptr ||
+      p->lse == nullptr)
+    return FMHA_ERR_NULL_POINTER;
+  int rc = check_common(p->batch, p->heads, p->seqlen_q, p->seqlen_k, p->head_dim, p->scale);
+  if (rc) return rc;
+  if (!aligned16(p->q) || !aligned16(p->k) || !aligned16(p->v) || !aligned16(p->o))
+    return FMHA_ERR_BAD_ALIGNMENT;
+  if ((rc = check_strides(p->q_strides, p->seqlen_q, p->heads, p->batch))) return rc;
+  if ((rc = check_strides(p->k_strides, p->seqlen_k, p->heads, p->batch))) return rc;
+  if ((rc = check_strides(p->v_strides, p->seqlen_k, p->heads, p->batch))) return rc;
+  if ((rc = check_strides(p->o_strides, p->seqlen_q, p->heads, p->batch))) return rc;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  return p->head_dim == 128 ? launch_fwd<128>(p, s) : launch_fwd<64>(p, s);
+}
+
+size_t fmha_bwd_workspace_bytes(const FmhaBwdParams* p) {
+  if (p == nullptr || p->batch <= 0 || p->heads <= 0 || p->seqlen_q <= 0 || p->head_dim <= 0)
+    return 0;
+  return carve_workspace(nullptr, p->batch, p->heads, p->seqlen_q, p->head_dim).bytes;
+}
+
+int fmha_bwd(const FmhaBwdParams* p, void* workspace, size_t workspace_bytes, void* stream) {
+  if (p == nullptr || p->q == nullptr || p->k == nullptr || p->v == nullptr || p->dout == nullptr ||
+      p->lse == nullptr)
+    return FMHA_ERR_NULL_POINTER;
+  const bool keep = (p->flags & FMHA_BWD_KEEP_WORKSPACE) != 0;
+  const bool skip_convert = (p->flags & FMHA_BWD_SKIP_DQ_CONVERT) != 0;
+  if (!keep && p->o == nullptr) return FMHA_ERR_NULL_POINTER;
+  if (!skip_convert && p->dq == nullptr) return FMHA_ERR_NULL_POINTER;
+  if (p->dk_accum == nullptr && p->dk == nullptr) return FMHA_ERR_NULL_POINTER;
+  if (p->dv_accum == nullptr && p->dv == nullptr) return FMHA_ERR_NULL_POINTER;
+  int rc = check_common(p->batch, p->heads, p->seqlen_q, p->seqlen_k, p->head_dim, p->scale);
+  if (rc) return rc;
+  if (!aligned16(p->q) || !aligned16(p->k) || !aligned16(p->v) || !aligned16(p->dout) ||
+      (!keep && !aligned16(p->o)) || (!skip_convert && !aligned16(p->dq)) ||
+      (p->dk_accum == nullptr && !aligned16(p->dk)) || (p->dv_accum == nullptr && !aligned16(p->dv)) ||
+      !aligned16(p->dk_accum) || !aligned16(p->dv_accum))
+    return FMHA_ERR_BAD_ALIGNMENT;
+  if ((rc = check_strides(p->q_strides, p->seqlen_q, p->heads, p->batch))) return rc;
+  if ((rc = check_strides(p->k_strides, p->seqlen_k, p->heads, p->batch))) return rc;
+  if ((rc = check_strides(p->v_strides, p->seqlen_k, p->heads, p->batch))) return rc;
+  if ((rc = check_strides(p->dout_strides, p->seqlen_q, p->heads, p->batch))) return rc;
+  if (!keep && (rc = check_strides(p->o_strides, p->seqlen_q, p->heads, p->batch))) return rc;
+  if (!skip_convert && (rc = check_strides(p->dq_strides, p->seqlen_q, p->heads, p->batch)))
+    return rc;
+  if (p->dk_accum == nullptr && (rc = check_strides(p->dk_strides, p->seqlen_k, p->heads, p->batch)))
+    return rc;
+  if (p->dv_accum == nullptr && (rc = check_strides(p->dv_strides, p->seqlen_k, p->heads, p->batch)))
+    return rc;
+  const BwdWorkspace w = carve_workspace(workspace, p->batch, p->heads, p->seqlen_q, p->head_dim);
+  if (workspace == nullptr || workspace_bytes < w.bytes) return FMHA_ERR_WORKSPACE;
+  if (!aligned16(workspace)) return FMHA_ERR_BAD_ALIGNMENT;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  return p->head_dim == 128 ? launch_bwd<128>(p, w, s) : launch_bwd<64>(p, w, s);
+}
+
+int fmha_merge(float* o_acc, float* lse_acc, const void* o_part, FmhaStrides o_part_strides,
+               const float* lse_part, void* o_out, int32_t batch, int32_t heads, int32_t rows,
+               int32_t head_dim, void* stream) {
+  if (o_acc == nullptr || lse_acc == nullptr || o_part == nullptr || lse_part == nullptr)
+    return FMHA_ERR_NULL_POINTER;
+  if (head_dim != 64 && head_dim != 128) return FMHA_ERR_BAD_HEAD_DIM;
+  if (batch <= 0 || heads <= 0 || rows <= 0) return FMHA_ERR_BAD_SHAPE;
+  if (!aligned16(o_acc) || !aligned16(o_part) || !aligned16(o_out)) return FMHA_ERR_BAD_ALIGNMENT;
+  int rc = check_strides(o_part_strides, rows, heads, batch);
+  if (rc) return rc;
+  const long long total = (long long)batch * rows * heads;
+  const int rows_per_block = 256 / (head_dim / 8);
+  const unsigned grid = (unsigned)((total + rows_per_block - 1) / rows_per_block);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (head_dim == 128)
+    fmha::fmha_merge_kernel<128><<<grid, 256, 0, s>>>(
+        o_acc, lse_acc, static_cast<const __half*>(o_part), to3(o_part_strides), lse_part,
+        static_cast<__half*>(o_out), heads, rows, total);
+  else
+    fmha::fmha_merge_kernel<64><<<grid, 256, 0, s>>>(
+        o_acc, lse_acc, static_cast<const __half*>(o_part), to3(o_part_strides), lse_part,
+        static_cast<__half*>(o_out), heads, rows, total);
+  return cudaGetLastError() == cudaSuccess ? FMHA_OK : FMHA_ERR_LAUNCH;
+}
+
+int fmha_b200_forward(const void* query_ptr, const void* key_ptr, const void* value_ptr,
+                      void* output_ptr, void* lse_ptr, int batch, int head, int m, int n, int k,
+                      float scale, int causal, void* stream) {
+  FmhaFwdParams p;
+  std::memset(&p, 0, sizeof(p));
+  p.q = query_ptr;
+  p.k = key_ptr;
+  p.v = value_ptr;
+  p.o = output_ptr;
+  p.lse = static_cast<float*>(lse_ptr);
+  p.q_strides = p.o_strides = dense_strides(m, head, k);
+  p.k_strides = p.v_strides = dense_strides(n, head, k);
+  p.batch = batch;
+  p.heads = head;
+  p.seqlen_q = m;
+  p.seqlen_k = n;
+  p.head_dim = k;
+  p.scale = scale;
+  p.causal = causal;
+  return fmha_fwd(&p, stream);
+}
+
+int fmha_b200_backward(const void* query_ptr, const void* key_ptr, const void* value_ptr,
+                       const void* output_ptr, const void* d_output_ptr, const void* lse_ptr,
+                       void* d_query_ptr, void* d_key_ptr, void* d_value_ptr, void* workspace,
+                       size_t workspace_bytes, int batch, int head, int m, int n, int k,
+                       float scale, int causal, void* stream) {
+  FmhaBwdParams p;
+  std::memset(&p, 0, sizeof(p));
+  p.q = query_ptr;
+  p.k = key_ptr;
+  p.v = value_ptr;
+  p.o = output_ptr;
+  p.dout = d_output_ptr;
+  p.lse = static_cast<const float*>(lse_ptr);
+  p.dq = d_query_ptr;
+  p.dk = d_key_ptr;
+  p.dv = d_value_ptr;
+  p.q_strides = p.o_strides = p.dout_strides = p.dq_strides = dense_strides(m, head, k);
+  p.k_strides = p.v_strides = p.dk_strides = p.dv_strides = dense_strides(n, head, k);
+  p.batch = batch;
+  p.heads = head;
+  p.seqlen_q = m;
+  p.seqlen_k = n;
+  p.head_dim = k;
+  p.scale = scale;
+  p.causal = causal;
+  return fmha_bwd(&p, workspace, workspace_bytes, stream);
+}
+
+const char* fmha_status_string(int status) {
+  switch (status) {
+    case FMHA_OK: return "ok";
+    case FMHA_ERR_NULL_POINTER: return "a required pointer is NULL";
+    case FMHA_ERR_BAD_HEAD_DIM: return "head_dim must be 64 or 128";
+    case FMHA_ERR_BAD_SHAPE: return "sizes must be positive and scale finite and non-zero";
+    case FMHA_ERR_BAD_STRIDE: return "strides must be positive multiples of 8 elements";
+    case FMHA_ERR_BAD_ALIGNMENT: return "pointers must be 16-byte aligned";
+    case FMHA_ERR_WORKSPACE: return "backward workspace missing or too small";
+    case FMHA_ERR_TENSOR_MAP: return "cuTensorMapEncodeTiled rejected a tensor";
+    case FMHA_ERR_NO_DEVICE: return "CUDA driver entry point unavailable";
+    case FMHA_ERR_LAUNCH: return "kernel launch failed";
+    case FMHA_ERR_TOO_LARGE: return "a size exceeds the supported maximum";
+    default: return "unknown status";
+  }
+}
+
+const char* fmha_version(void) { return "0.1.0"; }
+
+}  // extern "C"

@@ -1,0 +1,427 @@
+// Forward attention kernel for sm_100a: O = softmax(scale * Q K^T [+ mask]) V, LSE.
+//
+// Replaces fused_mha_forward_kernel of the reference (kernel/fused_mha_kernel.cu:20-323):
+// same mathematics (online softmax over KV tiles, running max / sum, O rescale), none of its
+// structure.  One CTA owns 256 query rows (two 128-row tiles) of one (batch, head) and walks
+// the KV sequence in 128-row tiles:
+//
+//   warp 8      TMA producer: Q tiles once, then K_0, V_0, K_1, V_1, ... through a ring of
+//               shared-memory slots (full / empty mbarriers per slot)
+//   warp 9      MMA issuer (one thread): S_t = Q_t K_j^T (both operands in shared memory) and
+//               O_t += P_t V_j (P_t read from tensor memory), accumulators in tensor memory
+//   warps 0-3   softmax of query tile 0: one thread per row, S_0 read with tcgen05.ld, online
+//               exp2 softmax, P_0 written back over S_0 as fp16, lazy O_0 rescale, epilogue
+//   warps 4-7   the same for query tile 1
+//
+// While one softmax group works on its tile the tensor pipe runs the other tile's MMAs.
+// Tensor memory (512 columns): S_0 [0,128) S_1 [128,256) O_0 [256,256+D) O_1 [256+D,256+2D);
+// P_t aliases the first 64 columns of S_t (two fp16 per 32-bit column).
+//
+// Shared memory: rows of 64 fp16 (128 bytes) in the TMA / UMMA 128-byte swizzle.  A 128 x D
+// tile is D/64 boxes of 128 x 64, box b at byte offset b * 16384.
+#pragma once
+#include <cuda.h>
+#include <math_constants.h>
+
+#include "ptx.cuh"
+
+namespace fmha {
+
+struct FwdKernelParams {
+  float* lse;
+  int heads, seqlen_q, seqlen_k;
+  int num_q_blocks;  // ceil(seqlen_q / 256)
+  float scale_log2;  // scale * log2(e)
+  int causal, causal_shift;
+  int* status;
+};
+
+template <int D>
+struct FwdTraits {
+  static constexpr int kBlockM = 128;  // rows per query tile
+  static constexpr int kTilesM = 2;    // query tiles per CTA
+  static constexpr int kBlockN = 128;  // rows per KV tile
+  static constexpr int kBoxes = D / 64;
+  static constexpr int kBoxBytes = 128 * 128;  // 128 rows x 128 bytes
+  static constexpr int kTileBytes = kBoxes * kBoxBytes;
+  static constexpr int kStages = (D == 128) ? 4 : 8;
+  static constexpr int kThreads = 320;
+  static constexpr int kSmemBytes = 1024 + (kTilesM + kStages) * kTileBytes;
+  static constexpr int kTmemCols = 512;
+  static constexpr uint32_t kIdescQK = umma_idesc_f16(128, kBlockN, 0, 0);
+  static constexpr uint32_t kIdescPV = umma_idesc_f16(128, D, 0, 1);
+};
+
+// lazy rescale threshold in the log2 domain: P may grow to 2^8 before O is rescaled
+constexpr float kRescaleThreshold = 8.0f;
+
+template <int D>
+__global__ void __launch_bounds__(320, 1)
+    fmha_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+                    const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_o,
+                    const FwdKernelParams p) {
+  using T = FwdTraits<D>;
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ uint64_t bar_q_full;
+  __shared__ uint64_t bar_kv_full[T::kStages];
+  __shared__ uint64_t bar_kv_empty[T::kStages];
+  __shared__ uint64_t bar_s_full[2];
+  __shared__ uint64_t bar_p_full[2];
+  __shared__ uint64_t bar_o_full[2];
+  __shared__ uint32_t tmem_base_slot;
+  __shared__ int abort_word;
+  __shared__ int skip_cta;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  // a status word already set by an earlier CTA means: drain the grid quickly
+  if (threadIdx.x == 0) {
+    skip_cta = (p.status != nullptr && *reinterpret_cast<volatile int*>(p.status) != 0) ? 1 : 0;
+    abort_word = 0;
+  }
+  __syncthreads();
+  if (skip_cta) return;
+
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const uint32_t q_smem = smem_base;                                // 2 query tiles
+  const uint32_t ring_smem = smem_base + T::kTilesM * T::kTileBytes;  // K/V ring
+
+  // ---- tile coordinates: consecutive CTAs = same head, heavy (late) query blocks first
+  const int nqb = p.num_q_blocks;
+  const int zh = blockIdx.x / nqb;
+  const int qb = nqb - 1 - (blockIdx.x % nqb);
+  const int z = zh / p.heads;
+  const int h = zh % p.heads;
+  const int q0 = qb * (T::kBlockM * T::kTilesM);
+
+  const int nk_total = (p.seqlen_k + T::kBlockN - 1) / T::kBlockN;
+  int n_kv[2];
+#pragma unroll
+  for (int t = 0; t < 2; ++t) {
+    const int r0 = q0 + t * T::kBlockM;
+    if (r0 >= p.seqlen_q) {
+      n_kv[t] = 0;
+    } else if (!p.causal) {
+      n_kv[t] = nk_total;
+    } else {
+      const int r_last = min(r0 + T::kBlockM - 1, p.seqlen_q - 1);
+      const long long lim = (long long)r_last + p.causal_shift;
+      n_kv[t] = lim < 0 ? 0 : (int)min((long long)nk_total, lim / T::kBlockN + 1);
+    }
+  }
+  const int n_max = max(n_kv[0], n_kv[1]);
+
+  // ---- set-up: barriers (thread 0), tensor memory (warp 9)
+  if (threadIdx.x == 0) {
+    mbar_init(smem_u32(&bar_q_full), 1);
+    for (int s = 0; s < T::kStages; ++s) {
+      mbar_init(smem_u32(&bar_kv_full[s]), 1);
+      mbar_init(smem_u32(&bar_kv_empty[s]), 1);
+    }
+    for (int t = 0; t < 2; ++t) {
+      mbar_init(smem_u32(&bar_s_full[t]), 1);
+      mbar_init(smem_u32(&bar_p_full[t]), 128);
+      mbar_init(smem_u32(&bar_o_full[t]), 1);
+    }
+    fence_barrier_init();
+  }
+  if (warp == 9) {
+    tmem_alloc(smem_u32(&tmem_base_slot), T::kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = tmem_base_slot;
+
+  if (warp == 8) {
+    // =========================== TMA producer ===========================
+    if (lane == 0 && n_max > 0) {
+      tma_prefetch_desc(&tm_q);
+      tma_prefetch_desc(&tm_k);
+      tma_prefetch_desc(&tm_v);
+      const uint32_t qbar = smem_u32(&bar_q_full);
+      mbar_arrive_expect_tx(qbar, T::kTilesM * T::kTileBytes);
+#pragma unroll
+      for (int t = 0; t < T::kTilesM; ++t)
+#pragma unroll
+        for (int b = 0; b < T::kBoxes; ++b)
+          tma_load_4d(q_smem + t * T::kTileBytes + b * T::kBoxBytes, &tm_q, qbar, b * 64,
+                      q0 + t * T::kBlockM, h, z);
+      const int n_loads = 2 * n_max;  // K_0, V_0, K_1, V_1, ...
+      for (int it = 0; it < n_loads; ++it) {
+        const int slot = it % T::kStages;
+        const int round = it / T::kStages;
+        if (round > 0 &&
+            !mbar_wait(smem_u32(&bar_kv_empty[slot]), (round - 1) & 1, &abort_word, 1))
+          break;
+        const uint32_t fbar = smem_u32(&bar_kv_full[slot]);
+        mbar_arrive_expect_tx(fbar, T::kTileBytes);
+        const CUtensorMap* tm = (it & 1) ? &tm_v : &tm_k;
+        const int row = (it >> 1) * T::kBlockN;
+#pragma unroll
+        for (int b = 0; b < T::kBoxes; ++b)
+          tma_load_4d(ring_smem + slot * T::kTileBytes + b * T::kBoxBytes, tm, fbar, b * 64, row,
+                      h, z);
+      }
+    }
+    __syncwarp();
+  } else if (warp == 9) {
+    // =========================== MMA issuer ===========================
+    if (lane == 0 && n_max > 0) {
+      auto issue_qk = [&](int t, uint32_t k_addr) {
+        const uint32_t d = tmem_base + t * 128;
+#pragma unroll
+        for (int ks = 0; ks < D / 16; ++ks) {
+          const uint32_t off = (ks >> 2) * T::kBoxBytes + (ks & 3) * 32;
+          umma_ss(d, umma_smem_desc(q_smem + t * T::kTileBytes + off, 16, 1024),
+                  umma_smem_desc(k_addr + off, 16, 1024), T::kIdescQK, ks > 0 ? 1u : 0u);
+        }
+      };
+      auto issue_pv = [&](int t, uint32_t v_addr, bool accumulate) {
+        const uint32_t d = tmem_base + 256 + t * D;
+        const uint32_t a = tmem_base + t * 128;
+#pragma unroll
+        for (int ks = 0; ks < T::kBlockN / 16; ++ks) {
+          umma_ts(d, a + ks * 8, umma_smem_desc(v_addr + ks * 2048, T::kBoxBytes, 1024),
+                  T::kIdescPV, (accumulate || ks > 0) ? 1u : 0u);
+        }
+      };
+      bool ok = mbar_wait(smem_u32(&bar_q_full), 0, &abort_word, 2);
+      ok = ok && mbar_wait(smem_u32(&bar_kv_full[0]), 0, &abort_word, 3);
+      if (ok) {
+        tc_fence_after();
+#pragma unroll
+        for (int t = 0; t < 2; ++t)
+          if (n_kv[t] > 0) {
+            issue_qk(t, ring_smem);
+            umma_commit(smem_u32(&bar_s_full[t]));
+          }
+        umma_commit(smem_u32(&bar_kv_empty[0]));
+      }
+      for (int j = 0; ok && j < n_max; ++j) {
+        const int it_v = 2 * j + 1;
+        const int slot_v = it_v % T::kStages;
+        if (!mbar_wait(smem_u32(&bar_kv_full[slot_v]), (it_v / T::kStages) & 1, &abort_word, 4)) {
+          ok = false;
+          break;
+        }
+        const bool have_next = (j + 1 < n_max);
+        const int it_k = 2 * j + 2;
+        const int slot_k = it_k % T::kStages;
+        bool k_ready = false;
+#pragma unroll
+        for (int t = 0; t < 2; ++t) {
+          if (j < n_kv[t]) {
+            if (!mbar_wait(smem_u32(&bar_p_full[t]), j & 1, &abort_word, 5)) {
+              ok = false;
+              break;
+            }
+            tc_fence_after();
+            issue_pv(t, ring_smem + slot_v * T::kTileBytes, j > 0);
+            if (j + 1 < n_kv[t]) {
+              if (!k_ready) {
+                if (!mbar_wait(smem_u32(&bar_kv_full[slot_k]), (it_k / T::kStages) & 1,
+                               &abort_word, 6)) {
+                  ok = false;
+                  break;
+                }
+                tc_fence_after();
+                k_ready = true;
+              }
+              issue_qk(t, ring_smem + slot_k * T::kTileBytes);
+              umma_commit(smem_u32(&bar_s_full[t]));
+            } else {
+              umma_commit(smem_u32(&bar_o_full[t]));
+            }
+          }
+        }
+        if (!ok) break;
+        umma_commit(smem_u32(&bar_kv_empty[slot_v]));
+        if (have_next) umma_commit(smem_u32(&bar_kv_empty[slot_k]));
+      }
+    }
+    __syncwarp();
+  } else {
+    // =========================== softmax / epilogue ===========================
+    const int t = warp >> 2;    // query tile of this warpgroup
+    const int quad = warp & 3;  // TMEM lane quadrant of this warp
+    const int row_in_tile = quad * 32 + lane;
+    const int row = q0 + t * T::kBlockM + row_in_tile;
+    const uint32_t lane_addr = uint32_t(quad * 32) << 16;
+    const uint32_t tS = tmem_base + lane_addr + t * 128;
+    const uint32_t tO = tmem_base + lane_addr + 256 + t * D;
+    const float c = p.scale_log2;
+    // a masked score must give exp2(s * c - m * c) = 0 whatever the sign of c
+    const float mask_val = (c >= 0.f) ? -CUDART_INF_F : CUDART_INF_F;
+    long long lim_ll = p.causal ? (long long)row + p.causal_shift : (long long)p.seqlen_k - 1;
+    lim_ll = min(lim_ll, (long long)p.seqlen_k - 1);
+    lim_ll = max(lim_ll, -1ll);
+    const int row_limit = (int)lim_ll;  // last visible key of this row (-1 = none)
+
+    float m_ref = mask_val;  // reference score of the running softmax (raw, unscaled)
+    float l = 0.f;           // running sum of exp2((s - m_ref) * c)
+    const int n = n_kv[t];
+    const bool tile_valid = (q0 + t * T::kBlockM) < p.seqlen_q;
+
+    for (int j = 0; j < n; ++j) {
+      if (!mbar_wait(smem_u32(&bar_s_full[t]), j & 1, &abort_word, 7)) break;
+      tc_fence_after();
+      uint32_t s[4][32];
+      tmem_ld32(tS + 0, s[0]);
+      tmem_ld32(tS + 32, s[1]);
+      tmem_ld32(tS + 64, s[2]);
+      tmem_ld32(tS + 96, s[3]);
+      tmem_wait_ld();
+
+      const int lim = row_limit - j * T::kBlockN;  // columns > lim of this tile are masked
+      if (lim < T::kBlockN - 1) {
+#pragma unroll
+        for (int cc = 0; cc < 4; ++cc)
+#pragma unroll
+          for (int i = 0; i < 32; ++i)
+            if (cc * 32 + i > lim) s[cc][i] = __float_as_uint(mask_val);
+      }
+
+      // row extreme: max of s when c >= 0, min when c < 0, so that m * c = max(s * c)
+      float mx0 = __uint_as_float(s[0][0]), mx1 = __uint_as_float(s[1][0]);
+      float mx2 = __uint_as_float(s[2][0]), mx3 = __uint_as_float(s[3][0]);
+      if (c >= 0.f) {
+#pragma unroll
+        for (int i = 1; i < 32; ++i) {
+          mx0 = fmaxf(mx0, __uint_as_float(s[0][i]));
+          mx1 = fmaxf(mx1, __uint_as_float(s[1][i]));
+          mx2 = fmaxf(mx2, __uint_as_float(s[2][i]));
+          mx3 = fmaxf(mx3, __uint_as_float(s[3][i]));
+        }
+      } else {
+#pragma unroll
+        for (int i = 1; i < 32; ++i) {
+          mx0 = fminf(mx0, __uint_as_float(s[0][i]));
+          mx1 = fminf(mx1, __uint_as_float(s[1][i]));
+          mx2 = fminf(mx2, __uint_as_float(s[2][i]));
+          mx3 = fminf(mx3, __uint_as_float(s[3][i]));
+        }
+      }
+      const float mx = (c >= 0.f) ? fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3))
+                                  : fminf(fminf(mx0, mx1), fminf(mx2, mx3));
+
+      if (j == 0) {
+        m_ref = mx;
+      } else {
+        const float m_new = (c >= 0.f) ? fmaxf(m_ref, mx) : fminf(m_ref, mx);
+        // growth of the scaled maximum; NaN (inf - inf) compares false
+        const bool need = (m_new - m_ref) * c > kRescaleThreshold;
+        if (__any_sync(0xffffffffu, need)) {
+          // O_t is idle here: S_t(j) is committed after O_t += P_t V_(j-1) was issued
+          const float alpha = isinf(m_new) ? 1.f : fast_exp2((m_ref - m_new) * c);
+          l *= alpha;
+          m_ref = m_new;
+#pragma unroll
+          for (int cc = 0; cc < D / 32; ++cc) {
+            uint32_t o[32];
+            tmem_ld32(tO + cc * 32, o);
+            tmem_wait_ld();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+            tmem_st32(tO + cc * 32, o);
+          }
+        }
+      }
+
+      const float neg_mc = isinf(m_ref) ? 0.f : -m_ref * c;
+      float l0 = 0.f, l1 = 0.f, l2 = 0.f, l3 = 0.f;
+#pragma unroll
+      for (int hf = 0; hf < 2; ++hf) {  // 64 scores -> 32 packed columns of P at a time
+        uint32_t pk[32];
+#pragma unroll
+        for (int c2 = 0; c2 < 2; ++c2) {
+          const int cc = hf * 2 + c2;
+#pragma unroll
+          for (int i = 0; i < 32; i += 4) {
+            const float p0 = fast_exp2(fmaf(__uint_as_float(s[cc][i + 0]), c, neg_mc));
+            const float p1 = fast_exp2(fmaf(__uint_as_float(s[cc][i + 1]), c, neg_mc));
+            const float p2 = fast_exp2(fmaf(__uint_as_float(s[cc][i + 2]), c, neg_mc));
+            const float p3 = fast_exp2(fmaf(__uint_as_float(s[cc][i + 3]), c, neg_mc));
+            l0 += p0;
+            l1 += p1;
+            l2 += p2;
+            l3 += p3;
+            pk[c2 * 16 + (i >> 1) + 0] = pack_half2(p0, p1);
+            pk[c2 * 16 + (i >> 1) + 1] = pack_half2(p2, p3);
+          }
+        }
+        tmem_st32(tS + hf * 32, pk);
+      }
+      l += (l0 + l1) + (l2 + l3);
+      tmem_wait_st();
+      tc_fence_before();
+      mbar_arrive(smem_u32(&bar_p_full[t]));
+    }
+
+    // ---- epilogue: O_t / l -> fp16 -> shared memory (over Q_t) -> TMA store; LSE
+    if (tile_valid) {
+      if (n > 0) mbar_wait(smem_u32(&bar_o_full[t]), 0, &abort_word, 8);
+      tc_fence_after();
+      const float inv_l = (l > 0.f) ? 1.f / l : 0.f;
+      const uint32_t o_smem = q_smem + t * T::kTileBytes;
+#pragma unroll
+      for (int cc = 0; cc < D / 32; ++cc) {
+        uint32_t o[32];
+        if (n > 0) {
+          tmem_ld32(tO + cc * 32, o);
+          tmem_wait_ld();
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) o[i] = 0u;
+        }
+#pragma unroll
+        for (int qd = 0; qd < 4; ++qd) {
+          const int ch = cc * 4 + qd;  // 16-byte chunk (8 fp16) of the row
+          const uint32_t addr = o_smem + (ch >> 3) * T::kBoxBytes + row_in_tile * 128 +
+                                (((ch & 7) ^ (row_in_tile & 7)) << 4);
+          const uint32_t w0 = pack_half2(__uint_as_float(o[qd * 8 + 0]) * inv_l,
+                                         __uint_as_float(o[qd * 8 + 1]) * inv_l);
+          const uint32_t w1 = pack_half2(__uint_as_float(o[qd * 8 + 2]) * inv_l,
+                                         __uint_as_float(o[qd * 8 + 3]) * inv_l);
+          const uint32_t w2 = pack_half2(__uint_as_float(o[qd * 8 + 4]) * inv_l,
+                                         __uint_as_float(o[qd * 8 + 5]) * inv_l);
+          const uint32_t w3 = pack_half2(__uint_as_float(o[qd * 8 + 6]) * inv_l,
+                                         __uint_as_float(o[qd * 8 + 7]) * inv_l);
+          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(w0), "r"(w1),
+                       "r"(w2), "r"(w3)
+                       : "memory");
+        }
+      }
+      if (row < p.seqlen_q) {
+        const float lse = (l > 0.f) ? (m_ref * c + log2f(l)) * 0.6931471805599453f : -CUDART_INF_F;
+        p.lse[((size_t)z * p.heads + h) * p.seqlen_q + row] = lse;
+      }
+      fence_proxy_async_smem();
+      named_bar_sync(1 + t, 128);
+      if (row_in_tile == 0) {
+#pragma unroll
+        for (int b = 0; b < T::kBoxes; ++b)
+          tma_store_4d(&tm_o, o_smem + b * T::kBoxBytes, b * 64, q0 + t * T::kBlockM, h, z);
+        tma_commit_group();
+        tma_wait_group<0>();
+      }
+    }
+  }
+
+  // ---- teardown
+  tc_fence_before();
+  __syncthreads();
+  if (abort_word != 0) {
+    if (threadIdx.x == 0 && p.status != nullptr) atomicCAS(p.status, 0, abort_word);
+    // let copies that may still be in flight land before the shared memory is released
+    for (int i = 0; i < 64; ++i) __nanosleep(1000);
+  }
+  if (warp == 9) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, T::kTmemCols);
+  }
+}
+
+}  // namespace fmha

@@ -1,0 +1,236 @@
+"""ctypes binding of the C ABI in ``include/fmha_b200.h`` for torch tensors.
+
+This is the same boundary a non-Python host would bind (the reference's launchers,
+``include/fused_mha.h:1-6``): plain pointers, sizes and a stream.  It exposes what the public
+``flash_attn_func`` does not need but the multi-GPU layer and the tests do: different query /
+key lengths, ``causal_shift``, fp32 dK/dV accumulation, the LSE merge, and the status word.
+
+Loading fails loudly if ``lib/libfmha_b200.so`` has not been built; nothing here computes on
+the CPU.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+from typing import Optional
+
+import torch
+
+_LIB_PATH = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "lib",
+                         "libfmha_b200.so")
+
+FMHA_OK = 0
+FMHA_BWD_KEEP_WORKSPACE = 1
+FMHA_BWD_SKIP_DQ_CONVERT = 2
+
+EXPORTED_SYMBOLS = (
+    "fmha_fwd", "fmha_bwd_workspace_bytes", "fmha_bwd", "fmha_merge", "fmha_b200_forward",
+    "fmha_b200_backward", "fmha_status_string", "fmha_version",
+)
+
+
+class FmhaStrides(ctypes.Structure):
+    _fields_ = [("batch", ctypes.c_int64), ("row", ctypes.c_int64), ("head", ctypes.c_int64)]
+
+
+class FmhaFwdParams(ctypes.Structure):
+    _fields_ = [
+        ("q", ctypes.c_void_p), ("k", ctypes.c_void_p), ("v", ctypes.c_void_p),
+        ("o", ctypes.c_void_p), ("lse", ctypes.c_void_p),
+        ("q_strides", FmhaStrides), ("k_strides", FmhaStrides), ("v_strides", FmhaStrides),
+        ("o_strides", FmhaStrides),
+        ("batch", ctypes.c_int32), ("heads", ctypes.c_int32), ("seqlen_q", ctypes.c_int32),
+        ("seqlen_k", ctypes.c_int32), ("head_dim", ctypes.c_int32),
+        ("scale", ctypes.c_float), ("causal", ctypes.c_int32), ("causal_shift", ctypes.c_int32),
+        ("status", ctypes.c_void_p),
+    ]
+
+
+class FmhaBwdParams(ctypes.Structure):
+    _fields_ = [
+        ("q", ctypes.c_void_p), ("k", ctypes.c_void_p), ("v", ctypes.c_void_p),
+        ("o", ctypes.c_void_p), ("dout", ctypes.c_void_p), ("lse", ctypes.c_void_p),
+        ("dq", ctypes.c_void_p), ("dk", ctypes.c_void_p), ("dv", ctypes.c_void_p),
+        ("dk_accum", ctypes.c_void_p), ("dv_accum", ctypes.c_void_p),
+        ("q_strides", FmhaStrides), ("k_strides", FmhaStrides), ("v_strides", FmhaStrides),
+        ("o_strides", FmhaStrides), ("dout_strides", FmhaStrides),
+        ("dq_strides", FmhaStrides), ("dk_strides", FmhaStrides), ("dv_strides", FmhaStrides),
+        ("batch", ctypes.c_int32), ("heads", ctypes.c_int32), ("seqlen_q", ctypes.c_int32),
+        ("seqlen_k", ctypes.c_int32), ("head_dim", ctypes.c_int32),
+        ("scale", ctypes.c_float), ("causal", ctypes.c_int32), ("causal_shift", ctypes.c_int32),
+        ("flags", ctypes.c_int32), ("status", ctypes.c_void_p),
+    ]
+
+
+_lib = None
+
+
+def load_library() -> ctypes.CDLL:
+    """dlopen ``lib/libfmha_b200.so`` (once) and declare the prototypes."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not os.path.exists(_LIB_PATH):
+        raise RuntimeError(
+            f"{_LIB_PATH} is missing: build it with `python flash-attention-v100_b200/build.py` "
+            "(there is no CPU fallback)")
+    lib = ctypes.CDLL(_LIB_PATH)
+    lib.fmha_fwd.restype = ctypes.c_int
+    lib.fmha_fwd.argtypes = [ctypes.POINTER(FmhaFwdParams), ctypes.c_void_p]
+    lib.fmha_bwd_workspace_bytes.restype = ctypes.c_size_t
+    lib.fmha_bwd_workspace_bytes.argtypes = [ctypes.POINTER(FmhaBwdParams)]
+    lib.fmha_bwd.restype = ctypes.c_int
+    lib.fmha_bwd.argtypes = [ctypes.POINTER(FmhaBwdParams), ctypes.c_void_p, ctypes.c_size_t,
+                             ctypes.c_void_p]
+    lib.fmha_merge.restype = ctypes.c_int
+    lib.fmha_merge.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, FmhaStrides,
+                               ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int32, ctypes.c_int32,
+                               ctypes.c_int32, ctypes.c_int32, ctypes.c_void_p]
+    lib.fmha_b200_forward.restype = ctypes.c_int
+    lib.fmha_b200_forward.argtypes = [ctypes.c_void_p] * 5 + [ctypes.c_int] * 5 + [
+        ctypes.c_float, ctypes.c_int, ctypes.c_void_p]
+    lib.fmha_b200_backward.restype = ctypes.c_int
+    lib.fmha_b200_backward.argtypes = [ctypes.c_void_p] * 10 + [ctypes.c_size_t] + [
+        ctypes.c_int] * 5 + [ctypes.c_float, ctypes.c_int, ctypes.c_void_p]
+    lib.fmha_status_string.restype = ctypes.c_char_p
+    lib.fmha_status_string.argtypes = [ctypes.c_int]
+    lib.fmha_version.restype = ctypes.c_char_p
+    lib.fmha_version.argtypes = []
+    _lib = lib
+    return lib
+
+
+def status_string(rc: int) -> str:
+    return load_library().fmha_status_string(rc).decode()
+
+
+def _check(rc: int, what: str):
+    if rc != FMHA_OK:
+        raise RuntimeError(f"{what} failed: {status_string(rc)} (status {rc})")
+
+
+def _strides(t: torch.Tensor) -> FmhaStrides:
+    return FmhaStrides(t.stride(0), t.stride(1), t.stride(2))
+
+
+def _ptr(t: Optional[torch.Tensor]):
+    return None if t is None else ctypes.c_void_p(t.data_ptr())
+
+
+def _stream(stream) -> ctypes.c_void_p:
+    if stream is None:
+        stream = torch.cuda.current_stream()
+    return ctypes.c_void_p(stream.cuda_stream)
+
+
+def _require_cuda_half(*tensors):
+    for t in tensors:
+        if t is None:
+            continue
+        if not t.is_cuda or t.dtype != torch.float16 or t.dim() != 4 or t.stride(-1) != 1:
+            raise RuntimeError("expected fp16 CUDA tensors (batch, seqlen, heads, head_dim) with a "
+                               "contiguous last dimension")
+
+
+def fwd_params(q, k, v, o, lse, scale, causal, causal_shift=0, status=None) -> FmhaFwdParams:
+    p = FmhaFwdParams()
+    p.q, p.k, p.v, p.o, p.lse = q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), lse.data_ptr()
+    p.q_strides, p.k_strides, p.v_strides, p.o_strides = _strides(q), _strides(k), _strides(v), _strides(o)
+    p.batch, p.seqlen_q, p.heads, p.head_dim = q.shape
+    p.seqlen_k = k.shape[1]
+    p.scale = float(scale)
+    p.causal = int(bool(causal))
+    p.causal_shift = int(causal_shift)
+    p.status = None if status is None else status.data_ptr()
+    return p
+
+
+def fwd(q, k, v, scale: float, causal: bool = False, causal_shift: int = 0,
+        out: Optional[torch.Tensor] = None, lse: Optional[torch.Tensor] = None,
+        status: Optional[torch.Tensor] = None, stream=None):
+    """O, LSE through ``fmha_fwd`` on the current (or given) stream; outputs allocated with torch
+    unless passed in."""
+    _require_cuda_half(q, k, v, out)
+    Z, Nq, H, D = q.shape
+    if out is None:
+        out = torch.empty_like(q)
+    if lse is None:
+        lse = torch.empty((Z, H, Nq), dtype=torch.float32, device=q.device)
+    p = fwd_params(q, k, v, out, lse, scale, causal, causal_shift, status)
+    with torch.cuda.device(q.device):
+        _check(load_library().fmha_fwd(ctypes.byref(p), _stream(stream)), "fmha_fwd")
+    return out, lse
+
+
+def bwd_params(q, k, v, o, dout, lse, dq, dk, dv, scale, causal, causal_shift=0, dk_accum=None,
+               dv_accum=None, flags=0, status=None) -> FmhaBwdParams:
+    p = FmhaBwdParams()
+    p.q, p.k, p.v, p.dout, p.lse = q.data_ptr(), k.data_ptr(), v.data_ptr(), dout.data_ptr(), lse.data_ptr()
+    p.o = None if o is None else o.data_ptr()
+    p.dq = None if dq is None else dq.data_ptr()
+    p.dk = None if dk is None else dk.data_ptr()
+    p.dv = None if dv is None else dv.data_ptr()
+    p.dk_accum = None if dk_accum is None else dk_accum.data_ptr()
+    p.dv_accum = None if dv_accum is None else dv_accum.data_ptr()
+    p.q_strides, p.k_strides, p.v_strides = _strides(q), _strides(k), _strides(v)
+    p.dout_strides = _strides(dout)
+    if o is not None:
+        p.o_strides = _strides(o)
+    if dq is not None:
+        p.dq_strides = _strides(dq)
+    if dk is not None:
+        p.dk_strides = _strides(dk)
+    if dv is not None:
+        p.dv_strides = _strides(dv)
+    p.batch, p.seqlen_q, p.heads, p.head_dim = q.shape
+    p.seqlen_k = k.shape[1]
+    p.scale = float(scale)
+    p.causal = int(bool(causal))
+    p.causal_shift = int(causal_shift)
+    p.flags = int(flags)
+    p.status = None if status is None else status.data_ptr()
+    return p
+
+
+def bwd_workspace_bytes(Z: int, Nq: int, H: int, D: int) -> int:
+    p = FmhaBwdParams()
+    p.batch, p.seqlen_q, p.heads, p.head_dim = Z, Nq, H, D
+    return int(load_library().fmha_bwd_workspace_bytes(ctypes.byref(p)))
+
+
+def bwd(q, k, v, o, dout, lse, scale: float, causal: bool = False, causal_shift: int = 0,
+        dq=None, dk=None, dv=None, dk_accum=None, dv_accum=None, workspace=None, flags: int = 0,
+        status=None, stream=None):
+    """dQ, dK, dV through ``fmha_bwd``.  Outputs and workspace are allocated with torch unless
+    passed in; with ``dk_accum`` / ``dv_accum`` (fp32) the fp16 dK / dV are not produced."""
+    _require_cuda_half(q, k, v, o, dout, dq, dk, dv)
+    Z, Nq, H, D = q.shape
+    if dq is None and not (flags & FMHA_BWD_SKIP_DQ_CONVERT):
+        dq = torch.empty_like(q)
+    if dk is None and dk_accum is None:
+        dk = torch.empty_like(k)
+    if dv is None and dv_accum is None:
+        dv = torch.empty_like(v)
+    if workspace is None:
+        workspace = torch.empty(bwd_workspace_bytes(Z, Nq, H, D), dtype=torch.uint8, device=q.device)
+    p = bwd_params(q, k, v, o, dout, lse, dq, dk, dv, scale, causal, causal_shift, dk_accum,
+                   dv_accum, flags, status)
+    with torch.cuda.device(q.device):
+        _check(load_library().fmha_bwd(ctypes.byref(p), ctypes.c_void_p(workspace.data_ptr()),
+                                       workspace.numel() * workspace.element_size(),
+                                       _stream(stream)), "fmha_bwd")
+    return dq, dk, dv
+
+
+def merge(o_acc, lse_acc, o_part, lse_part, o_out=None, stream=None):
+    """In-place LSE merge of (o_part fp16, lse_part) into (o_acc fp32 contiguous, lse_acc)."""
+    Z, N, H, D = o_part.shape
+    if not (o_acc.is_contiguous() and lse_acc.is_contiguous() and lse_part.is_contiguous()):
+        raise RuntimeError("o_acc, lse_acc and lse_part must be contiguous")
+    if o_out is not None and not o_out.is_contiguous():
+        raise RuntimeError("o_out must be contiguous")
+    with torch.cuda.device(o_part.device):
+        _check(load_library().fmha_merge(_ptr(o_acc), _ptr(lse_acc), _ptr(o_part), _strides(o_part),
+                                         _ptr(lse_part), _ptr(o_out), Z, H, N, D, _stream(stream)),
+               "fmha_merge")
+    return o_acc, lse_acc

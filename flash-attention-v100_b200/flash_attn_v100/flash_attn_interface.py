@@ -1,0 +1,80 @@
+"""Python surface and autograd glue of the B200 attention library.
+
+Mirrors ``flash_attn_v100/flash_attn_interface.py`` of the reference: the same public
+``flash_attn_func(q, k, v, softmax_scale=None, causal=False)`` (reference :101-110), the same
+``FlashAttnFunc`` autograd Function with five inputs and ``(dq, dk, dv, None, None)`` gradients
+(:62-99), the same helper names ``_flash_attn_forward`` / ``_flash_attn_backward`` (:11-60), on
+fp16 CUDA tensors of shape (Z, N_CTX, H, D_HEAD).
+
+What changed underneath:
+  * the extension ``flash_attn_v100_cuda`` runs hand-written sm_100a kernels and returns one
+    log-sum-exp per row instead of the (max, sum) pair (the pair is still returned for
+    compatibility: max carries the LSE and sum is all ones);
+  * D = rowsum(dO * O) is computed in fp32 inside the extension, not here in fp16 (:43-44);
+  * dq/dk/dv need no zero-fill (:84): the kernels overwrite them;
+  * the contract "N_CTX is a multiple of 32, right-padded by the caller" (README.md:3) is
+    checked, and tail tiles are masked inside the kernels.
+
+There is no CPU path: importing this module needs the compiled extension, and calling it needs
+a CUDA device.
+"""
+from typing import Optional
+
+import torch
+
+# the CUDA kernels must be imported after torch (same order as the reference, :8-9)
+import flash_attn_v100_cuda as flash_attn_cuda
+
+
+def _maybe_contiguous(x):
+    return x.contiguous() if x.stride(-1) != 1 else x
+
+
+def _flash_attn_forward(q, k, v, softmax_scale, causal):
+    q, k, v = [_maybe_contiguous(x) for x in (q, k, v)]
+    out, softmax_lse, softmax_sum = flash_attn_cuda.fwd(q, k, v, None, softmax_scale, causal)
+    return out, q, k, v, softmax_lse, softmax_sum
+
+
+def _flash_attn_backward(dout, q, k, v, out, softmax_lse, softmax_sum, dq, dk, dv,
+                         softmax_scale, causal):
+    # dq, dk, dv are allocated by us, so they are contiguous already
+    dout, q, k, v, out = [_maybe_contiguous(x) for x in (dout, q, k, v, out)]
+    dq, dk, dv = flash_attn_cuda.bwd(
+        dout, q, k, v, out,
+        None,          # D: computed by the extension in fp32
+        softmax_sum,   # None here: softmax_lse already is max + ln(sum)
+        softmax_lse,
+        dq, dk, dv, softmax_scale, causal,
+    )
+    return dq, dk, dv
+
+
+class FlashAttnFunc(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, q, k, v, softmax_scale, causal):
+        if softmax_scale is None:
+            softmax_scale = q.shape[-1] ** (-0.5)
+        out, q, k, v, softmax_lse, _ = _flash_attn_forward(q, k, v, softmax_scale, causal=causal)
+        ctx.save_for_backward(q, k, v, out, softmax_lse)
+        ctx.softmax_scale = softmax_scale
+        ctx.causal = causal
+        return out
+
+    @staticmethod
+    def backward(ctx, dout, *args):
+        q, k, v, out, softmax_lse = ctx.saved_tensors
+        dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+        _flash_attn_backward(dout, q, k, v, out, softmax_lse, None, dq, dk, dv,
+                             ctx.softmax_scale, ctx.causal)
+        return dq, dk, dv, None, None
+
+
+def flash_attn_func(q, k, v, softmax_scale: Optional[float] = None, causal: bool = False):
+    """softmax(q k^T * softmax_scale [+ causal mask]) v with autograd.
+
+    q, k, v: fp16 CUDA tensors (batch, seqlen, heads, head_dim), head_dim 64 or 128, seqlen a
+    multiple of 32.  softmax_scale defaults to head_dim ** -0.5.  Returns (batch, seqlen, heads,
+    head_dim) fp16.
+    """
+    return FlashAttnFunc.apply(q, k, v, softmax_scale, causal)

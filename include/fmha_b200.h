@@ -1,0 +1,153 @@
+/*
+ * fmha_b200.h - C ABI of the B200 (sm_100a) fused multi-head attention library.
+ *
+ * This header is the drop-in boundary for the attention hot path of
+ * flash-attention-v100.  It replaces the two C++-linkage launchers of the reference
+ * (include/fused_mha.h:1-2 `fused_mha_forward`, include/fused_mha.h:4-6
+ * `fused_mha_backward`, defined in kernel/fused_mha_kernel.cu:891-916) with `extern "C"`
+ * entry points that take plain pointers and sizes, return a status code instead of
+ * `void`, and never abort the process.
+ *
+ * Conventions
+ *  - All tensors are fp16 unless stated; logical layout (Z, N, H, D) = (batch, sequence,
+ *    heads, head_dim) as in the reference (kernel/fused_mha_api.cpp:37-47).  Strides are in
+ *    ELEMENTS and the head_dim stride must be 1.  Row/head/batch strides must be multiples
+ *    of 8 elements and base pointers 16-byte aligned (TMA requirement).
+ *  - `lse` is fp32 (Z, H, seqlen_q) contiguous: lse = max + ln(sum) of the scaled scores,
+ *    i.e. the reference's `softmax_max` and `softmax_sum` (kernel/fused_mha_api.cpp:65-66)
+ *    folded into one number per row.
+ *  - Causal masking: key j is visible to query i iff j <= i + causal_shift.  The reference
+ *    (square, kernel/fused_mha_kernel.cu:232-235) is causal_shift = 0.
+ *  - The library allocates no device memory: the caller owns every buffer, including the
+ *    backward workspace whose size `fmha_bwd_workspace_bytes` reports.
+ *  - `stream` is a cudaStream_t passed as void*.  All launches are asynchronous on it.
+ *  - `status` (optional, may be NULL) points to one int32 in DEVICE memory that the caller
+ *    zeroes once; a kernel that gives up on a bounded wait writes a non-zero code there.
+ *  - Thread safety: entry points keep no mutable global state and may be called from any
+ *    thread with the target device current.
+ */
+#ifndef FMHA_B200_H_
+#define FMHA_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* status codes returned by every entry point */
+enum {
+  FMHA_OK = 0,
+  FMHA_ERR_NULL_POINTER = 1,
+  FMHA_ERR_BAD_HEAD_DIM = 2,   /* head_dim not in {64, 128} */
+  FMHA_ERR_BAD_SHAPE = 3,      /* non-positive sizes */
+  FMHA_ERR_BAD_STRIDE = 4,     /* stride not a multiple of 8 elements, or too small */
+  FMHA_ERR_BAD_ALIGNMENT = 5,  /* pointer not 16-byte aligned */
+  FMHA_ERR_WORKSPACE = 6,      /* workspace missing or too small */
+  FMHA_ERR_TENSOR_MAP = 7,     /* cuTensorMapEncodeTiled failed */
+  FMHA_ERR_NO_DEVICE = 8,      /* no sm_100 device / driver entry point unavailable */
+  FMHA_ERR_LAUNCH = 9,         /* cudaLaunchKernel failed (see cudaGetLastError) */
+  FMHA_ERR_TOO_LARGE = 10      /* a size exceeds a stated limit */
+};
+
+/* element strides of one (Z, N, H, D) tensor; the D stride is 1 */
+typedef struct {
+  int64_t batch;
+  int64_t row;
+  int64_t head;
+} FmhaStrides;
+
+typedef struct {
+  const void* q; /* (Z, seqlen_q, H, D) fp16 */
+  const void* k; /* (Z, seqlen_k, H, D) fp16 */
+  const void* v; /* (Z, seqlen_k, H, D) fp16 */
+  void* o;       /* (Z, seqlen_q, H, D) fp16, written */
+  float* lse;    /* (Z, H, seqlen_q) fp32, written */
+  FmhaStrides q_strides, k_strides, v_strides, o_strides;
+  int32_t batch, heads, seqlen_q, seqlen_k, head_dim;
+  float scale;          /* softmax scale applied to q.k^T */
+  int32_t causal;       /* 0 / 1 */
+  int32_t causal_shift; /* see above; 0 for the reference's square causal mask */
+  int32_t* status;      /* optional device status word */
+} FmhaFwdParams;
+
+typedef struct {
+  const void* q;
+  const void* k;
+  const void* v;
+  const void* o;    /* forward output */
+  const void* dout; /* (Z, seqlen_q, H, D) fp16 upstream gradient */
+  const float* lse; /* (Z, H, seqlen_q) fp32 from the forward */
+  void* dq;         /* (Z, seqlen_q, H, D) fp16, written */
+  void* dk;         /* (Z, seqlen_k, H, D) fp16, written (may be NULL if dk_accum is set) */
+  void* dv;         /* (Z, seqlen_k, H, D) fp16, written (may be NULL if dv_accum is set) */
+  float* dk_accum;  /* optional fp32 (Z, seqlen_k, H, D) contiguous: dK is ADDED into it */
+  float* dv_accum;  /* optional fp32 (Z, seqlen_k, H, D) contiguous: dV is ADDED into it */
+  FmhaStrides q_strides, k_strides, v_strides, o_strides, dout_strides;
+  FmhaStrides dq_strides, dk_strides, dv_strides;
+  int32_t batch, heads, seqlen_q, seqlen_k, head_dim;
+  float scale;
+  int32_t causal;
+  int32_t causal_shift;
+  /* ring attention: 0 = normal (compute D, zero the fp32 dQ accumulator, convert dQ to fp16);
+   * bit 0 set = do not zero the dQ accumulator nor recompute D (workspace carries both over
+   * from an earlier call); bit 1 set = do not convert dQ (a later call will). */
+  int32_t flags;
+  int32_t* status;
+} FmhaBwdParams;
+
+#define FMHA_BWD_KEEP_WORKSPACE 1
+#define FMHA_BWD_SKIP_DQ_CONVERT 2
+
+/* Forward: O = softmax(scale * Q K^T [+ causal mask]) V and LSE.
+ * Replaces fused_mha_forward (include/fused_mha.h:1-2, kernel/fused_mha_kernel.cu:891-902). */
+int fmha_fwd(const FmhaFwdParams* p, void* stream);
+
+/* Bytes of device workspace the backward needs for these sizes: an fp32 dQ accumulator
+ * (Z, seqlen_q, H, D) followed by fp32 D = rowsum(dO * O) (Z, H, seqlen_q).  The reference
+ * has no counterpart: it accumulates dQ with fp16 atomics in place
+ * (kernel/fused_mha_kernel.cu:543,693) and computes D in PyTorch
+ * (flash_attn_v100/flash_attn_interface.py:43-44). */
+size_t fmha_bwd_workspace_bytes(const FmhaBwdParams* p);
+
+/* Backward: dQ, dK, dV.  Runs the D/zero preprocess kernel, the fused dK/dV/dQ kernel and the
+ * dQ convert kernel on `stream`.
+ * Replaces fused_mha_backward (include/fused_mha.h:4-6, kernel/fused_mha_kernel.cu:904-916)
+ * together with the D computation of flash_attn_v100/flash_attn_interface.py:43-44 and the
+ * zero-fill of :84. */
+int fmha_bwd(const FmhaBwdParams* p, void* workspace, size_t workspace_bytes, void* stream);
+
+/* Ring-attention merge of a partial result into running fp32 accumulators, in place:
+ *   lse' = logaddexp(lse_acc, lse_part);  o_acc = e^(lse_acc-lse') o_acc + e^(lse_part-lse') o_part
+ * o_acc fp32 (Z, N, H, D) contiguous, lse_acc fp32 (Z, H, N) contiguous; o_part fp16 with
+ * strides, lse_part fp32 (Z, H, N).  rows = N.  When `o_out` is not NULL the merged result is
+ * also written as fp16 (Z, N, H, D) contiguous (used on the last ring step).
+ * No counterpart in the reference (it has no multi-GPU path). */
+int fmha_merge(float* o_acc, float* lse_acc, const void* o_part, FmhaStrides o_part_strides,
+               const float* lse_part, void* o_out, int32_t batch, int32_t heads, int32_t rows,
+               int32_t head_dim, void* stream);
+
+/* Reference-shaped launchers: same argument meaning as include/fused_mha.h:1-6, dense
+ * (batch, m|n, head, k) tensors, except that the `max`/`sum` pair becomes one `lse` buffer,
+ * the backward's `d_ptr` (fp16 D) is dropped in favour of a caller workspace, and a status
+ * is returned.  m = seqlen_q, n = seqlen_k, k = head_dim. */
+int fmha_b200_forward(const void* query_ptr, const void* key_ptr, const void* value_ptr,
+                      void* output_ptr, void* lse_ptr, int batch, int head, int m, int n, int k,
+                      float scale, int causal, void* stream);
+int fmha_b200_backward(const void* query_ptr, const void* key_ptr, const void* value_ptr,
+                       const void* output_ptr, const void* d_output_ptr, const void* lse_ptr,
+                       void* d_query_ptr, void* d_key_ptr, void* d_value_ptr, void* workspace,
+                       size_t workspace_bytes, int batch, int head, int m, int n, int k,
+                       float scale, int causal, void* stream);
+
+/* Human-readable text for a status code (static storage). */
+const char* fmha_status_string(int status);
+
+/* Library version, "major.minor.patch". */
+const char* fmha_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FMHA_B200_H_ */
