@@ -118,13 +118,16 @@ def test_linearity_in_v_and_dout_full_size():
     s = D ** -0.5
     o1, l1 = cabi.fwd(q, k, v, s, True)
     o2, l2 = cabi.fwd(q, k, 2 * v, s, True)
-    assert torch.equal(o2, 2 * o1) and torch.equal(l1, l2)
+    # exact up to fp16 subnormals (2 * fp16(x) != fp16(2 * x) below 6.1e-5)
+    assert (o2.float() - 2 * o1.float()).abs().max().item() <= 2.0 ** -23 and torch.equal(l1, l2)
     ones = torch.ones_like(v)
     o3, _ = cabi.fwd(q, k, ones, s, True)
     assert (o3.float() - 1).abs().max().item() < 2e-3
     dq1, dk1, dv1 = cabi.bwd(q, k, v, o1, dout, l1, s, True)
     dq2, dk2, dv2 = cabi.bwd(q, k, v, o1, 2 * dout, l1, s, True)
-    assert torch.equal(dv2, 2 * dv1) and torch.equal(dk2, 2 * dk1)
+    assert (dv2.float() - 2 * dv1.float()).abs().max().item() <= 2.0 ** -23
+    # dS = P o (dP - D) is rounded to fp16 before the dK / dQ MMAs: subnormal dS breaks exactness
+    assert oracle.rel_l2(dk2.float(), 2 * dk1.float()) < 1e-4
     assert oracle.rel_l2(dq2.float(), 2 * dq1.float()) < 1e-3
     # against torch's own fp32 math on the GPU for one (batch, head) slice
     sl = lambda t: t[3:4, :, 7:8].cpu()
