@@ -12,19 +12,24 @@
 //   S^T  = K  Q_i^T    (A = K  smem K-major,  B = Q_i  smem K-major)      -> TMEM [0,128)
 //   dP^T = V  dO_i^T   (A = V  smem K-major,  B = dO_i smem K-major)      -> TMEM [128,256)
 //   dV  += P^T dO_i    (A = P^T TMEM fp16 over S^T, B = dO_i smem MN-major)-> TMEM [256+D, ..)
+//                      (P^T columns [0,32) and [64,96): one 32-column block per compute group)
 //   dK  += dS^T Q_i    (A = dS^T smem K-major, B = Q_i smem MN-major)      -> TMEM [256, 256+D)
 //   dQ_i = dS  K       (A = dS^T smem read MN-major, B = K smem MN-major)  -> TMEM [128,128+D)
 //                      (aliases dP^T, which is dead once dS^T is in shared memory)
 //
-//   warps 0-3  compute group: one thread per KV row; P^T and dS^T
-//   warps 4-7  dQ group: one thread per query row; moves dQ_i from tensor memory into the fp32
-//              accumulator in global memory with vector reductions
-//   warp 8     TMA producer (K, V once; Q_i, dO_i through 2-stage rings)
-//   warp 9     MMA issuer (one thread)
+//   warps 0-3, 4-7  two compute groups: one thread per KV row, group g owns query columns
+//                   [64g, 64g+64) of the tile: P^T = exp2(S^T*c - lse2) (two exp2 per MUFU op,
+//                   fp16) and dS^T = P^T o (dP^T - D)
+//   warps 8-11      dQ group: one thread per query row; tensor memory -> registers -> per-warp
+//                   shared-memory staging -> TMA reduce-add into the fp32 dQ accumulator
+//                   (bulk async adds: no per-thread atomics in the load/store pipeline)
+//   warp 12         TMA producer (K, V once; Q_i through a 2-stage ring, dO_i single stage)
+//   warp 13         MMA issuer: the whole warp runs the loop, one elected lane issues
 //
 // The per-row statistics come from the workspace the preprocess kernel fills:
 // lse2 = lse * log2(e) (+inf on padding rows) and delta = rowsum(dO o O) (0 on padding rows),
-// both padded to a multiple of 128 rows per (batch, head).
+// both padded to a multiple of 128 rows per (batch, head); a tile's 2 x 128 values are staged
+// through shared memory once instead of being re-read by every thread.
 #pragma once
 #include <cuda.h>
 #include <math_constants.h>
@@ -34,7 +39,6 @@
 namespace fmha {
 
 struct BwdKernelParams {
-  float* dq_accum;      // fp32 (Z, seqlen_q, H, D) contiguous
   const float* lse2;    // fp32 (Z*H, seqlen_q_pad)
   const float* delta;   // fp32 (Z*H, seqlen_q_pad)
   float* dk_accum;      // optional fp32 (Z, seqlen_k, H, D) contiguous
@@ -44,6 +48,8 @@ struct BwdKernelParams {
   float scale, scale_log2;
   int causal, causal_shift;
   int* status;
+  long long* timeline;  // debug builds (-DFMHA_TIMELINE) only
+  int timeline_block;
 };
 
 template <int D>
@@ -53,10 +59,13 @@ struct BwdTraits {
   static constexpr int kBoxBytes = 128 * 128;
   static constexpr int kTileBytes = kBoxes * kBoxBytes;  // a 128 x D fp16 tile
   static constexpr int kDsBytes = 2 * kBoxBytes;         // dS^T: 128 x 128 fp16
-  static constexpr int kStages = 2;
-  static constexpr int kThreads = 320;
-  // K, V, Q x2, dO x2, dS^T
-  static constexpr int kSmemBytes = 1024 + (2 + 2 * kStages) * kTileBytes + kDsBytes;
+  static constexpr int kQStages = 2;
+  static constexpr int kStageBytes = 4 * 4096;           // dQ staging: 32 x 32 fp32 per warp
+  static constexpr int kStatBytes = 2 * 256 * 4;         // 2 buffers of lse2[128] + delta[128]
+  static constexpr int kThreads = 448;
+  // K, V, Q x2, dO, dS^T, dQ staging, statistics
+  static constexpr int kSmemBytes =
+      1024 + (3 + kQStages) * kTileBytes + kDsBytes + kStageBytes + kStatBytes;
   static constexpr int kTmemCols = 512;
   static constexpr int kColS = 0, kColDP = 128, kColDQ = 128, kColDK = 256, kColDV = 256 + D;
   static constexpr uint32_t kIdescST = umma_idesc_f16(128, 128, 0, 0);  // S^T, dP^T
@@ -64,23 +73,17 @@ struct BwdTraits {
   static constexpr uint32_t kIdescDQ = umma_idesc_f16(128, D, 1, 1);    // dQ
 };
 
-__device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float c, float d) {
-  asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c),
-               "f"(d)
-               : "memory");
-}
-
 template <int D>
-__global__ void __launch_bounds__(320, 1)
+__global__ void __launch_bounds__(448, 1)
     fmha_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                     const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_do,
                     const __grid_constant__ CUtensorMap tm_dk, const __grid_constant__ CUtensorMap tm_dv,
-                    const BwdKernelParams p) {
+                    const __grid_constant__ CUtensorMap tm_dqacc, const BwdKernelParams p) {
   using T = BwdTraits<D>;
   extern __shared__ uint8_t smem_raw[];
   __shared__ uint64_t bar_kv_full;
-  __shared__ uint64_t bar_q_full[T::kStages], bar_q_empty[T::kStages];
-  __shared__ uint64_t bar_do_full[T::kStages], bar_do_empty[T::kStages];
+  __shared__ uint64_t bar_q_full[T::kQStages], bar_q_empty[T::kQStages];
+  __shared__ uint64_t bar_do_full, bar_do_empty;
   __shared__ uint64_t bar_s_full, bar_dp_full, bar_p_ready, bar_ds_ready, bar_dq_full,
       bar_dq_empty, bar_done;
   __shared__ uint32_t tmem_base_slot;
@@ -100,9 +103,11 @@ __global__ void __launch_bounds__(320, 1)
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const uint32_t k_smem = smem_base;
   const uint32_t v_smem = k_smem + T::kTileBytes;
-  const uint32_t q_smem = v_smem + T::kTileBytes;                  // kStages tiles
-  const uint32_t do_smem = q_smem + T::kStages * T::kTileBytes;    // kStages tiles
-  const uint32_t ds_smem = do_smem + T::kStages * T::kTileBytes;   // dS^T
+  const uint32_t q_smem = v_smem + T::kTileBytes;                   // kQStages tiles
+  const uint32_t do_smem = q_smem + T::kQStages * T::kTileBytes;    // one tile
+  const uint32_t ds_smem = do_smem + T::kTileBytes;                 // dS^T
+  const uint32_t stg_smem = ds_smem + T::kDsBytes;                  // dQ staging, 4 KB per warp
+  const uint32_t stat_smem = stg_smem + T::kStageBytes;             // statistics
 
   // ---- coordinates: consecutive CTAs = same head; early KV tiles (most query tiles) first
   const int nkb = p.num_kv_blocks;
@@ -123,22 +128,22 @@ __global__ void __launch_bounds__(320, 1)
 
   if (threadIdx.x == 0) {
     mbar_init(smem_u32(&bar_kv_full), 1);
-    for (int s = 0; s < T::kStages; ++s) {
+    for (int s = 0; s < T::kQStages; ++s) {
       mbar_init(smem_u32(&bar_q_full[s]), 1);
       mbar_init(smem_u32(&bar_q_empty[s]), 1);
-      mbar_init(smem_u32(&bar_do_full[s]), 1);
-      mbar_init(smem_u32(&bar_do_empty[s]), 1);
     }
+    mbar_init(smem_u32(&bar_do_full), 1);
+    mbar_init(smem_u32(&bar_do_empty), 1);
     mbar_init(smem_u32(&bar_s_full), 1);
     mbar_init(smem_u32(&bar_dp_full), 1);
-    mbar_init(smem_u32(&bar_p_ready), 128);
-    mbar_init(smem_u32(&bar_ds_ready), 128);
+    mbar_init(smem_u32(&bar_p_ready), 256);
+    mbar_init(smem_u32(&bar_ds_ready), 256);
     mbar_init(smem_u32(&bar_dq_full), 1);
     mbar_init(smem_u32(&bar_dq_empty), 128);
     mbar_init(smem_u32(&bar_done), 1);
     fence_barrier_init();
   }
-  if (warp == 9) {
+  if (warp == 13) {
     tmem_alloc(smem_u32(&tmem_base_slot), T::kTmemCols);
     tmem_relinquish();
   }
@@ -147,139 +152,166 @@ __global__ void __launch_bounds__(320, 1)
   tc_fence_after();
   const uint32_t tmem_base = tmem_base_slot;
 
-  if (warp == 8) {
+  if (warp == 12) {
     // =========================== TMA producer ===========================
-    if (lane == 0 && cnt > 0) {
-      tma_prefetch_desc(&tm_q);
-      tma_prefetch_desc(&tm_k);
-      tma_prefetch_desc(&tm_v);
-      tma_prefetch_desc(&tm_do);
-      const uint32_t kvbar = smem_u32(&bar_kv_full);
-      mbar_arrive_expect_tx(kvbar, 2 * T::kTileBytes);
+    if (cnt > 0) {
+      if (elect_one()) {
+        tma_prefetch_desc(&tm_q);
+        tma_prefetch_desc(&tm_k);
+        tma_prefetch_desc(&tm_v);
+        tma_prefetch_desc(&tm_do);
+        const uint32_t kvbar = smem_u32(&bar_kv_full);
+        mbar_arrive_expect_tx(kvbar, 2 * T::kTileBytes);
 #pragma unroll
-      for (int b = 0; b < T::kBoxes; ++b) {
-        tma_load_4d(k_smem + b * T::kBoxBytes, &tm_k, kvbar, b * 64, kv0, h, z);
-        tma_load_4d(v_smem + b * T::kBoxBytes, &tm_v, kvbar, b * 64, kv0, h, z);
+        for (int b = 0; b < T::kBoxes; ++b) {
+          tma_load_4d(k_smem + b * T::kBoxBytes, &tm_k, kvbar, b * 64, kv0, h, z);
+          tma_load_4d(v_smem + b * T::kBoxBytes, &tm_v, kvbar, b * 64, kv0, h, z);
+        }
       }
+      __syncwarp();
       for (int n = 0; n < cnt; ++n) {
-        const int st = n % T::kStages;
-        const int round = n / T::kStages;
+        const int st = n % T::kQStages;
+        const int round = n / T::kQStages;
         const int row = (i_begin + n) * T::kBlock;
-        if (round > 0 && !mbar_wait(smem_u32(&bar_q_empty[st]), (round - 1) & 1, &abort_word, 1))
+        if (round > 0 &&
+            !mbar_wait_warp(smem_u32(&bar_q_empty[st]), (round - 1) & 1, &abort_word, 1))
           break;
-        const uint32_t qbar = smem_u32(&bar_q_full[st]);
-        mbar_arrive_expect_tx(qbar, T::kTileBytes);
+        if (elect_one()) {
+          const uint32_t qbar = smem_u32(&bar_q_full[st]);
+          mbar_arrive_expect_tx(qbar, T::kTileBytes);
 #pragma unroll
-        for (int b = 0; b < T::kBoxes; ++b)
-          tma_load_4d(q_smem + st * T::kTileBytes + b * T::kBoxBytes, &tm_q, qbar, b * 64, row, h,
-                      z);
-        if (round > 0 && !mbar_wait(smem_u32(&bar_do_empty[st]), (round - 1) & 1, &abort_word, 2))
-          break;
-        const uint32_t dbar = smem_u32(&bar_do_full[st]);
-        mbar_arrive_expect_tx(dbar, T::kTileBytes);
+          for (int b = 0; b < T::kBoxes; ++b)
+            tma_load_4d(q_smem + st * T::kTileBytes + b * T::kBoxBytes, &tm_q, qbar, b * 64, row, h,
+                        z);
+        }
+        __syncwarp();
+        if (n > 0 && !mbar_wait_warp(smem_u32(&bar_do_empty), (n - 1) & 1, &abort_word, 2)) break;
+        if (elect_one()) {
+          const uint32_t dbar = smem_u32(&bar_do_full);
+          mbar_arrive_expect_tx(dbar, T::kTileBytes);
 #pragma unroll
-        for (int b = 0; b < T::kBoxes; ++b)
-          tma_load_4d(do_smem + st * T::kTileBytes + b * T::kBoxBytes, &tm_do, dbar, b * 64, row,
-                      h, z);
+          for (int b = 0; b < T::kBoxes; ++b)
+            tma_load_4d(do_smem + b * T::kBoxBytes, &tm_do, dbar, b * 64, row, h, z);
+        }
+        __syncwarp();
       }
     }
-    __syncwarp();
-  } else if (warp == 9) {
-    // =========================== MMA issuer ===========================
-    if (lane == 0 && cnt > 0) {
+  } else if (warp == 13) {
+    // =========================== MMA issuer (converged warp) ===========================
+    if (cnt > 0) {
       // C[128 x 128] = A[128 x D] B[128 x D]^T, both K-major in shared memory
       auto issue_kmajor = [&](uint32_t d_col, uint32_t a_addr, uint32_t b_addr) {
+        const uint32_t a_lo = umma_desc_lo(a_addr, kLboKMajor);
+        const uint32_t b_lo = umma_desc_lo(b_addr, kLboKMajor);
 #pragma unroll
         for (int ks = 0; ks < D / 16; ++ks) {
-          const uint32_t off = (ks >> 2) * T::kBoxBytes + (ks & 3) * 32;
-          umma_ss(tmem_base + d_col, umma_smem_desc(a_addr + off, 16, 1024),
-                  umma_smem_desc(b_addr + off, 16, 1024), T::kIdescST, ks > 0 ? 1u : 0u);
+          const uint32_t off = ((ks >> 2) * T::kBoxBytes + (ks & 3) * 32) >> 4;
+          umma_ss_elect(tmem_base + d_col, a_lo + off, b_lo + off, T::kIdescST, ks > 0 ? 1u : 0u);
         }
       };
-      bool ok = mbar_wait(smem_u32(&bar_kv_full), 0, &abort_word, 3);
-      ok = ok && mbar_wait(smem_u32(&bar_q_full[0]), 0, &abort_word, 4);
+      const uint32_t ds_lo_k = umma_desc_lo(ds_smem, kLboKMajor);    // dS^T as K-major A (dK)
+      const uint32_t ds_lo_mn = umma_desc_lo(ds_smem, kLboMnMajor);  // dS^T read as MN-major A (dQ)
+      const uint32_t k_lo_mn = umma_desc_lo(k_smem, kLboMnMajor);    // K as MN-major B (dQ)
+      const uint32_t do_lo_mn = umma_desc_lo(do_smem, kLboMnMajor);  // dO as MN-major B (dV)
+
+      bool ok = mbar_wait_warp(smem_u32(&bar_kv_full), 0, &abort_word, 3);
+      ok = ok && mbar_wait_warp(smem_u32(&bar_q_full[0]), 0, &abort_word, 4);
       if (ok) {
         tc_fence_after();
         issue_kmajor(T::kColS, k_smem, q_smem);
-        umma_commit(smem_u32(&bar_s_full));
+        umma_commit_elect(smem_u32(&bar_s_full));
       }
-      ok = ok && mbar_wait(smem_u32(&bar_do_full[0]), 0, &abort_word, 5);
+      ok = ok && mbar_wait_warp(smem_u32(&bar_do_full), 0, &abort_word, 5);
       if (ok) {
         tc_fence_after();
         issue_kmajor(T::kColDP, v_smem, do_smem);
-        umma_commit(smem_u32(&bar_dp_full));
+        umma_commit_elect(smem_u32(&bar_dp_full));
       }
       for (int n = 0; ok && n < cnt; ++n) {
-        const int st = n % T::kStages;
+        const int st = n % T::kQStages;
         const uint32_t q_addr = q_smem + st * T::kTileBytes;
-        const uint32_t do_addr = do_smem + st * T::kTileBytes;
         // ---- dV += P^T dO_i
-        if (!mbar_wait(smem_u32(&bar_p_ready), n & 1, &abort_word, 6)) break;
+        FMHA_TL(2, n, 0);
+        if (!mbar_wait_warp(smem_u32(&bar_p_ready), n & 1, &abort_word, 6)) break;
         tc_fence_after();
+        FMHA_TL(2, n, 1);
 #pragma unroll
         for (int ks = 0; ks < T::kBlock / 16; ++ks)
-          umma_ts(tmem_base + T::kColDV, tmem_base + T::kColS + ks * 8,
-                  umma_smem_desc(do_addr + ks * 2048, T::kBoxBytes, 1024), T::kIdescDV,
-                  (n > 0 || ks > 0) ? 1u : 0u);
-        umma_commit(smem_u32(&bar_do_empty[st]));
+          umma_ts_elect(tmem_base + T::kColDV,
+                        tmem_base + T::kColS + (ks >> 2) * 64 + (ks & 3) * 8, do_lo_mn + ks * 128,
+                        T::kIdescDV, (n > 0 || ks > 0) ? 1u : 0u);
+        umma_commit_elect(smem_u32(&bar_do_empty));
         // ---- S^T of the next query tile (the S region is free once dV has read P^T)
         if (n + 1 < cnt) {
-          const int st1 = (n + 1) % T::kStages;
-          if (!mbar_wait(smem_u32(&bar_q_full[st1]), ((n + 1) / T::kStages) & 1, &abort_word, 7))
+          const int st1 = (n + 1) % T::kQStages;
+          if (!mbar_wait_warp(smem_u32(&bar_q_full[st1]), ((n + 1) / T::kQStages) & 1, &abort_word,
+                              7))
             break;
           tc_fence_after();
           issue_kmajor(T::kColS, k_smem, q_smem + st1 * T::kTileBytes);
-          umma_commit(smem_u32(&bar_s_full));
+          umma_commit_elect(smem_u32(&bar_s_full));
         }
-        // ---- dK += dS^T Q_i ; dQ_i = dS K
-        if (!mbar_wait(smem_u32(&bar_ds_ready), n & 1, &abort_word, 8)) break;
+        // ---- dK += dS^T Q_i ; dQ_i = dS K   (independent accumulators: interleaved)
+        FMHA_TL(2, n, 2);
+        if (!mbar_wait_warp(smem_u32(&bar_ds_ready), n & 1, &abort_word, 8)) break;
         tc_fence_after();
+        FMHA_TL(2, n, 3);
+        const uint32_t q_lo_mn = umma_desc_lo(q_addr, kLboMnMajor);
 #pragma unroll
         for (int ks = 0; ks < T::kBlock / 16; ++ks) {
-          const uint32_t off = (ks >> 2) * T::kBoxBytes + (ks & 3) * 32;
-          umma_ss(tmem_base + T::kColDK, umma_smem_desc(ds_smem + off, 16, 1024),
-                  umma_smem_desc(q_addr + ks * 2048, T::kBoxBytes, 1024), T::kIdescDV,
-                  (n > 0 || ks > 0) ? 1u : 0u);
+          const uint32_t off = ((ks >> 2) * T::kBoxBytes + (ks & 3) * 32) >> 4;
+          umma_ss_elect(tmem_base + T::kColDQ, ds_lo_mn + ks * 128, k_lo_mn + ks * 128, T::kIdescDQ,
+                        ks > 0 ? 1u : 0u);
+          umma_ss_elect(tmem_base + T::kColDK, ds_lo_k + off, q_lo_mn + ks * 128, T::kIdescDV,
+                        (n > 0 || ks > 0) ? 1u : 0u);
         }
-#pragma unroll
-        for (int ks = 0; ks < T::kBlock / 16; ++ks)
-          umma_ss(tmem_base + T::kColDQ, umma_smem_desc(ds_smem + ks * 2048, T::kBoxBytes, 1024),
-                  umma_smem_desc(k_smem + ks * 2048, T::kBoxBytes, 1024), T::kIdescDQ,
-                  ks > 0 ? 1u : 0u);
-        umma_commit(smem_u32(&bar_dq_full));
-        umma_commit(smem_u32(&bar_q_empty[st]));
+        umma_commit_elect(smem_u32(&bar_dq_full));
+        umma_commit_elect(smem_u32(&bar_q_empty[st]));
+        FMHA_TL(2, n, 4);
         // ---- dP^T of the next query tile (its columns hold dQ_i until the dQ group read it)
         if (n + 1 < cnt) {
-          const int st1 = (n + 1) % T::kStages;
-          if (!mbar_wait(smem_u32(&bar_do_full[st1]), ((n + 1) / T::kStages) & 1, &abort_word, 9))
-            break;
-          if (!mbar_wait(smem_u32(&bar_dq_empty), n & 1, &abort_word, 10)) break;
+          if (!mbar_wait_warp(smem_u32(&bar_do_full), (n + 1) & 1, &abort_word, 9)) break;
+          if (!mbar_wait_warp(smem_u32(&bar_dq_empty), n & 1, &abort_word, 10)) break;
           tc_fence_after();
-          issue_kmajor(T::kColDP, v_smem, do_smem + st1 * T::kTileBytes);
-          umma_commit(smem_u32(&bar_dp_full));
+          FMHA_TL(2, n, 5);
+          issue_kmajor(T::kColDP, v_smem, do_smem);
+          umma_commit_elect(smem_u32(&bar_dp_full));
+          FMHA_TL(2, n, 6);
         }
       }
-      umma_commit(smem_u32(&bar_done));
+      umma_commit_elect(smem_u32(&bar_done));
     }
-    __syncwarp();
   } else {
-    const int group = warp >> 2;  // 0 = compute, 1 = dQ
     const int quad = warp & 3;
     const int r = quad * 32 + lane;  // TMEM lane of this thread
     const uint32_t lane_addr = uint32_t(quad * 32) << 16;
     const size_t stat_base = (size_t)zh * p.seqlen_q_pad;
 
-    if (group == 0) {
-      // =========================== compute group: P^T, dS^T ===========================
-      const int kvi = kv0 + r;  // key of this thread
+    if (warp < 8) {
+      // =========================== compute groups: P^T, dS^T ===========================
+      const int cg = warp >> 2;           // query-column half of this group
+      const int ct = threadIdx.x;         // 0..255 among the compute threads
+      const int kvi = kv0 + r;            // key of this thread
       const float c = p.scale_log2;
-      const uint32_t tS = tmem_base + lane_addr + T::kColS;
-      const uint32_t tDP = tmem_base + lane_addr + T::kColDP;
+      const uint32_t tS = tmem_base + lane_addr + T::kColS + cg * 64;
+      // P^T (32 packed columns) goes over the start of this group's own S^T half, which only
+      // this group reads: no ordering between the two groups is needed
+      const uint32_t tP = tS;
+      const uint32_t tDP = tmem_base + lane_addr + T::kColDP + cg * 64;
+      // statistics: thread ct < 128 carries lse2[q0 + ct], the others delta[q0 + ct - 128]
+      const float* stat_src = (ct < 128 ? p.lse2 : p.delta) + stat_base + (ct & 127);
+      float stat_next = (cnt > 0) ? __ldg(stat_src + (size_t)i_begin * T::kBlock) : 0.f;
+      const bool tl = (threadIdx.x == 0);
+
       for (int n = 0; n < cnt; ++n) {
         const int qbase = (i_begin + n) * T::kBlock;
-        const float* lse2_p = p.lse2 + stat_base + qbase;
-        const float* dl_p = p.delta + stat_base + qbase;
-        // first visible query column of this tile for this key (>= 128: none)
+        const uint32_t sb = stat_smem + (n & 1) * 1024;  // lse2 at [0, 512), delta at [512, 1024)
+        asm volatile("st.shared.f32 [%0], %1;" ::"r"(sb + ct * 4), "f"(stat_next) : "memory");
+        if (n + 1 < cnt) stat_next = __ldg(stat_src + (size_t)(i_begin + n + 1) * T::kBlock);
+        // everybody is done with the other buffer's previous use and sees this buffer
+        named_bar_sync(3, 256);
+
+        // first visible query column of this thread's half (>= 64: none)
         int first_visible = 0;
         if (kvi >= p.seqlen_k) {
           first_visible = T::kBlock;
@@ -287,109 +319,137 @@ __global__ void __launch_bounds__(320, 1)
           const long long fv = (long long)kvi - p.causal_shift - qbase;
           first_visible = fv <= 0 ? 0 : (int)min(fv, (long long)T::kBlock);
         }
-        uint32_t pp[2][32];  // P^T of this row, fp16 pairs
-        if (!mbar_wait(smem_u32(&bar_s_full), n & 1, &abort_word, 11)) break;
+        const int fvh = first_visible - cg * 64;
+
+        uint32_t pp[32];  // P^T of this row and half, fp16 pairs
+        if (tl) FMHA_TL(0, n, 0);
+        mbar_wait(smem_u32(&bar_s_full), n & 1, &abort_word, 11);  // on a time-out: keep going,
+        // every later wait returns at once and all 256 threads still meet at the named barrier
         tc_fence_after();
-#pragma unroll
-        for (int cc = 0; cc < 4; ++cc) {
-          uint32_t s[32];
-          tmem_ld32(tS + cc * 32, s);
+        if (tl) FMHA_TL(0, n, 1);
+        {
+          uint32_t s[2][32];
+          tmem_ld32(tS, s[0]);
+          tmem_ld32(tS + 32, s[1]);
           tmem_wait_ld();
 #pragma unroll
-          for (int i = 0; i < 32; i += 4) {
-            const float4 L = __ldg(reinterpret_cast<const float4*>(lse2_p + cc * 32 + i));
-            float p0 = fast_exp2(fmaf(__uint_as_float(s[i + 0]), c, -L.x));
-            float p1 = fast_exp2(fmaf(__uint_as_float(s[i + 1]), c, -L.y));
-            float p2 = fast_exp2(fmaf(__uint_as_float(s[i + 2]), c, -L.z));
-            float p3 = fast_exp2(fmaf(__uint_as_float(s[i + 3]), c, -L.w));
-            if (first_visible > 0) {
-              const int col = cc * 32 + i;
-              if (col + 0 < first_visible) p0 = 0.f;
-              if (col + 1 < first_visible) p1 = 0.f;
-              if (col + 2 < first_visible) p2 = 0.f;
-              if (col + 3 < first_visible) p3 = 0.f;
+          for (int cc = 0; cc < 2; ++cc)
+#pragma unroll
+            for (int i = 0; i < 32; i += 4) {
+              const float4 L = lds128(sb + (cg * 64 + cc * 32 + i) * 4);
+              const float x0 = fmaf(__uint_as_float(s[cc][i + 0]), c, -L.x);
+              const float x1 = fmaf(__uint_as_float(s[cc][i + 1]), c, -L.y);
+              const float x2 = fmaf(__uint_as_float(s[cc][i + 2]), c, -L.z);
+              const float x3 = fmaf(__uint_as_float(s[cc][i + 3]), c, -L.w);
+              pp[cc * 16 + (i >> 1) + 0] = exp2_half2(pack_half2(x0, x1));
+              pp[cc * 16 + (i >> 1) + 1] = exp2_half2(pack_half2(x2, x3));
             }
-            pp[cc >> 1][(cc & 1) * 16 + (i >> 1) + 0] = pack_half2(p0, p1);
-            pp[cc >> 1][(cc & 1) * 16 + (i >> 1) + 1] = pack_half2(p2, p3);
+          if (fvh > 0) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {  // pair j = columns 2j, 2j+1 of this half
+              if (2 * j + 1 < fvh) pp[j] = 0u;
+              else if (2 * j < fvh) pp[j] &= 0xffff0000u;
+            }
           }
         }
-        tmem_st32(tS + 0, pp[0]);
-        tmem_st32(tS + 32, pp[1]);
+        tmem_st32(tP, pp);
         tmem_wait_st();
         tc_fence_before();
         mbar_arrive(smem_u32(&bar_p_ready));
+        if (tl) FMHA_TL(0, n, 2);
 
-        if (!mbar_wait(smem_u32(&bar_dp_full), n & 1, &abort_word, 12)) break;
+        mbar_wait(smem_u32(&bar_dp_full), n & 1, &abort_word, 12);
+        if (tl) FMHA_TL(0, n, 3);
         // dS^T of the previous tile must have been consumed by its dK / dQ MMAs
-        if (n > 0 && !mbar_wait(smem_u32(&bar_dq_full), (n - 1) & 1, &abort_word, 13)) break;
+        if (n > 0) mbar_wait(smem_u32(&bar_dq_full), (n - 1) & 1, &abort_word, 13);
         tc_fence_after();
-#pragma unroll
-        for (int cc = 0; cc < 4; ++cc) {
-          uint32_t dp[32];
-          tmem_ld32(tDP + cc * 32, dp);
+        if (tl) FMHA_TL(0, n, 4);
+        {
+          uint32_t dp[2][32];
+          tmem_ld32(tDP, dp[0]);
+          tmem_ld32(tDP + 32, dp[1]);
           tmem_wait_ld();
-          uint32_t w[16];
+          const uint32_t row_addr = ds_smem + cg * T::kBoxBytes + r * 128;
 #pragma unroll
-          for (int i = 0; i < 32; i += 4) {
-            const float4 Dl = __ldg(reinterpret_cast<const float4*>(dl_p + cc * 32 + i));
-            const uint32_t pk0 = pp[cc >> 1][(cc & 1) * 16 + (i >> 1) + 0];
-            const uint32_t pk1 = pp[cc >> 1][(cc & 1) * 16 + (i >> 1) + 1];
-            const float2 pa = __half22float2(*reinterpret_cast<const __half2*>(&pk0));
-            const float2 pb = __half22float2(*reinterpret_cast<const __half2*>(&pk1));
-            const float d0 = pa.x * (__uint_as_float(dp[i + 0]) - Dl.x);
-            const float d1 = pa.y * (__uint_as_float(dp[i + 1]) - Dl.y);
-            const float d2 = pb.x * (__uint_as_float(dp[i + 2]) - Dl.z);
-            const float d3 = pb.y * (__uint_as_float(dp[i + 3]) - Dl.w);
-            w[(i >> 1) + 0] = pack_half2(d0, d1);
-            w[(i >> 1) + 1] = pack_half2(d2, d3);
-          }
+          for (int cc = 0; cc < 2; ++cc)
 #pragma unroll
-          for (int k4 = 0; k4 < 4; ++k4) {
-            const int ch = cc * 4 + k4;  // 16-byte chunk (8 query columns) of this row
-            const uint32_t addr =
-                ds_smem + (ch >> 3) * T::kBoxBytes + r * 128 + (((ch & 7) ^ (r & 7)) << 4);
-            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(w[k4 * 4 + 0]),
-                         "r"(w[k4 * 4 + 1]), "r"(w[k4 * 4 + 2]), "r"(w[k4 * 4 + 3])
-                         : "memory");
-          }
+            for (int k8 = 0; k8 < 4; ++k8) {  // 8 columns = one 16-byte chunk
+              uint32_t w[4];
+#pragma unroll
+              for (int hh = 0; hh < 2; ++hh) {
+                const int i = k8 * 8 + hh * 4;
+                const float4 Dl = lds128(sb + 512 + (cg * 64 + cc * 32 + i) * 4);
+                const uint32_t a01 = pack_half2(__uint_as_float(dp[cc][i + 0]) - Dl.x,
+                                                __uint_as_float(dp[cc][i + 1]) - Dl.y);
+                const uint32_t a23 = pack_half2(__uint_as_float(dp[cc][i + 2]) - Dl.z,
+                                                __uint_as_float(dp[cc][i + 3]) - Dl.w);
+                w[hh * 2 + 0] = mul_half2(pp[cc * 16 + (i >> 1) + 0], a01);
+                w[hh * 2 + 1] = mul_half2(pp[cc * 16 + (i >> 1) + 1], a23);
+              }
+              const int ch = cc * 4 + k8;  // chunk of this thread's 128-byte row
+              sts128(row_addr + ((ch ^ (r & 7)) << 4), w[0], w[1], w[2], w[3]);
+            }
         }
         fence_proxy_async_smem();
         tc_fence_before();
         mbar_arrive(smem_u32(&bar_ds_ready));
+        if (tl) FMHA_TL(0, n, 5);
       }
     } else {
       // =========================== dQ group ===========================
       const uint32_t tDQ = tmem_base + lane_addr + T::kColDQ;
+      const uint32_t stage = stg_smem + quad * 4096;
+      const uint32_t my_row = stage + lane * 128;
+      const bool tl = (r == 0);
       for (int n = 0; n < cnt; ++n) {
-        const int qrow = (i_begin + n) * T::kBlock + r;
+        const int q0w = (i_begin + n) * T::kBlock + quad * 32;  // first query row of this warp
+        if (tl) FMHA_TL(1, n, 0);
         if (!mbar_wait(smem_u32(&bar_dq_full), n & 1, &abort_word, 14)) break;
         tc_fence_after();
-        uint32_t acc[D / 32][32];
+        if (tl) FMHA_TL(1, n, 1);
 #pragma unroll
-        for (int cc = 0; cc < D / 32; ++cc) tmem_ld32(tDQ + cc * 32, acc[cc]);
-        tmem_wait_ld();
-        tc_fence_before();
-        mbar_arrive(smem_u32(&bar_dq_empty));
-        if (qrow < p.seqlen_q) {
-          float* dst = p.dq_accum + (((size_t)z * p.seqlen_q + qrow) * p.heads + h) * D;
+        for (int pair = 0; pair < D / 64; ++pair) {
+          uint32_t acc[2][32];
+          tmem_ld32(tDQ + pair * 64, acc[0]);
+          tmem_ld32(tDQ + pair * 64 + 32, acc[1]);
+          tmem_wait_ld();
+          if (pair == D / 64 - 1) {
+            // the whole dQ tile is in registers: its columns may take the next dP^T
+            tc_fence_before();
+            mbar_arrive(smem_u32(&bar_dq_empty));
+            if (tl) FMHA_TL(1, n, 2);
+          }
 #pragma unroll
-          for (int cc = 0; cc < D / 32; ++cc)
+          for (int cc = 0; cc < 2; ++cc) {
+            // the previous reduce-add must have finished reading the staging buffer
+            if (lane == 0) tma_wait_group_read<0>();
+            __syncwarp();
 #pragma unroll
-            for (int i = 0; i < 32; i += 4)
-              red_add_v4(dst + cc * 32 + i, __uint_as_float(acc[cc][i + 0]),
-                         __uint_as_float(acc[cc][i + 1]), __uint_as_float(acc[cc][i + 2]),
-                         __uint_as_float(acc[cc][i + 3]));
+            for (int k4 = 0; k4 < 8; ++k4)
+              sts128(my_row + ((k4 ^ (lane & 7)) << 4), acc[cc][k4 * 4 + 0], acc[cc][k4 * 4 + 1],
+                     acc[cc][k4 * 4 + 2], acc[cc][k4 * 4 + 3]);
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) {
+              tma_reduce_add_4d(&tm_dqacc, stage, pair * 64 + cc * 32, q0w, h, z);
+              tma_commit_group();
+            }
+          }
         }
+        if (tl) FMHA_TL(1, n, 3);
       }
+      if (lane == 0) tma_wait_group<0>();
+      __syncwarp();
     }
 
-    // =========================== epilogue: dK (group 0), dV (group 1) ===========================
-    {
+    // ============ epilogue: dK (warps 0-3), dV (warps 8-11); warps 4-7 are done ============
+    if (warp < 4 || warp >= 8) {
+      const bool is_dk = warp < 4;
       if (cnt > 0) mbar_wait(smem_u32(&bar_done), 0, &abort_word, 15);
       tc_fence_after();
-      const uint32_t tAcc = tmem_base + lane_addr + (group == 0 ? T::kColDK : T::kColDV);
-      const float mul = (group == 0) ? p.scale : 1.f;
-      float* accum = (group == 0) ? p.dk_accum : p.dv_accum;
+      const uint32_t tAcc = tmem_base + lane_addr + (is_dk ? T::kColDK : T::kColDV);
+      const float mul = is_dk ? p.scale : 1.f;
+      float* accum = is_dk ? p.dk_accum : p.dv_accum;
       const int kvi = kv0 + r;
       if (accum != nullptr) {
         // ring attention: add this block's contribution into the travelling fp32 buffer
@@ -412,8 +472,8 @@ __global__ void __launch_bounds__(320, 1)
           }
         }
       } else {
-        // fp16 tile -> shared memory (over Q stage 0 / dO stage 0) -> TMA store
-        const uint32_t out_smem = (group == 0) ? q_smem : do_smem;
+        // fp16 tile -> shared memory (over Q stage 0 / dO) -> TMA store
+        const uint32_t out_smem = is_dk ? q_smem : do_smem;
 #pragma unroll
         for (int cc = 0; cc < D / 32; ++cc) {
           uint32_t a[32];
@@ -429,23 +489,17 @@ __global__ void __launch_bounds__(320, 1)
             const int ch = cc * 4 + k4;
             const uint32_t addr =
                 out_smem + (ch >> 3) * T::kBoxBytes + r * 128 + (((ch & 7) ^ (r & 7)) << 4);
-            const uint32_t w0 = pack_half2(__uint_as_float(a[k4 * 8 + 0]) * mul,
-                                           __uint_as_float(a[k4 * 8 + 1]) * mul);
-            const uint32_t w1 = pack_half2(__uint_as_float(a[k4 * 8 + 2]) * mul,
-                                           __uint_as_float(a[k4 * 8 + 3]) * mul);
-            const uint32_t w2 = pack_half2(__uint_as_float(a[k4 * 8 + 4]) * mul,
-                                           __uint_as_float(a[k4 * 8 + 5]) * mul);
-            const uint32_t w3 = pack_half2(__uint_as_float(a[k4 * 8 + 6]) * mul,
-                                           __uint_as_float(a[k4 * 8 + 7]) * mul);
-            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(w0), "r"(w1),
-                         "r"(w2), "r"(w3)
-                         : "memory");
+            sts128(addr,
+                   pack_half2(__uint_as_float(a[k4 * 8 + 0]) * mul, __uint_as_float(a[k4 * 8 + 1]) * mul),
+                   pack_half2(__uint_as_float(a[k4 * 8 + 2]) * mul, __uint_as_float(a[k4 * 8 + 3]) * mul),
+                   pack_half2(__uint_as_float(a[k4 * 8 + 4]) * mul, __uint_as_float(a[k4 * 8 + 5]) * mul),
+                   pack_half2(__uint_as_float(a[k4 * 8 + 6]) * mul, __uint_as_float(a[k4 * 8 + 7]) * mul));
           }
         }
         fence_proxy_async_smem();
-        named_bar_sync(1 + group, 128);
+        named_bar_sync(is_dk ? 1 : 2, 128);
         if (r == 0) {
-          const CUtensorMap* tm = (group == 0) ? &tm_dk : &tm_dv;
+          const CUtensorMap* tm = is_dk ? &tm_dk : &tm_dv;
 #pragma unroll
           for (int b = 0; b < T::kBoxes; ++b)
             tma_store_4d(tm, out_smem + b * T::kBoxBytes, b * 64, kv0, h, z);
@@ -463,7 +517,7 @@ __global__ void __launch_bounds__(320, 1)
     if (threadIdx.x == 0 && p.status != nullptr) atomicCAS(p.status, 0, abort_word);
     for (int i = 0; i < 64; ++i) __nanosleep(1000);
   }
-  if (warp == 9) {
+  if (warp == 13) {
     tc_fence_after();
     tmem_dealloc(tmem_base, T::kTmemCols);
   }

@@ -57,6 +57,25 @@ int make_tensor_map(CUtensorMap* map, const void* base, int Z, int N, int H, int
   return r == CUDA_SUCCESS ? FMHA_OK : FMHA_ERR_TENSOR_MAP;
 }
 
+// fp32 dQ accumulator (Z, N, H, D) contiguous -> 4-D map, box 32 x 32 x 1 x 1 (one warp's 32 query
+// rows x 32 columns = 128-byte rows), 128-byte swizzle; used by TMA reduce-add
+int make_accum_map(CUtensorMap* map, float* base, int Z, int N, int H, int D) {
+  EncodeTiledFn encode = get_encode_fn();
+  if (encode == nullptr) return FMHA_ERR_NO_DEVICE;
+  const cuuint64_t dims[4] = {(cuuint64_t)D, (cuuint64_t)N, (cuuint64_t)H, (cuuint64_t)Z};
+  const cuuint64_t strides[3] = {(cuuint64_t)H * D * 4, (cuuint64_t)D * 4, (cuuint64_t)N * H * D * 4};
+  const cuuint32_t box[4] = {32, 32, 1, 1};
+  const cuuint32_t estr[4] = {1, 1, 1, 1};
+  const CUresult r = encode(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, base, dims, strides, box, estr,
+                            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                            CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? FMHA_OK : FMHA_ERR_TENSOR_MAP;
+}
+
+// debug builds (-DFMHA_TIMELINE) set these through fmha_debug_set_timeline; otherwise unused
+long long* g_timeline = nullptr;
+int g_timeline_block = 0;
+
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 int check_strides(const FmhaStrides& s, int N, int H, int Z) {
@@ -118,6 +137,8 @@ int launch_fwd(const FmhaFwdParams* p, cudaStream_t stream) {
   kp.causal = p->causal ? 1 : 0;
   kp.causal_shift = p->causal_shift;
   kp.status = p->status;
+  kp.timeline = g_timeline;
+  kp.timeline_block = g_timeline_block;
   auto kernel = fmha::fmha_fwd_kernel<D>;
   if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, T::kSmemBytes) !=
       cudaSuccess)
@@ -144,8 +165,9 @@ int launch_bwd(const FmhaBwdParams* p, const BwdWorkspace& w, cudaStream_t strea
   }
 
   {
-    CUtensorMap tq, tk, tv, tdo, tdk, tdv;
+    CUtensorMap tq, tk, tv, tdo, tdk, tdv, tacc;
     int rc;
+    if ((rc = make_accum_map(&tacc, w.dq_accum, Z, Nq, H, D))) return rc;
     if ((rc = make_tensor_map(&tq, p->q, Z, Nq, H, D, p->q_strides))) return rc;
     if ((rc = make_tensor_map(&tk, p->k, Z, Nk, H, D, p->k_strides))) return rc;
     if ((rc = make_tensor_map(&tv, p->v, Z, Nk, H, D, p->v_strides))) return rc;
@@ -159,7 +181,6 @@ int launch_bwd(const FmhaBwdParams* p, const BwdWorkspace& w, cudaStream_t strea
                               acc_v ? p->v_strides : p->dv_strides)))
       return rc;
     fmha::BwdKernelParams kp;
-    kp.dq_accum = w.dq_accum;
     kp.lse2 = w.lse2;
     kp.delta = w.delta;
     kp.dk_accum = p->dk_accum;
@@ -174,12 +195,14 @@ int launch_bwd(const FmhaBwdParams* p, const BwdWorkspace& w, cudaStream_t strea
     kp.causal = p->causal ? 1 : 0;
     kp.causal_shift = p->causal_shift;
     kp.status = p->status;
+    kp.timeline = g_timeline;
+    kp.timeline_block = g_timeline_block;
     auto kernel = fmha::fmha_bwd_kernel<D>;
     if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, T::kSmemBytes) !=
         cudaSuccess)
       return FMHA_ERR_LAUNCH;
     const unsigned grid = (unsigned)((long long)kp.num_kv_blocks * H * Z);
-    kernel<<<grid, T::kThreads, T::kSmemBytes, stream>>>(tq, tk, tv, tdo, tdk, tdv, kp);
+    kernel<<<grid, T::kThreads, T::kSmemBytes, stream>>>(tq, tk, tv, tdo, tdk, tdv, tacc, kp);
     if (cudaGetLastError() != cudaSuccess) return FMHA_ERR_LAUNCH;
   }
 
@@ -356,5 +379,13 @@ const char* fmha_status_string(int status) {
 }
 
 const char* fmha_version(void) { return "0.1.0"; }
+
+#ifdef FMHA_TIMELINE
+// debug builds only: device buffer (>= 3 * 512 int64) and the CTA whose events are recorded
+void fmha_debug_set_timeline(long long* buf, int block) {
+  g_timeline = buf;
+  g_timeline_block = block;
+}
+#endif
 
 }  // extern "C"

@@ -34,6 +34,9 @@ struct FwdKernelParams {
   float scale_log2;  // scale * log2(e)
   int causal, causal_shift;
   int* status;
+  // debug builds (-DFMHA_TIMELINE) only: clock64 stamps of one CTA, see FMHA_TL below
+  long long* timeline;
+  int timeline_block;
 };
 
 template <int D>
@@ -136,74 +139,86 @@ __global__ void __launch_bounds__(320, 1)
   const uint32_t tmem_base = tmem_base_slot;
 
   if (warp == 8) {
-    // =========================== TMA producer ===========================
-    if (lane == 0 && n_max > 0) {
-      tma_prefetch_desc(&tm_q);
-      tma_prefetch_desc(&tm_k);
-      tma_prefetch_desc(&tm_v);
-      const uint32_t qbar = smem_u32(&bar_q_full);
-      mbar_arrive_expect_tx(qbar, T::kTilesM * T::kTileBytes);
+    // =========================== TMA producer (converged warp, elected issue) ==========
+    if (n_max > 0) {
+      if (elect_one()) {
+        tma_prefetch_desc(&tm_q);
+        tma_prefetch_desc(&tm_k);
+        tma_prefetch_desc(&tm_v);
+        const uint32_t qbar = smem_u32(&bar_q_full);
+        mbar_arrive_expect_tx(qbar, T::kTilesM * T::kTileBytes);
 #pragma unroll
-      for (int t = 0; t < T::kTilesM; ++t)
+        for (int t = 0; t < T::kTilesM; ++t)
 #pragma unroll
-        for (int b = 0; b < T::kBoxes; ++b)
-          tma_load_4d(q_smem + t * T::kTileBytes + b * T::kBoxBytes, &tm_q, qbar, b * 64,
-                      q0 + t * T::kBlockM, h, z);
+          for (int b = 0; b < T::kBoxes; ++b)
+            tma_load_4d(q_smem + t * T::kTileBytes + b * T::kBoxBytes, &tm_q, qbar, b * 64,
+                        q0 + t * T::kBlockM, h, z);
+      }
+      __syncwarp();
       const int n_loads = 2 * n_max;  // K_0, V_0, K_1, V_1, ...
       for (int it = 0; it < n_loads; ++it) {
         const int slot = it % T::kStages;
         const int round = it / T::kStages;
         if (round > 0 &&
-            !mbar_wait(smem_u32(&bar_kv_empty[slot]), (round - 1) & 1, &abort_word, 1))
+            !mbar_wait_warp(smem_u32(&bar_kv_empty[slot]), (round - 1) & 1, &abort_word, 1))
           break;
-        const uint32_t fbar = smem_u32(&bar_kv_full[slot]);
-        mbar_arrive_expect_tx(fbar, T::kTileBytes);
-        const CUtensorMap* tm = (it & 1) ? &tm_v : &tm_k;
-        const int row = (it >> 1) * T::kBlockN;
+        if (elect_one()) {
+          const uint32_t fbar = smem_u32(&bar_kv_full[slot]);
+          mbar_arrive_expect_tx(fbar, T::kTileBytes);
+          const CUtensorMap* tm = (it & 1) ? &tm_v : &tm_k;
+          const int row = (it >> 1) * T::kBlockN;
 #pragma unroll
-        for (int b = 0; b < T::kBoxes; ++b)
-          tma_load_4d(ring_smem + slot * T::kTileBytes + b * T::kBoxBytes, tm, fbar, b * 64, row,
-                      h, z);
+          for (int b = 0; b < T::kBoxes; ++b)
+            tma_load_4d(ring_smem + slot * T::kTileBytes + b * T::kBoxBytes, tm, fbar, b * 64, row,
+                        h, z);
+        }
+        __syncwarp();
       }
     }
-    __syncwarp();
   } else if (warp == 9) {
-    // =========================== MMA issuer ===========================
-    if (lane == 0 && n_max > 0) {
+    // =========================== MMA issuer (converged warp, elected issue) ============
+    // All 32 lanes run the loop so that addresses and descriptors live in uniform registers;
+    // a loop run by one lane only makes every operand a per-thread value that has to be moved
+    // to a uniform register before each tcgen05.mma, and the issue rate falls below the
+    // tensor pipe's 64 cycles per 128x128x16 MMA.
+    if (n_max > 0) {
+      const uint32_t q_lo0 = umma_desc_lo(q_smem, kLboKMajor);
       auto issue_qk = [&](int t, uint32_t k_addr) {
         const uint32_t d = tmem_base + t * 128;
+        const uint32_t a_lo = q_lo0 + ((t * T::kTileBytes) >> 4);
+        const uint32_t b_lo = umma_desc_lo(k_addr, kLboKMajor);
 #pragma unroll
         for (int ks = 0; ks < D / 16; ++ks) {
-          const uint32_t off = (ks >> 2) * T::kBoxBytes + (ks & 3) * 32;
-          umma_ss(d, umma_smem_desc(q_smem + t * T::kTileBytes + off, 16, 1024),
-                  umma_smem_desc(k_addr + off, 16, 1024), T::kIdescQK, ks > 0 ? 1u : 0u);
+          const uint32_t off = ((ks >> 2) * T::kBoxBytes + (ks & 3) * 32) >> 4;
+          umma_ss_elect(d, a_lo + off, b_lo + off, T::kIdescQK, ks > 0 ? 1u : 0u);
         }
       };
       auto issue_pv = [&](int t, uint32_t v_addr, bool accumulate) {
         const uint32_t d = tmem_base + 256 + t * D;
         const uint32_t a = tmem_base + t * 128;
+        const uint32_t b_lo = umma_desc_lo(v_addr, kLboMnMajor);
 #pragma unroll
-        for (int ks = 0; ks < T::kBlockN / 16; ++ks) {
-          umma_ts(d, a + ks * 8, umma_smem_desc(v_addr + ks * 2048, T::kBoxBytes, 1024),
-                  T::kIdescPV, (accumulate || ks > 0) ? 1u : 0u);
-        }
+        for (int ks = 0; ks < T::kBlockN / 16; ++ks)
+          umma_ts_elect(d, a + ks * 8, b_lo + ((ks * 2048) >> 4), T::kIdescPV,
+                        (accumulate || ks > 0) ? 1u : 0u);
       };
-      bool ok = mbar_wait(smem_u32(&bar_q_full), 0, &abort_word, 2);
-      ok = ok && mbar_wait(smem_u32(&bar_kv_full[0]), 0, &abort_word, 3);
+      bool ok = mbar_wait_warp(smem_u32(&bar_q_full), 0, &abort_word, 2);
+      ok = ok && mbar_wait_warp(smem_u32(&bar_kv_full[0]), 0, &abort_word, 3);
       if (ok) {
         tc_fence_after();
 #pragma unroll
         for (int t = 0; t < 2; ++t)
           if (n_kv[t] > 0) {
             issue_qk(t, ring_smem);
-            umma_commit(smem_u32(&bar_s_full[t]));
+            umma_commit_elect(smem_u32(&bar_s_full[t]));
           }
-        umma_commit(smem_u32(&bar_kv_empty[0]));
+        umma_commit_elect(smem_u32(&bar_kv_empty[0]));
       }
       for (int j = 0; ok && j < n_max; ++j) {
         const int it_v = 2 * j + 1;
         const int slot_v = it_v % T::kStages;
-        if (!mbar_wait(smem_u32(&bar_kv_full[slot_v]), (it_v / T::kStages) & 1, &abort_word, 4)) {
+        if (!mbar_wait_warp(smem_u32(&bar_kv_full[slot_v]), (it_v / T::kStages) & 1, &abort_word,
+                            4)) {
           ok = false;
           break;
         }
@@ -214,16 +229,19 @@ __global__ void __launch_bounds__(320, 1)
 #pragma unroll
         for (int t = 0; t < 2; ++t) {
           if (j < n_kv[t]) {
-            if (!mbar_wait(smem_u32(&bar_p_full[t]), j & 1, &abort_word, 5)) {
+            FMHA_TL(2, j, t * 4 + 0);
+            if (!mbar_wait_warp(smem_u32(&bar_p_full[t]), j & 1, &abort_word, 5)) {
               ok = false;
               break;
             }
             tc_fence_after();
+            FMHA_TL(2, j, t * 4 + 1);
             issue_pv(t, ring_smem + slot_v * T::kTileBytes, j > 0);
+            FMHA_TL(2, j, t * 4 + 2);
             if (j + 1 < n_kv[t]) {
               if (!k_ready) {
-                if (!mbar_wait(smem_u32(&bar_kv_full[slot_k]), (it_k / T::kStages) & 1,
-                               &abort_word, 6)) {
+                if (!mbar_wait_warp(smem_u32(&bar_kv_full[slot_k]), (it_k / T::kStages) & 1,
+                                    &abort_word, 6)) {
                   ok = false;
                   break;
                 }
@@ -231,19 +249,19 @@ __global__ void __launch_bounds__(320, 1)
                 k_ready = true;
               }
               issue_qk(t, ring_smem + slot_k * T::kTileBytes);
-              umma_commit(smem_u32(&bar_s_full[t]));
+              umma_commit_elect(smem_u32(&bar_s_full[t]));
             } else {
-              umma_commit(smem_u32(&bar_o_full[t]));
+              umma_commit_elect(smem_u32(&bar_o_full[t]));
             }
+            FMHA_TL(2, j, t * 4 + 3);
           }
         }
         if (!ok) break;
-        umma_commit(smem_u32(&bar_kv_empty[slot_v]));
-        if (have_next) umma_commit(smem_u32(&bar_kv_empty[slot_k]));
+        umma_commit_elect(smem_u32(&bar_kv_empty[slot_v]));
+        if (have_next) umma_commit_elect(smem_u32(&bar_kv_empty[slot_k]));
       }
     }
-    __syncwarp();
-  } else {
+  } else if (warp < 8) {
     // =========================== softmax / epilogue ===========================
     const int t = warp >> 2;    // query tile of this warpgroup
     const int quad = warp & 3;  // TMEM lane quadrant of this warp
@@ -265,15 +283,19 @@ __global__ void __launch_bounds__(320, 1)
     const int n = n_kv[t];
     const bool tile_valid = (q0 + t * T::kBlockM) < p.seqlen_q;
 
+    const bool tl = (lane == 0 && quad == 0);
     for (int j = 0; j < n; ++j) {
+      if (tl) FMHA_TL(t, j, 0);
       if (!mbar_wait(smem_u32(&bar_s_full[t]), j & 1, &abort_word, 7)) break;
       tc_fence_after();
+      if (tl) FMHA_TL(t, j, 1);
       uint32_t s[4][32];
       tmem_ld32(tS + 0, s[0]);
       tmem_ld32(tS + 32, s[1]);
       tmem_ld32(tS + 64, s[2]);
       tmem_ld32(tS + 96, s[3]);
       tmem_wait_ld();
+      if (tl) FMHA_TL(t, j, 2);
 
       const int lim = row_limit - j * T::kBlockN;  // columns > lim of this tile are masked
       if (lim < T::kBlockN - 1) {
@@ -304,8 +326,9 @@ __global__ void __launch_bounds__(320, 1)
           mx3 = fminf(mx3, __uint_as_float(s[3][i]));
         }
       }
-      const float mx = (c >= 0.f) ? fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3))
-                                  : fminf(fminf(mx0, mx1), fminf(mx2, mx3));
+      float mx = (c >= 0.f) ? fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3))
+                            : fminf(fminf(mx0, mx1), fminf(mx2, mx3));
+      if (FMHA_ABLATE & 2) mx = __uint_as_float(s[0][0]);
 
       if (j == 0) {
         m_ref = mx;
@@ -330,6 +353,7 @@ __global__ void __launch_bounds__(320, 1)
         }
       }
 
+      if (tl) FMHA_TL(t, j, 3);
       const float neg_mc = isinf(m_ref) ? 0.f : -m_ref * c;
       float l0 = 0.f, l1 = 0.f, l2 = 0.f, l3 = 0.f;
 #pragma unroll
@@ -352,13 +376,16 @@ __global__ void __launch_bounds__(320, 1)
             pk[c2 * 16 + (i >> 1) + 1] = pack_half2(p2, p3);
           }
         }
-        tmem_st32(tS + hf * 32, pk);
+        if (!(FMHA_ABLATE & 4)) tmem_st32(tS + hf * 32, pk);
       }
       l += (l0 + l1) + (l2 + l3);
+      if (tl) FMHA_TL(t, j, 4);
       tmem_wait_st();
       tc_fence_before();
       mbar_arrive(smem_u32(&bar_p_full[t]));
+      if (tl) FMHA_TL(t, j, 5);
     }
+    if (tl) FMHA_TL(t, 31, 0);
 
     // ---- epilogue: O_t / l -> fp16 -> shared memory (over Q_t) -> TMA store; LSE
     if (tile_valid) {
@@ -407,6 +434,7 @@ __global__ void __launch_bounds__(320, 1)
         tma_commit_group();
         tma_wait_group<0>();
       }
+      if (tl) FMHA_TL(t, 31, 1);
     }
   }
 

@@ -11,6 +11,23 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+// Timeline instrumentation, compiled in only with -DFMHA_TIMELINE: the chosen CTA's elected
+// threads store clock64() at pipeline events so that stalls can be located without a profiler.
+#ifndef FMHA_ABLATE
+#define FMHA_ABLATE 0  // debug builds: bit 0 no exp2, bit 1 no row max, bit 2 no P store
+#endif
+#ifdef FMHA_TIMELINE
+#define FMHA_TL(role, j, k)                                                        \
+  do {                                                                              \
+    if (p.timeline != nullptr && (int)blockIdx.x == p.timeline_block && (j) < 32)  \
+      p.timeline[(role)*512 + (j)*16 + (k)] = clock64();                           \
+  } while (0)
+#else
+#define FMHA_TL(role, j, k) \
+  do {                      \
+  } while (0)
+#endif
+
 namespace fmha {
 
 // ---------------------------------------------------------------------------------
@@ -227,36 +244,121 @@ __device__ __forceinline__ uint64_t umma_smem_desc(uint32_t saddr, uint32_t lbo_
   return d;
 }
 
+// The descriptor split in two 32-bit words, so that an MMA issue loop only adds a constant
+// to the low word (address field) instead of rebuilding 64-bit values:
+//   low  word = address >> 4 | (LBO >> 4) << 16
+//   high word = SBO >> 4 | version 1 << 14 | layout 2 << 29      (the same for every tile here)
+__host__ __device__ constexpr uint32_t umma_desc_hi(uint32_t sbo_bytes) {
+  return ((sbo_bytes >> 4) & 0x3fffu) | (1u << 14) | (2u << 29);
+}
+__device__ __forceinline__ uint32_t umma_desc_lo(uint32_t saddr, uint32_t lbo_bytes) {
+  return ((saddr >> 4) & 0x3fffu) | (((lbo_bytes >> 4) & 0x3fffu) << 16);
+}
+constexpr uint32_t kDescHi = umma_desc_hi(1024);
+constexpr uint32_t kLboKMajor = 16;      // unused by the hardware for swizzled K-major tiles
+constexpr uint32_t kLboMnMajor = 16384;  // next 64-element block along M/N = next TMA box
+
 // D[tmem] (+)= A[smem] * B[smem]
-__device__ __forceinline__ void umma_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
+__device__ __forceinline__ void umma_ss(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo,
                                         uint32_t idesc, uint32_t accumulate) {
   asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t}"
+      "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
+      "mov.b64 da, {%1, %3};\n\t"
+      "mov.b64 db, {%2, %3};\n\t"
+      "setp.ne.b32 p, %5, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %4, {%6, %6, %6, %6}, p;\n\t}"
       :
-      : "r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(0u)
+      : "r"(d_tmem), "r"(a_lo), "r"(b_lo), "r"(kDescHi), "r"(idesc), "r"(accumulate), "r"(0u)
       : "memory");
 }
 // D[tmem] (+)= A[tmem] * B[smem]   (A: 128 lanes x K fp16, two per 32-bit column)
-__device__ __forceinline__ void umma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc,
+__device__ __forceinline__ void umma_ts(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_lo,
                                         uint32_t idesc, uint32_t accumulate) {
   asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, {%5, %5, %5, %5}, p;\n\t}"
+      "{\n\t.reg .pred p;\n\t.reg .b64 db;\n\t"
+      "mov.b64 db, {%2, %3};\n\t"
+      "setp.ne.b32 p, %5, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], db, %4, {%6, %6, %6, %6}, p;\n\t}"
       :
-      : "r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(0u)
+      : "r"(d_tmem), "r"(a_tmem), "r"(b_lo), "r"(kDescHi), "r"(idesc), "r"(accumulate), "r"(0u)
       : "memory");
+}
+
+// ---- converged-warp variants.  The MMA / TMA issue loops are run by all 32 lanes of a warp so
+// that addresses and descriptors stay in uniform registers; only the instruction itself is
+// issued by one elected lane.  Call these from a converged warp only.
+__device__ __forceinline__ uint32_t elect_one() {
+  uint32_t pred;
+  asm volatile(
+      "{\n\t.reg .pred P;\n\t"
+      "elect.sync _|P, 0xffffffff;\n\t"
+      "selp.u32 %0, 1, 0, P;\n\t}"
+      : "=r"(pred));
+  return pred;
+}
+__device__ __forceinline__ void umma_ss_elect(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo,
+                                              uint32_t idesc, uint32_t accumulate) {
+  if (elect_one()) umma_ss(d_tmem, a_lo, b_lo, idesc, accumulate);
+}
+__device__ __forceinline__ void umma_ts_elect(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_lo,
+                                              uint32_t idesc, uint32_t accumulate) {
+  if (elect_one()) umma_ts(d_tmem, a_tmem, b_lo, idesc, accumulate);
+}
+__device__ __forceinline__ void umma_commit_elect(uint32_t bar) {
+  if (elect_one()) umma_commit(bar);
+}
+// bounded wait by a whole converged warp, with a warp-uniform result
+__device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity,
+                                               volatile int* abort_word, int who) {
+  const bool ok = mbar_wait(bar, parity, abort_word, who);
+  return __all_sync(0xffffffffu, ok);
+}
+
+// warpgroup-wide register re-budgeting: every warp of an aligned group of 4 warps executes it
+template <int N>
+__device__ __forceinline__ void reg_alloc() {
+  asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N));
+}
+template <int N>
+__device__ __forceinline__ void reg_dealloc() {
+  asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N));
 }
 
 // ---------------------------------------------------------------------------------
 // small math helpers
 // ---------------------------------------------------------------------------------
 __device__ __forceinline__ float fast_exp2(float x) {
+#if defined(FMHA_ABLATE) && (FMHA_ABLATE & 1)
+  return x;  // timing experiments only
+#else
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
+#endif
+}
+// two exp2 per MUFU operation, fp16 in and out (inputs here are <= ~0, results in [0, 1])
+__device__ __forceinline__ uint32_t exp2_half2(uint32_t x) {
+  uint32_t y;
+  asm("ex2.approx.f16x2 %0, %1;" : "=r"(y) : "r"(x));
+  return y;
+}
+__device__ __forceinline__ uint32_t mul_half2(uint32_t a, uint32_t b) {
+  uint32_t y;
+  asm("mul.rn.f16x2 %0, %1, %2;" : "=r"(y) : "r"(a), "r"(b));
+  return y;
+}
+__device__ __forceinline__ float4 lds128(uint32_t addr) {
+  float4 v;
+  asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];"
+               : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
+               : "r"(addr));
+  return v;
+}
+__device__ __forceinline__ void sts128(uint32_t addr, uint32_t a, uint32_t b, uint32_t c,
+                                       uint32_t d) {
+  asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c),
+               "r"(d)
+               : "memory");
 }
 __device__ __forceinline__ uint32_t pack_half2(float lo, float hi) {
   __half2 h = __floats2half2_rn(lo, hi);
