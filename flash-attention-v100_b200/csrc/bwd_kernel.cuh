@@ -52,6 +52,10 @@ struct BwdKernelParams {
   int timeline_block;
 };
 
+constexpr int kBwdRegsIssue = 80;     // warps 12-15
+constexpr int kBwdRegsCompute = 120;  // warps 0-7
+constexpr int kBwdRegsDq = 128 + (128 - kBwdRegsIssue) + 2 * (128 - kBwdRegsCompute);  // warps 8-11
+
 template <int D>
 struct BwdTraits {
   static constexpr int kBlock = 128;
@@ -60,9 +64,9 @@ struct BwdTraits {
   static constexpr int kTileBytes = kBoxes * kBoxBytes;  // a 128 x D fp16 tile
   static constexpr int kDsBytes = 2 * kBoxBytes;         // dS^T: 128 x 128 fp16
   static constexpr int kQStages = 2;
-  static constexpr int kStageBytes = 4 * 4096;           // dQ staging: 32 x 32 fp32 per warp
-  static constexpr int kStatBytes = 2 * 256 * 4;         // 2 buffers of lse2[128] + delta[128]
-  static constexpr int kThreads = 448;
+  static constexpr int kStageBytes = 4 * 2 * 4096;       // dQ staging: 2 x (32 x 32 fp32) per warp
+  static constexpr int kStatBytes = 256 * 4;             // lse2[128] + delta[128] of one tile
+  static constexpr int kThreads = 512;  // 4 warpgroups; warps 14, 15 only take part in barriers
   // K, V, Q x2, dO, dS^T, dQ staging, statistics
   static constexpr int kSmemBytes =
       1024 + (3 + kQStages) * kTileBytes + kDsBytes + kStageBytes + kStatBytes;
@@ -74,7 +78,7 @@ struct BwdTraits {
 };
 
 template <int D>
-__global__ void __launch_bounds__(448, 1)
+__global__ void __launch_bounds__(512, 1)
     fmha_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                     const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_do,
                     const __grid_constant__ CUtensorMap tm_dk, const __grid_constant__ CUtensorMap tm_dv,
@@ -85,7 +89,7 @@ __global__ void __launch_bounds__(448, 1)
   __shared__ uint64_t bar_q_full[T::kQStages], bar_q_empty[T::kQStages];
   __shared__ uint64_t bar_do_full, bar_do_empty;
   __shared__ uint64_t bar_s_full, bar_dp_full, bar_p_ready, bar_ds_ready, bar_dq_full,
-      bar_dq_empty, bar_done;
+      bar_dq_empty, bar_ds_free, bar_done;
   __shared__ uint32_t tmem_base_slot;
   __shared__ int abort_word;
   __shared__ int skip_cta;
@@ -106,7 +110,7 @@ __global__ void __launch_bounds__(448, 1)
   const uint32_t q_smem = v_smem + T::kTileBytes;                   // kQStages tiles
   const uint32_t do_smem = q_smem + T::kQStages * T::kTileBytes;    // one tile
   const uint32_t ds_smem = do_smem + T::kTileBytes;                 // dS^T
-  const uint32_t stg_smem = ds_smem + T::kDsBytes;                  // dQ staging, 4 KB per warp
+  const uint32_t stg_smem = ds_smem + T::kDsBytes;                  // dQ staging, 2 x 4 KB per warp
   const uint32_t stat_smem = stg_smem + T::kStageBytes;             // statistics
 
   // ---- coordinates: consecutive CTAs = same head; early KV tiles (most query tiles) first
@@ -140,6 +144,7 @@ __global__ void __launch_bounds__(448, 1)
     mbar_init(smem_u32(&bar_ds_ready), 256);
     mbar_init(smem_u32(&bar_dq_full), 1);
     mbar_init(smem_u32(&bar_dq_empty), 128);
+    mbar_init(smem_u32(&bar_ds_free), 1);
     mbar_init(smem_u32(&bar_done), 1);
     fence_barrier_init();
   }
@@ -152,6 +157,13 @@ __global__ void __launch_bounds__(448, 1)
   tc_fence_after();
   const uint32_t tmem_base = tmem_base_slot;
 
+  // Register budget: 512 threads leave 128 per thread.  The producer / MMA warpgroup and the
+  // compute warpgroups hand part of their share to the dQ warpgroup, which must hold a whole
+  // 128-column dQ row per thread to drain tensor memory in one go (the next dP^T waits for
+  // those columns).  Each setmaxnreg sits at the top of its warpgroup's own branch: the
+  // compiler budgets registers per region only when the instruction dominates the region.
+  if (warp >= 12) {
+    reg_dealloc<kBwdRegsIssue>();
   if (warp == 12) {
     // =========================== TMA producer ===========================
     if (cnt > 0) {
@@ -251,22 +263,25 @@ __global__ void __launch_bounds__(448, 1)
           issue_kmajor(T::kColS, k_smem, q_smem + st1 * T::kTileBytes);
           umma_commit_elect(smem_u32(&bar_s_full));
         }
-        // ---- dK += dS^T Q_i ; dQ_i = dS K   (independent accumulators: interleaved)
+        // ---- dQ_i = dS K first (its read-out is on the critical path), then dK += dS^T Q_i
         FMHA_TL(2, n, 2);
         if (!mbar_wait_warp(smem_u32(&bar_ds_ready), n & 1, &abort_word, 8)) break;
         tc_fence_after();
         FMHA_TL(2, n, 3);
+#pragma unroll
+        for (int ks = 0; ks < T::kBlock / 16; ++ks)
+          umma_ss_elect(tmem_base + T::kColDQ, ds_lo_mn + ks * 128, k_lo_mn + ks * 128, T::kIdescDQ,
+                        ks > 0 ? 1u : 0u);
+        umma_commit_elect(smem_u32(&bar_dq_full));
         const uint32_t q_lo_mn = umma_desc_lo(q_addr, kLboMnMajor);
 #pragma unroll
         for (int ks = 0; ks < T::kBlock / 16; ++ks) {
           const uint32_t off = ((ks >> 2) * T::kBoxBytes + (ks & 3) * 32) >> 4;
-          umma_ss_elect(tmem_base + T::kColDQ, ds_lo_mn + ks * 128, k_lo_mn + ks * 128, T::kIdescDQ,
-                        ks > 0 ? 1u : 0u);
           umma_ss_elect(tmem_base + T::kColDK, ds_lo_k + off, q_lo_mn + ks * 128, T::kIdescDV,
                         (n > 0 || ks > 0) ? 1u : 0u);
         }
-        umma_commit_elect(smem_u32(&bar_dq_full));
         umma_commit_elect(smem_u32(&bar_q_empty[st]));
+        umma_commit_elect(smem_u32(&bar_ds_free));
         FMHA_TL(2, n, 4);
         // ---- dP^T of the next query tile (its columns hold dQ_i until the dQ group read it)
         if (n + 1 < cnt) {
@@ -281,6 +296,7 @@ __global__ void __launch_bounds__(448, 1)
       }
       umma_commit_elect(smem_u32(&bar_done));
     }
+  }
   } else {
     const int quad = warp & 3;
     const int r = quad * 32 + lane;  // TMEM lane of this thread
@@ -289,6 +305,7 @@ __global__ void __launch_bounds__(448, 1)
 
     if (warp < 8) {
       // =========================== compute groups: P^T, dS^T ===========================
+      reg_dealloc<kBwdRegsCompute>();
       const int cg = warp >> 2;           // query-column half of this group
       const int ct = threadIdx.x;         // 0..255 among the compute threads
       const int kvi = kv0 + r;            // key of this thread
@@ -305,11 +322,11 @@ __global__ void __launch_bounds__(448, 1)
 
       for (int n = 0; n < cnt; ++n) {
         const int qbase = (i_begin + n) * T::kBlock;
-        const uint32_t sb = stat_smem + (n & 1) * 1024;  // lse2 at [0, 512), delta at [512, 1024)
+        const uint32_t sb = stat_smem;  // lse2 at [0, 512), delta at [512, 1024)
+        named_bar_sync(3, 256);  // every thread is done reading the previous tile's values
         asm volatile("st.shared.f32 [%0], %1;" ::"r"(sb + ct * 4), "f"(stat_next) : "memory");
         if (n + 1 < cnt) stat_next = __ldg(stat_src + (size_t)(i_begin + n + 1) * T::kBlock);
-        // everybody is done with the other buffer's previous use and sees this buffer
-        named_bar_sync(3, 256);
+        named_bar_sync(4, 256);  // this tile's values are visible
 
         // first visible query column of this thread's half (>= 64: none)
         int first_visible = 0;
@@ -322,6 +339,7 @@ __global__ void __launch_bounds__(448, 1)
         const int fvh = first_visible - cg * 64;
 
         uint32_t pp[32];  // P^T of this row and half, fp16 pairs
+        uint32_t npd[32]; // -(P^T o delta), fp16 pairs: dS^T = P^T o dP^T - P^T o delta
         if (tl) FMHA_TL(0, n, 0);
         mbar_wait(smem_u32(&bar_s_full), n & 1, &abort_word, 11);  // on a time-out: keep going,
         // every later wait returns at once and all 256 threads still meet at the named barrier
@@ -357,11 +375,18 @@ __global__ void __launch_bounds__(448, 1)
         tc_fence_before();
         mbar_arrive(smem_u32(&bar_p_ready));
         if (tl) FMHA_TL(0, n, 2);
+        // off the critical path (dP^T is not there yet): -(P o delta)
+#pragma unroll
+        for (int j = 0; j < 32; j += 2) {
+          const float4 Dl = lds128(sb + 512 + (cg * 64 + 2 * j) * 4);
+          npd[j + 0] = mul_half2(pp[j + 0], pack_half2(-Dl.x, -Dl.y));
+          npd[j + 1] = mul_half2(pp[j + 1], pack_half2(-Dl.z, -Dl.w));
+        }
 
         mbar_wait(smem_u32(&bar_dp_full), n & 1, &abort_word, 12);
         if (tl) FMHA_TL(0, n, 3);
         // dS^T of the previous tile must have been consumed by its dK / dQ MMAs
-        if (n > 0) mbar_wait(smem_u32(&bar_dq_full), (n - 1) & 1, &abort_word, 13);
+        if (n > 0) mbar_wait(smem_u32(&bar_ds_free), (n - 1) & 1, &abort_word, 13);
         tc_fence_after();
         if (tl) FMHA_TL(0, n, 4);
         {
@@ -376,15 +401,12 @@ __global__ void __launch_bounds__(448, 1)
             for (int k8 = 0; k8 < 4; ++k8) {  // 8 columns = one 16-byte chunk
               uint32_t w[4];
 #pragma unroll
-              for (int hh = 0; hh < 2; ++hh) {
-                const int i = k8 * 8 + hh * 4;
-                const float4 Dl = lds128(sb + 512 + (cg * 64 + cc * 32 + i) * 4);
-                const uint32_t a01 = pack_half2(__uint_as_float(dp[cc][i + 0]) - Dl.x,
-                                                __uint_as_float(dp[cc][i + 1]) - Dl.y);
-                const uint32_t a23 = pack_half2(__uint_as_float(dp[cc][i + 2]) - Dl.z,
-                                                __uint_as_float(dp[cc][i + 3]) - Dl.w);
-                w[hh * 2 + 0] = mul_half2(pp[cc * 16 + (i >> 1) + 0], a01);
-                w[hh * 2 + 1] = mul_half2(pp[cc * 16 + (i >> 1) + 1], a23);
+              for (int q2 = 0; q2 < 4; ++q2) {
+                const int i = k8 * 8 + q2 * 2;     // column within this 32-column block
+                const int j = cc * 16 + (i >> 1);  // its fp16 pair
+                w[q2] = fma_half2(pp[j],
+                                  pack_half2(__uint_as_float(dp[cc][i]), __uint_as_float(dp[cc][i + 1])),
+                                  npd[j]);
               }
               const int ch = cc * 4 + k8;  // chunk of this thread's 128-byte row
               sts128(row_addr + ((ch ^ (r & 7)) << 4), w[0], w[1], w[2], w[3]);
@@ -397,8 +419,9 @@ __global__ void __launch_bounds__(448, 1)
       }
     } else {
       // =========================== dQ group ===========================
+      reg_alloc<kBwdRegsDq>();
       const uint32_t tDQ = tmem_base + lane_addr + T::kColDQ;
-      const uint32_t stage = stg_smem + quad * 4096;
+      const uint32_t stage = stg_smem + quad * 8192;
       const uint32_t my_row = stage + lane * 128;
       const bool tl = (r == 0);
       for (int n = 0; n < cnt; ++n) {
@@ -407,33 +430,30 @@ __global__ void __launch_bounds__(448, 1)
         if (!mbar_wait(smem_u32(&bar_dq_full), n & 1, &abort_word, 14)) break;
         tc_fence_after();
         if (tl) FMHA_TL(1, n, 1);
+        // The whole dQ row goes to registers first so that the dQ columns are released to the
+        // next dP^T as early as possible; then 32-column chunks go out through shared memory.
+        uint32_t acc[D / 32][32];
 #pragma unroll
-        for (int pair = 0; pair < D / 64; ++pair) {
-          uint32_t acc[2][32];
-          tmem_ld32(tDQ + pair * 64, acc[0]);
-          tmem_ld32(tDQ + pair * 64 + 32, acc[1]);
-          tmem_wait_ld();
-          if (pair == D / 64 - 1) {
-            // the whole dQ tile is in registers: its columns may take the next dP^T
-            tc_fence_before();
-            mbar_arrive(smem_u32(&bar_dq_empty));
-            if (tl) FMHA_TL(1, n, 2);
-          }
+        for (int cc = 0; cc < D / 32; ++cc) tmem_ld32(tDQ + cc * 32, acc[cc]);
+        tmem_wait_ld();
+        tc_fence_before();
+        mbar_arrive(smem_u32(&bar_dq_empty));
+        if (tl) FMHA_TL(1, n, 2);
 #pragma unroll
-          for (int cc = 0; cc < 2; ++cc) {
-            // the previous reduce-add must have finished reading the staging buffer
-            if (lane == 0) tma_wait_group_read<0>();
-            __syncwarp();
+        for (int cc = 0; cc < D / 32; ++cc) {
+          // buffer (cc & 1) was last used two reduce-adds ago: at most one group may still read
+          if (lane == 0) tma_wait_group_read<1>();
+          __syncwarp();
+          const uint32_t buf_row = my_row + (cc & 1) * 4096;
 #pragma unroll
-            for (int k4 = 0; k4 < 8; ++k4)
-              sts128(my_row + ((k4 ^ (lane & 7)) << 4), acc[cc][k4 * 4 + 0], acc[cc][k4 * 4 + 1],
-                     acc[cc][k4 * 4 + 2], acc[cc][k4 * 4 + 3]);
-            fence_proxy_async_smem();
-            __syncwarp();
-            if (lane == 0) {
-              tma_reduce_add_4d(&tm_dqacc, stage, pair * 64 + cc * 32, q0w, h, z);
-              tma_commit_group();
-            }
+          for (int k4 = 0; k4 < 8; ++k4)
+            sts128(buf_row + ((k4 ^ (lane & 7)) << 4), acc[cc][k4 * 4 + 0], acc[cc][k4 * 4 + 1],
+                   acc[cc][k4 * 4 + 2], acc[cc][k4 * 4 + 3]);
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            tma_reduce_add_4d(&tm_dqacc, stage + (cc & 1) * 4096, cc * 32, q0w, h, z);
+            tma_commit_group();
           }
         }
         if (tl) FMHA_TL(1, n, 3);

@@ -48,18 +48,21 @@ struct FwdTraits {
   static constexpr int kBoxBytes = 128 * 128;  // 128 rows x 128 bytes
   static constexpr int kTileBytes = kBoxes * kBoxBytes;
   static constexpr int kStages = (D == 128) ? 4 : 8;
-  static constexpr int kThreads = 320;
+  static constexpr int kThreads = 384;  // softmax 0, softmax 1, {TMA, MMA, 2 idle} warpgroups
   static constexpr int kSmemBytes = 1024 + (kTilesM + kStages) * kTileBytes;
   static constexpr int kTmemCols = 512;
   static constexpr uint32_t kIdescQK = umma_idesc_f16(128, kBlockN, 0, 0);
   static constexpr uint32_t kIdescPV = umma_idesc_f16(128, D, 0, 1);
 };
 
+constexpr int kFwdRegsIssue = 88;                               // warps 8-11
+constexpr int kFwdRegsSoftmax = 168 + (168 - kFwdRegsIssue) / 2;  // warps 0-7: 208
+
 // lazy rescale threshold in the log2 domain: P may grow to 2^8 before O is rescaled
 constexpr float kRescaleThreshold = 8.0f;
 
 template <int D>
-__global__ void __launch_bounds__(320, 1)
+__global__ void __launch_bounds__(384, 1)
     fmha_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                     const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_o,
                     const FwdKernelParams p) {
@@ -138,6 +141,11 @@ __global__ void __launch_bounds__(320, 1)
   tc_fence_after();
   const uint32_t tmem_base = tmem_base_slot;
 
+  // Register budget: 384 threads leave 168 per thread.  The producer / MMA warpgroup hands part
+  // of its share to the softmax warpgroups, whose threads hold a 128-column row of S.  Each
+  // setmaxnreg sits at the top of its warpgroup's own branch.
+  if (warp >= 8) {
+    reg_dealloc<kFwdRegsIssue>();
   if (warp == 8) {
     // =========================== TMA producer (converged warp, elected issue) ==========
     if (n_max > 0) {
@@ -261,8 +269,10 @@ __global__ void __launch_bounds__(320, 1)
         if (have_next) umma_commit_elect(smem_u32(&bar_kv_empty[slot_k]));
       }
     }
-  } else if (warp < 8) {
+  }
+  } else {
     // =========================== softmax / epilogue ===========================
+    reg_alloc<kFwdRegsSoftmax>();
     const int t = warp >> 2;    // query tile of this warpgroup
     const int quad = warp & 3;  // TMEM lane quadrant of this warp
     const int row_in_tile = quad * 32 + lane;

@@ -347,6 +347,11 @@ __device__ __forceinline__ uint32_t mul_half2(uint32_t a, uint32_t b) {
   asm("mul.rn.f16x2 %0, %1, %2;" : "=r"(y) : "r"(a), "r"(b));
   return y;
 }
+__device__ __forceinline__ uint32_t fma_half2(uint32_t a, uint32_t b, uint32_t c) {
+  uint32_t y;
+  asm("fma.rn.f16x2 %0, %1, %2, %3;" : "=r"(y) : "r"(a), "r"(b), "r"(c));
+  return y;
+}
 __device__ __forceinline__ float4 lds128(uint32_t addr) {
   float4 v;
   asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];"
