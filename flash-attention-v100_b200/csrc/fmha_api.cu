@@ -6,6 +6,7 @@
 #include <cuda.h>
 #include <cuda_runtime.h>
 
+#include <algorithm>
 #include <cmath>
 #include <cstdint>
 #include <cstring>
@@ -76,6 +77,14 @@ int make_accum_map(CUtensorMap* map, float* base, int Z, int N, int H, int D) {
 long long* g_timeline = nullptr;
 int g_timeline_block = 0;
 
+int sm_count() {
+  int dev = 0, n = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess ||
+      cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0)
+    return 148;
+  return n;
+}
+
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 int check_strides(const FmhaStrides& s, int N, int H, int Z) {
@@ -133,6 +142,7 @@ int launch_fwd(const FmhaFwdParams* p, cudaStream_t stream) {
   kp.seqlen_q = p->seqlen_q;
   kp.seqlen_k = p->seqlen_k;
   kp.num_q_blocks = (p->seqlen_q + 255) / 256;
+  kp.num_heads_total = p->batch * p->heads;
   kp.scale_log2 = p->scale * 1.4426950408889634f;
   kp.causal = p->causal ? 1 : 0;
   kp.causal_shift = p->causal_shift;
@@ -143,7 +153,9 @@ int launch_fwd(const FmhaFwdParams* p, cudaStream_t stream) {
   if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, T::kSmemBytes) !=
       cudaSuccess)
     return FMHA_ERR_LAUNCH;
-  const unsigned grid = (unsigned)((long long)kp.num_q_blocks * p->heads * p->batch);
+  // persistent grid: one CTA per SM (or per super-item = pair of query blocks, if fewer)
+  const long long n_super = (long long)((kp.num_q_blocks + 1) / 2) * kp.num_heads_total;
+  const unsigned grid = (unsigned)std::min<long long>(n_super, sm_count());
   kernel<<<grid, T::kThreads, T::kSmemBytes, stream>>>(tq, tk, tv, to, kp);
   return cudaGetLastError() == cudaSuccess ? FMHA_OK : FMHA_ERR_LAUNCH;
 }

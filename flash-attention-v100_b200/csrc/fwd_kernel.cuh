@@ -2,23 +2,37 @@
 //
 // Replaces fused_mha_forward_kernel of the reference (kernel/fused_mha_kernel.cu:20-323):
 // same mathematics (online softmax over KV tiles, running max / sum, O rescale), none of its
-// structure.  One CTA owns 256 query rows (two 128-row tiles) of one (batch, head) and walks
-// the KV sequence in 128-row tiles:
+// structure.  The kernel is PERSISTENT: one CTA per SM walks a list of work items; a work item
+// is 256 query rows (two 128-row tiles) of one (batch, head), processed against the KV sequence
+// in 128-row tiles:
 //
-//   warp 8      TMA producer: Q tiles once, then K_0, V_0, K_1, V_1, ... through a ring of
-//               shared-memory slots (full / empty mbarriers per slot)
-//   warp 9      MMA issuer (one thread): S_t = Q_t K_j^T (both operands in shared memory) and
-//               O_t += P_t V_j (P_t read from tensor memory), accumulators in tensor memory
+//   warp 8      TMA producer for K_0, V_0, K_1, V_1, ... through a ring of shared-memory slots
+//               (full / empty mbarriers per slot); runs ahead into the next item as slots free
+//   warp 10     TMA producer for the two Q tiles of an item, as soon as the previous item's
+//               last S = Q K^T has released them
+//   warp 9      MMA issuer: S_t = Q_t K_j^T (both operands in shared memory) and
+//               O_t += P_t V_j (P_t read from tensor memory), accumulators in tensor memory.
+//               The whole warp runs the loop so that descriptors stay in uniform registers;
+//               one elected lane issues.
 //   warps 0-3   softmax of query tile 0: one thread per row, S_0 read with tcgen05.ld, online
 //               exp2 softmax, P_0 written back over S_0 as fp16, lazy O_0 rescale, epilogue
 //   warps 4-7   the same for query tile 1
 //
-// While one softmax group works on its tile the tensor pipe runs the other tile's MMAs.
+// While one softmax group works on its tile the tensor pipe runs the other tile's MMAs, and
+// while the groups run an item's epilogue the producer and the MMA warp already start the next
+// item (its Q / K loads and first S = Q K^T), so that the load latency at the head of an item
+// and the store at its tail are hidden.
+//
 // Tensor memory (512 columns): S_0 [0,128) S_1 [128,256) O_0 [256,256+D) O_1 [256+D,256+2D);
 // P_t aliases the first 64 columns of S_t (two fp16 per 32-bit column).
 //
 // Shared memory: rows of 64 fp16 (128 bytes) in the TMA / UMMA 128-byte swizzle.  A 128 x D
-// tile is D/64 boxes of 128 x 64, box b at byte offset b * 16384.
+// tile is D/64 boxes of 128 x 64, box b at byte offset b * 16384.  Per softmax group one
+// extra tile stages the output for the TMA store.
+//
+// Work items are paired (heaviest with lightest query block of a head) into super-items of
+// equal cost, and super-items are dealt round-robin to the CTAs: balanced without a global
+// work counter, and CTAs that run at the same time work on neighbouring heads (K/V stay in L2).
 #pragma once
 #include <cuda.h>
 #include <math_constants.h>
@@ -30,79 +44,78 @@ namespace fmha {
 struct FwdKernelParams {
   float* lse;
   int heads, seqlen_q, seqlen_k;
-  int num_q_blocks;  // ceil(seqlen_q / 256)
-  float scale_log2;  // scale * log2(e)
+  int num_q_blocks;     // ceil(seqlen_q / 256)
+  int num_heads_total;  // batch * heads
+  float scale_log2;     // scale * log2(e)
   int causal, causal_shift;
   int* status;
-  // debug builds (-DFMHA_TIMELINE) only: clock64 stamps of one CTA, see FMHA_TL below
+  // debug builds (-DFMHA_TIMELINE) only: clock64 stamps of one CTA, see FMHA_TL
   long long* timeline;
   int timeline_block;
 };
 
+#ifndef FMHA_ABLATE
+#define FMHA_ABLATE 0  // debug builds: bit 0 no exp2, bit 1 no row max, bit 2 no P store
+#endif
+
 template <int D>
 struct FwdTraits {
   static constexpr int kBlockM = 128;  // rows per query tile
-  static constexpr int kTilesM = 2;    // query tiles per CTA
+  static constexpr int kTilesM = 2;    // query tiles per work item
   static constexpr int kBlockN = 128;  // rows per KV tile
   static constexpr int kBoxes = D / 64;
   static constexpr int kBoxBytes = 128 * 128;  // 128 rows x 128 bytes
   static constexpr int kTileBytes = kBoxes * kBoxBytes;
-  static constexpr int kStages = (D == 128) ? 4 : 8;
+  static constexpr int kStages = (D == 128) ? 3 : 6;
   static constexpr int kThreads = 384;  // softmax 0, softmax 1, {TMA, MMA, 2 idle} warpgroups
-  static constexpr int kSmemBytes = 1024 + (kTilesM + kStages) * kTileBytes;
+  // Q tiles, K/V ring, one output staging tile per softmax group
+  static constexpr int kSmemBytes = 1024 + (kTilesM + kStages + 2) * kTileBytes;
   static constexpr int kTmemCols = 512;
   static constexpr uint32_t kIdescQK = umma_idesc_f16(128, kBlockN, 0, 0);
   static constexpr uint32_t kIdescPV = umma_idesc_f16(128, D, 0, 1);
 };
 
-constexpr int kFwdRegsIssue = 88;                               // warps 8-11
+constexpr int kFwdRegsIssue = 88;                                 // warps 8-11
 constexpr int kFwdRegsSoftmax = 168 + (168 - kFwdRegsIssue) / 2;  // warps 0-7: 208
 
 // lazy rescale threshold in the log2 domain: P may grow to 2^8 before O is rescaled
 constexpr float kRescaleThreshold = 8.0f;
 
-template <int D>
-__global__ void __launch_bounds__(384, 1)
-    fmha_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
-                    const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_o,
-                    const FwdKernelParams p) {
-  using T = FwdTraits<D>;
-  extern __shared__ uint8_t smem_raw[];
-  __shared__ uint64_t bar_q_full;
-  __shared__ uint64_t bar_kv_full[T::kStages];
-  __shared__ uint64_t bar_kv_empty[T::kStages];
-  __shared__ uint64_t bar_s_full[2];
-  __shared__ uint64_t bar_p_full[2];
-  __shared__ uint64_t bar_o_full[2];
-  __shared__ uint32_t tmem_base_slot;
-  __shared__ int abort_word;
-  __shared__ int skip_cta;
-
-  const int warp = threadIdx.x >> 5;
-  const int lane = threadIdx.x & 31;
-
-  // a status word already set by an earlier CTA means: drain the grid quickly
-  if (threadIdx.x == 0) {
-    skip_cta = (p.status != nullptr && *reinterpret_cast<volatile int*>(p.status) != 0) ? 1 : 0;
-    abort_word = 0;
+// The work list of one CTA.  Super-item s = (head zh, pair k): query blocks nqb-1-k (heavy,
+// first) and k (light), one item only when they coincide.  Every role of the CTA walks the
+// same list with its own copy of this iterator.
+struct FwdWorkIter {
+  int s, sub, n_super, pairs_per_head, nqb, stride;
+  __device__ FwdWorkIter(int first, int stride_, int nqb_, int heads_total)
+      : s(first), sub(0), pairs_per_head((nqb_ + 1) / 2), nqb(nqb_), stride(stride_) {
+    n_super = pairs_per_head * heads_total;
   }
-  __syncthreads();
-  if (skip_cta) return;
+  __device__ bool next(int& zh, int& qb) {
+    while (s < n_super) {
+      const int k = s % pairs_per_head;
+      const int hi = nqb - 1 - k;
+      zh = s / pairs_per_head;
+      if (sub == 0) {
+        sub = 1;
+        qb = hi;
+        return true;
+      }
+      sub = 0;
+      s += stride;
+      if (k != hi) {
+        qb = k;
+        return true;
+      }
+    }
+    return false;
+  }
+};
 
-  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-  const uint32_t q_smem = smem_base;                                // 2 query tiles
-  const uint32_t ring_smem = smem_base + T::kTilesM * T::kTileBytes;  // K/V ring
-
-  // ---- tile coordinates: consecutive CTAs = same head, heavy (late) query blocks first
-  const int nqb = p.num_q_blocks;
-  const int zh = blockIdx.x / nqb;
-  const int qb = nqb - 1 - (blockIdx.x % nqb);
-  const int z = zh / p.heads;
-  const int h = zh % p.heads;
-  const int q0 = qb * (T::kBlockM * T::kTilesM);
-
+// KV tiles each of the two query tiles of an item has to visit (0 = none)
+template <int D>
+__device__ __forceinline__ void fwd_item_extent(const FwdKernelParams& p, int q0, int (&n_kv)[2]) {
+  using T = FwdTraits<D>;
   const int nk_total = (p.seqlen_k + T::kBlockN - 1) / T::kBlockN;
-  int n_kv[2];
 #pragma unroll
   for (int t = 0; t < 2; ++t) {
     const int r0 = q0 + t * T::kBlockM;
@@ -116,19 +129,56 @@ __global__ void __launch_bounds__(384, 1)
       n_kv[t] = lim < 0 ? 0 : (int)min((long long)nk_total, lim / T::kBlockN + 1);
     }
   }
-  const int n_max = max(n_kv[0], n_kv[1]);
+}
+
+template <int D>
+__global__ void __launch_bounds__(384, 1)
+    fmha_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+                    const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_o,
+                    const FwdKernelParams p) {
+  using T = FwdTraits<D>;
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ uint64_t bar_q_full[2];   // Q_t of the current item has landed
+  __shared__ uint64_t bar_q_free[2];   // the last S_t = Q_t K^T of the item is done: Q_t reusable
+  __shared__ uint64_t bar_kv_full[T::kStages];
+  __shared__ uint64_t bar_kv_empty[T::kStages];
+  __shared__ uint64_t bar_s_full[2];
+  __shared__ uint64_t bar_p_full[2];
+  __shared__ uint64_t bar_o_full[2];
+  __shared__ uint64_t bar_o_read[2];   // the softmax group has O_t in registers: O_t reusable
+  __shared__ uint32_t tmem_base_slot;
+  __shared__ int abort_word;
+  __shared__ int skip_cta;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  // a status word already set by an earlier launch / CTA means: drain the grid quickly
+  if (threadIdx.x == 0) {
+    skip_cta = (p.status != nullptr && *reinterpret_cast<volatile int*>(p.status) != 0) ? 1 : 0;
+    abort_word = 0;
+  }
+  __syncthreads();
+  if (skip_cta) return;
+
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const uint32_t q_smem = smem_base;                                    // 2 query tiles
+  const uint32_t ring_smem = smem_base + T::kTilesM * T::kTileBytes;    // K/V ring
+  const uint32_t ostage_smem = ring_smem + T::kStages * T::kTileBytes;  // 2 output tiles
 
   // ---- set-up: barriers (thread 0), tensor memory (warp 9)
   if (threadIdx.x == 0) {
-    mbar_init(smem_u32(&bar_q_full), 1);
     for (int s = 0; s < T::kStages; ++s) {
       mbar_init(smem_u32(&bar_kv_full[s]), 1);
       mbar_init(smem_u32(&bar_kv_empty[s]), 1);
     }
     for (int t = 0; t < 2; ++t) {
+      mbar_init(smem_u32(&bar_q_full[t]), 1);
+      mbar_init(smem_u32(&bar_q_free[t]), 1);
       mbar_init(smem_u32(&bar_s_full[t]), 1);
       mbar_init(smem_u32(&bar_p_full[t]), 128);
       mbar_init(smem_u32(&bar_o_full[t]), 1);
+      mbar_init(smem_u32(&bar_o_read[t]), 128);
     }
     fence_barrier_init();
   }
@@ -141,55 +191,104 @@ __global__ void __launch_bounds__(384, 1)
   tc_fence_after();
   const uint32_t tmem_base = tmem_base_slot;
 
+  FwdWorkIter work(blockIdx.x, gridDim.x, p.num_q_blocks, p.num_heads_total);
+  int zh, qb;
+
   // Register budget: 384 threads leave 168 per thread.  The producer / MMA warpgroup hands part
   // of its share to the softmax warpgroups, whose threads hold a 128-column row of S.  Each
   // setmaxnreg sits at the top of its warpgroup's own branch.
   if (warp >= 8) {
     reg_dealloc<kFwdRegsIssue>();
-  if (warp == 8) {
-    // =========================== TMA producer (converged warp, elected issue) ==========
-    if (n_max > 0) {
+    if (warp == 8) {
+      // =========================== TMA producer (converged warp, elected issue) ==========
       if (elect_one()) {
         tma_prefetch_desc(&tm_q);
         tma_prefetch_desc(&tm_k);
         tma_prefetch_desc(&tm_v);
-        const uint32_t qbar = smem_u32(&bar_q_full);
-        mbar_arrive_expect_tx(qbar, T::kTilesM * T::kTileBytes);
-#pragma unroll
-        for (int t = 0; t < T::kTilesM; ++t)
-#pragma unroll
-          for (int b = 0; b < T::kBoxes; ++b)
-            tma_load_4d(q_smem + t * T::kTileBytes + b * T::kBoxBytes, &tm_q, qbar, b * 64,
-                        q0 + t * T::kBlockM, h, z);
       }
       __syncwarp();
-      const int n_loads = 2 * n_max;  // K_0, V_0, K_1, V_1, ...
-      for (int it = 0; it < n_loads; ++it) {
-        const int slot = it % T::kStages;
-        const int round = it / T::kStages;
-        if (round > 0 &&
-            !mbar_wait_warp(smem_u32(&bar_kv_empty[slot]), (round - 1) & 1, &abort_word, 1))
-          break;
-        if (elect_one()) {
-          const uint32_t fbar = smem_u32(&bar_kv_full[slot]);
-          mbar_arrive_expect_tx(fbar, T::kTileBytes);
-          const CUtensorMap* tm = (it & 1) ? &tm_v : &tm_k;
-          const int row = (it >> 1) * T::kBlockN;
+      uint32_t kv_it = 0;  // K/V tiles loaded so far (ring slot and phase)
+      bool ok = true;
+      while (ok && work.next(zh, qb)) {
+        const int z = zh / p.heads, h = zh % p.heads;
+        const int q0 = qb * (T::kBlockM * T::kTilesM);
+        int n_kv[2];
+        fwd_item_extent<D>(p, q0, n_kv);
+        const int n_loads = 2 * max(n_kv[0], n_kv[1]);  // K_0, V_0, K_1, V_1, ...
+        for (int it = 0; it < n_loads; ++it, ++kv_it) {
+          const uint32_t slot = kv_it % T::kStages;
+          const uint32_t round = kv_it / T::kStages;
+          if (round > 0 &&
+              !mbar_wait_warp(smem_u32(&bar_kv_empty[slot]), (round - 1) & 1, &abort_word, 2)) {
+            ok = false;
+            break;
+          }
+          if (elect_one()) {
+            const uint32_t fbar = smem_u32(&bar_kv_full[slot]);
+            mbar_arrive_expect_tx(fbar, T::kTileBytes);
+            const CUtensorMap* tm = (it & 1) ? &tm_v : &tm_k;
+            const int row = (it >> 1) * T::kBlockN;
 #pragma unroll
-          for (int b = 0; b < T::kBoxes; ++b)
-            tma_load_4d(ring_smem + slot * T::kTileBytes + b * T::kBoxBytes, tm, fbar, b * 64, row,
-                        h, z);
+            for (int b = 0; b < T::kBoxes; ++b)
+              tma_load_4d(ring_smem + slot * T::kTileBytes + b * T::kBoxBytes, tm, fbar, b * 64,
+                          row, h, z);
+          }
+          __syncwarp();
         }
-        __syncwarp();
       }
-    }
-  } else if (warp == 9) {
-    // =========================== MMA issuer (converged warp, elected issue) ============
-    // All 32 lanes run the loop so that addresses and descriptors live in uniform registers;
-    // a loop run by one lane only makes every operand a per-thread value that has to be moved
-    // to a uniform register before each tcgen05.mma, and the issue rate falls below the
-    // tensor pipe's 64 cycles per 128x128x16 MMA.
-    if (n_max > 0) {
+    } else if (warp == 10) {
+      // =========================== Q producer ===========================
+      // its own warp, so that waiting for the Q buffers of the running item never holds back
+      // the K/V prefetch of the next one
+      uint32_t items = 0;  // items with work seen so far (phase of the Q barriers)
+      bool ok = true;
+      while (ok && work.next(zh, qb)) {
+        const int z = zh / p.heads, h = zh % p.heads;
+        const int q0 = qb * (T::kBlockM * T::kTilesM);
+        int n_kv[2];
+        fwd_item_extent<D>(p, q0, n_kv);
+        if (max(n_kv[0], n_kv[1]) == 0) continue;
+#pragma unroll
+        for (int t = 0; t < T::kTilesM; ++t) {
+          if (items > 0 &&
+              !mbar_wait_warp(smem_u32(&bar_q_free[t]), (items - 1) & 1, &abort_word, 1)) {
+            ok = false;
+            break;
+          }
+          FMHA_TL(2, (int)items * 16 + 13, t);
+          if (elect_one()) {
+            const uint32_t qbar = smem_u32(&bar_q_full[t]);
+            mbar_arrive_expect_tx(qbar, T::kTileBytes);
+#pragma unroll
+            for (int b = 0; b < T::kBoxes; ++b)
+              tma_load_4d(q_smem + t * T::kTileBytes + b * T::kBoxBytes, &tm_q, qbar, b * 64,
+                          q0 + t * T::kBlockM, h, z);
+          }
+          __syncwarp();
+        }
+        ++items;
+        // the next item's Q tiles come cold from HBM (microseconds): start them towards L2 now,
+        // a whole item ahead of the load that needs them
+        {
+          FwdWorkIter peek = work;
+          int zh2, qb2;
+          if (peek.next(zh2, qb2) && elect_one()) {
+#pragma unroll
+            for (int t = 0; t < T::kTilesM; ++t)
+#pragma unroll
+              for (int b = 0; b < T::kBoxes; ++b)
+                tma_prefetch_l2_4d(&tm_q, b * 64, qb2 * (T::kBlockM * T::kTilesM) + t * T::kBlockM,
+                                   zh2 % p.heads, zh2 / p.heads);
+          }
+          __syncwarp();
+        }
+      }
+    } else if (warp == 9) {
+      // =========================== MMA issuer (converged warp, elected issue) ============
+      // All 32 lanes run the loop so that addresses and descriptors live in uniform registers;
+      // a loop run by one lane only makes every operand a per-thread value that has to be moved
+      // to a uniform register before each tcgen05.mma, and the issue rate falls below the
+      // tensor pipe's 64 cycles per 128x128x16 MMA.
       const uint32_t q_lo0 = umma_desc_lo(q_smem, kLboKMajor);
       auto issue_qk = [&](int t, uint32_t k_addr) {
         const uint32_t d = tmem_base + t * 128;
@@ -210,242 +309,296 @@ __global__ void __launch_bounds__(384, 1)
           umma_ts_elect(d, a + ks * 8, b_lo + ((ks * 2048) >> 4), T::kIdescPV,
                         (accumulate || ks > 0) ? 1u : 0u);
       };
-      bool ok = mbar_wait_warp(smem_u32(&bar_q_full), 0, &abort_word, 2);
-      ok = ok && mbar_wait_warp(smem_u32(&bar_kv_full[0]), 0, &abort_word, 3);
-      if (ok) {
-        tc_fence_after();
-#pragma unroll
-        for (int t = 0; t < 2; ++t)
-          if (n_kv[t] > 0) {
-            issue_qk(t, ring_smem);
-            umma_commit_elect(smem_u32(&bar_s_full[t]));
-          }
-        umma_commit_elect(smem_u32(&bar_kv_empty[0]));
-      }
-      for (int j = 0; ok && j < n_max; ++j) {
-        const int it_v = 2 * j + 1;
-        const int slot_v = it_v % T::kStages;
-        if (!mbar_wait_warp(smem_u32(&bar_kv_full[slot_v]), (it_v / T::kStages) & 1, &abort_word,
-                            4)) {
-          ok = false;
-          break;
+      uint32_t items = 0, kv_it = 0;
+      int tl_base = 0;  // timeline slot offset of the current item (debug builds)
+      uint32_t p_cnt[2] = {0, 0};  // P_t tiles consumed so far (phase of p_full[t])
+      uint32_t o_cnt[2] = {0, 0};  // items in which tile t produced an O_t (phase of o_read[t])
+      bool ok = true;
+      // first S_t = Q_t K_0^T of an item (slot0 holds K_0), with the item's bookkeeping
+      auto first_qk = [&](int t, int n_t, uint32_t slot0) {
+        if (n_t > 0) {
+          issue_qk(t, ring_smem + slot0 * T::kTileBytes);
+          umma_commit_elect(smem_u32(&bar_s_full[t]));
         }
-        const bool have_next = (j + 1 < n_max);
-        const int it_k = 2 * j + 2;
-        const int slot_k = it_k % T::kStages;
-        bool k_ready = false;
+        // with at most one KV tile this was the item's last use of Q_t
+        if (n_t <= 1) umma_commit_elect(smem_u32(&bar_q_free[t]));
+      };
+      while (ok && work.next(zh, qb)) {
+        const int q0 = qb * (T::kBlockM * T::kTilesM);
+        int n_kv[2];
+        fwd_item_extent<D>(p, q0, n_kv);
+        const int n_max = max(n_kv[0], n_kv[1]);
+        if (n_max == 0) continue;
+        {
+          const uint32_t slot0 = kv_it % T::kStages;
 #pragma unroll
-        for (int t = 0; t < 2; ++t) {
-          if (j < n_kv[t]) {
-            FMHA_TL(2, j, t * 4 + 0);
-            if (!mbar_wait_warp(smem_u32(&bar_p_full[t]), j & 1, &abort_word, 5)) {
-              ok = false;
-              break;
-            }
+          for (int t = 0; t < 2; ++t) {
+            ok = ok && mbar_wait_warp(smem_u32(&bar_q_full[t]), items & 1, &abort_word, 3) &&
+                 mbar_wait_warp(smem_u32(&bar_kv_full[slot0]), (kv_it / T::kStages) & 1,
+                                &abort_word, 4);
+            if (!ok) break;
             tc_fence_after();
-            FMHA_TL(2, j, t * 4 + 1);
-            issue_pv(t, ring_smem + slot_v * T::kTileBytes, j > 0);
-            FMHA_TL(2, j, t * 4 + 2);
-            if (j + 1 < n_kv[t]) {
-              if (!k_ready) {
-                if (!mbar_wait_warp(smem_u32(&bar_kv_full[slot_k]), (it_k / T::kStages) & 1,
-                                    &abort_word, 6)) {
-                  ok = false;
-                  break;
-                }
-                tc_fence_after();
-                k_ready = true;
-              }
-              issue_qk(t, ring_smem + slot_k * T::kTileBytes);
-              umma_commit_elect(smem_u32(&bar_s_full[t]));
-            } else {
-              umma_commit_elect(smem_u32(&bar_o_full[t]));
-            }
-            FMHA_TL(2, j, t * 4 + 3);
+            first_qk(t, n_kv[t], slot0);
           }
+          if (!ok) break;
+          umma_commit_elect(smem_u32(&bar_kv_empty[slot0]));
         }
-        if (!ok) break;
-        umma_commit_elect(smem_u32(&bar_kv_empty[slot_v]));
-        if (have_next) umma_commit_elect(smem_u32(&bar_kv_empty[slot_k]));
+        for (int j = 0; ok && j < n_max; ++j) {
+          const uint32_t it_v = kv_it + 2 * j + 1;
+          const uint32_t slot_v = it_v % T::kStages;
+          if (!mbar_wait_warp(smem_u32(&bar_kv_full[slot_v]), (it_v / T::kStages) & 1, &abort_word,
+                              5)) {
+            ok = false;
+            break;
+          }
+          const bool have_next = (j + 1 < n_max);
+          const uint32_t it_k = it_v + 1;
+          const uint32_t slot_k = it_k % T::kStages;
+          bool k_ready = false;
+#pragma unroll
+          for (int t = 0; t < 2; ++t) {
+            if (j < n_kv[t]) {
+              FMHA_TL(2, tl_base + j, t * 4 + 0);
+              if (!mbar_wait_warp(smem_u32(&bar_p_full[t]), p_cnt[t] & 1, &abort_word, 6)) {
+                ok = false;
+                break;
+              }
+              ++p_cnt[t];
+              // the first O_t += of an item overwrites O_t: the previous item's epilogue must
+              // have read it out of tensor memory
+              if (j == 0 && o_cnt[t] > 0 &&
+                  !mbar_wait_warp(smem_u32(&bar_o_read[t]), (o_cnt[t] - 1) & 1, &abort_word, 7)) {
+                ok = false;
+                break;
+              }
+              tc_fence_after();
+              FMHA_TL(2, tl_base + j, t * 4 + 1);
+              issue_pv(t, ring_smem + slot_v * T::kTileBytes, j > 0);
+              FMHA_TL(2, tl_base + j, t * 4 + 2);
+              if (j + 1 < n_kv[t]) {
+                if (!k_ready) {
+                  if (!mbar_wait_warp(smem_u32(&bar_kv_full[slot_k]), (it_k / T::kStages) & 1,
+                                      &abort_word, 8)) {
+                    ok = false;
+                    break;
+                  }
+                  tc_fence_after();
+                  k_ready = true;
+                }
+                issue_qk(t, ring_smem + slot_k * T::kTileBytes);
+                umma_commit_elect(smem_u32(&bar_s_full[t]));
+                if (j + 2 == n_kv[t]) umma_commit_elect(smem_u32(&bar_q_free[t]));
+              } else {
+                umma_commit_elect(smem_u32(&bar_o_full[t]));
+                ++o_cnt[t];
+              }
+              FMHA_TL(2, tl_base + j, t * 4 + 3);
+            }
+          }
+          if (!ok) break;
+          umma_commit_elect(smem_u32(&bar_kv_empty[slot_v]));
+          if (have_next) umma_commit_elect(smem_u32(&bar_kv_empty[slot_k]));
+        }
+        kv_it += 2 * n_max;
+        ++items;
+        tl_base += 16;
       }
     }
-  }
   } else {
     // =========================== softmax / epilogue ===========================
     reg_alloc<kFwdRegsSoftmax>();
     const int t = warp >> 2;    // query tile of this warpgroup
     const int quad = warp & 3;  // TMEM lane quadrant of this warp
     const int row_in_tile = quad * 32 + lane;
-    const int row = q0 + t * T::kBlockM + row_in_tile;
     const uint32_t lane_addr = uint32_t(quad * 32) << 16;
     const uint32_t tS = tmem_base + lane_addr + t * 128;
     const uint32_t tO = tmem_base + lane_addr + 256 + t * D;
+    const uint32_t o_stage = ostage_smem + t * T::kTileBytes;
+    bool stored = false;  // a TMA store of this group may still be reading the staging box
     const float c = p.scale_log2;
     // a masked score must give exp2(s * c - m * c) = 0 whatever the sign of c
     const float mask_val = (c >= 0.f) ? -CUDART_INF_F : CUDART_INF_F;
-    long long lim_ll = p.causal ? (long long)row + p.causal_shift : (long long)p.seqlen_k - 1;
-    lim_ll = min(lim_ll, (long long)p.seqlen_k - 1);
-    lim_ll = max(lim_ll, -1ll);
-    const int row_limit = (int)lim_ll;  // last visible key of this row (-1 = none)
-
-    float m_ref = mask_val;  // reference score of the running softmax (raw, unscaled)
-    float l = 0.f;           // running sum of exp2((s - m_ref) * c)
-    const int n = n_kv[t];
-    const bool tile_valid = (q0 + t * T::kBlockM) < p.seqlen_q;
-
     const bool tl = (lane == 0 && quad == 0);
-    for (int j = 0; j < n; ++j) {
-      if (tl) FMHA_TL(t, j, 0);
-      if (!mbar_wait(smem_u32(&bar_s_full[t]), j & 1, &abort_word, 7)) break;
-      tc_fence_after();
-      if (tl) FMHA_TL(t, j, 1);
-      uint32_t s[4][32];
-      tmem_ld32(tS + 0, s[0]);
-      tmem_ld32(tS + 32, s[1]);
-      tmem_ld32(tS + 64, s[2]);
-      tmem_ld32(tS + 96, s[3]);
-      tmem_wait_ld();
-      if (tl) FMHA_TL(t, j, 2);
+    uint32_t s_cnt = 0;   // S_t tiles consumed so far (phase of s_full[t])
+    uint32_t o_cnt = 0;   // O_t tiles read so far (phase of o_full[t])
+    int tl_base = 0;      // timeline slot offset of the current item (debug builds)
 
-      const int lim = row_limit - j * T::kBlockN;  // columns > lim of this tile are masked
-      if (lim < T::kBlockN - 1) {
-#pragma unroll
-        for (int cc = 0; cc < 4; ++cc)
-#pragma unroll
-          for (int i = 0; i < 32; ++i)
-            if (cc * 32 + i > lim) s[cc][i] = __float_as_uint(mask_val);
-      }
+    while (work.next(zh, qb)) {
+      const int z = zh / p.heads, h = zh % p.heads;
+      const int q0 = qb * (T::kBlockM * T::kTilesM);
+      int n_kv[2];
+      fwd_item_extent<D>(p, q0, n_kv);
+      const int n = n_kv[t];
+      const bool tile_valid = (q0 + t * T::kBlockM) < p.seqlen_q;
+      const int row = q0 + t * T::kBlockM + row_in_tile;
+      long long lim_ll = p.causal ? (long long)row + p.causal_shift : (long long)p.seqlen_k - 1;
+      lim_ll = min(lim_ll, (long long)p.seqlen_k - 1);
+      lim_ll = max(lim_ll, -1ll);
+      const int row_limit = (int)lim_ll;  // last visible key of this row (-1 = none)
 
-      // row extreme: max of s when c >= 0, min when c < 0, so that m * c = max(s * c)
-      float mx0 = __uint_as_float(s[0][0]), mx1 = __uint_as_float(s[1][0]);
-      float mx2 = __uint_as_float(s[2][0]), mx3 = __uint_as_float(s[3][0]);
-      if (c >= 0.f) {
+      float m_ref = mask_val;  // reference score of the running softmax (raw, unscaled)
+      float l = 0.f;           // running sum of exp2((s - m_ref) * c)
+
+      for (int j = 0; j < n; ++j, ++s_cnt) {
+        if (tl) FMHA_TL(t, tl_base + j, 0);
+        // on a time-out keep going: every later wait returns at once, and all 128 threads of
+        // the group still meet at the named barriers of the epilogue
+        mbar_wait(smem_u32(&bar_s_full[t]), s_cnt & 1, &abort_word, 9);
+        tc_fence_after();
+        if (tl) FMHA_TL(t, tl_base + j, 1);
+        uint32_t s[4][32];
+        tmem_ld32(tS + 0, s[0]);
+        tmem_ld32(tS + 32, s[1]);
+        tmem_ld32(tS + 64, s[2]);
+        tmem_ld32(tS + 96, s[3]);
+        tmem_wait_ld();
+        if (tl) FMHA_TL(t, tl_base + j, 2);
+
+        const int lim = row_limit - j * T::kBlockN;  // columns > lim of this tile are masked
+        if (lim < T::kBlockN - 1) {
 #pragma unroll
-        for (int i = 1; i < 32; ++i) {
-          mx0 = fmaxf(mx0, __uint_as_float(s[0][i]));
-          mx1 = fmaxf(mx1, __uint_as_float(s[1][i]));
-          mx2 = fmaxf(mx2, __uint_as_float(s[2][i]));
-          mx3 = fmaxf(mx3, __uint_as_float(s[3][i]));
+          for (int cc = 0; cc < 4; ++cc)
+#pragma unroll
+            for (int i = 0; i < 32; ++i)
+              if (cc * 32 + i > lim) s[cc][i] = __float_as_uint(mask_val);
         }
-      } else {
-#pragma unroll
-        for (int i = 1; i < 32; ++i) {
-          mx0 = fminf(mx0, __uint_as_float(s[0][i]));
-          mx1 = fminf(mx1, __uint_as_float(s[1][i]));
-          mx2 = fminf(mx2, __uint_as_float(s[2][i]));
-          mx3 = fminf(mx3, __uint_as_float(s[3][i]));
-        }
-      }
-      float mx = (c >= 0.f) ? fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3))
-                            : fminf(fminf(mx0, mx1), fminf(mx2, mx3));
-      if (FMHA_ABLATE & 2) mx = __uint_as_float(s[0][0]);
 
-      if (j == 0) {
-        m_ref = mx;
-      } else {
-        const float m_new = (c >= 0.f) ? fmaxf(m_ref, mx) : fminf(m_ref, mx);
-        // growth of the scaled maximum; NaN (inf - inf) compares false
-        const bool need = (m_new - m_ref) * c > kRescaleThreshold;
-        if (__any_sync(0xffffffffu, need)) {
-          // O_t is idle here: S_t(j) is committed after O_t += P_t V_(j-1) was issued
-          const float alpha = isinf(m_new) ? 1.f : fast_exp2((m_ref - m_new) * c);
-          l *= alpha;
-          m_ref = m_new;
+        // row extreme: max of s when c >= 0, min when c < 0, so that m * c = max(s * c)
+        float mx0 = __uint_as_float(s[0][0]), mx1 = __uint_as_float(s[1][0]);
+        float mx2 = __uint_as_float(s[2][0]), mx3 = __uint_as_float(s[3][0]);
+        if (c >= 0.f) {
 #pragma unroll
-          for (int cc = 0; cc < D / 32; ++cc) {
-            uint32_t o[32];
-            tmem_ld32(tO + cc * 32, o);
-            tmem_wait_ld();
-#pragma unroll
-            for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
-            tmem_st32(tO + cc * 32, o);
+          for (int i = 1; i < 32; ++i) {
+            mx0 = fmaxf(mx0, __uint_as_float(s[0][i]));
+            mx1 = fmaxf(mx1, __uint_as_float(s[1][i]));
+            mx2 = fmaxf(mx2, __uint_as_float(s[2][i]));
+            mx3 = fmaxf(mx3, __uint_as_float(s[3][i]));
           }
-        }
-      }
-
-      if (tl) FMHA_TL(t, j, 3);
-      const float neg_mc = isinf(m_ref) ? 0.f : -m_ref * c;
-      float l0 = 0.f, l1 = 0.f, l2 = 0.f, l3 = 0.f;
-#pragma unroll
-      for (int hf = 0; hf < 2; ++hf) {  // 64 scores -> 32 packed columns of P at a time
-        uint32_t pk[32];
-#pragma unroll
-        for (int c2 = 0; c2 < 2; ++c2) {
-          const int cc = hf * 2 + c2;
-#pragma unroll
-          for (int i = 0; i < 32; i += 4) {
-            const float p0 = fast_exp2(fmaf(__uint_as_float(s[cc][i + 0]), c, neg_mc));
-            const float p1 = fast_exp2(fmaf(__uint_as_float(s[cc][i + 1]), c, neg_mc));
-            const float p2 = fast_exp2(fmaf(__uint_as_float(s[cc][i + 2]), c, neg_mc));
-            const float p3 = fast_exp2(fmaf(__uint_as_float(s[cc][i + 3]), c, neg_mc));
-            l0 += p0;
-            l1 += p1;
-            l2 += p2;
-            l3 += p3;
-            pk[c2 * 16 + (i >> 1) + 0] = pack_half2(p0, p1);
-            pk[c2 * 16 + (i >> 1) + 1] = pack_half2(p2, p3);
-          }
-        }
-        if (!(FMHA_ABLATE & 4)) tmem_st32(tS + hf * 32, pk);
-      }
-      l += (l0 + l1) + (l2 + l3);
-      if (tl) FMHA_TL(t, j, 4);
-      tmem_wait_st();
-      tc_fence_before();
-      mbar_arrive(smem_u32(&bar_p_full[t]));
-      if (tl) FMHA_TL(t, j, 5);
-    }
-    if (tl) FMHA_TL(t, 31, 0);
-
-    // ---- epilogue: O_t / l -> fp16 -> shared memory (over Q_t) -> TMA store; LSE
-    if (tile_valid) {
-      if (n > 0) mbar_wait(smem_u32(&bar_o_full[t]), 0, &abort_word, 8);
-      tc_fence_after();
-      const float inv_l = (l > 0.f) ? 1.f / l : 0.f;
-      const uint32_t o_smem = q_smem + t * T::kTileBytes;
-#pragma unroll
-      for (int cc = 0; cc < D / 32; ++cc) {
-        uint32_t o[32];
-        if (n > 0) {
-          tmem_ld32(tO + cc * 32, o);
-          tmem_wait_ld();
         } else {
 #pragma unroll
-          for (int i = 0; i < 32; ++i) o[i] = 0u;
+          for (int i = 1; i < 32; ++i) {
+            mx0 = fminf(mx0, __uint_as_float(s[0][i]));
+            mx1 = fminf(mx1, __uint_as_float(s[1][i]));
+            mx2 = fminf(mx2, __uint_as_float(s[2][i]));
+            mx3 = fminf(mx3, __uint_as_float(s[3][i]));
+          }
         }
+        float mx = (c >= 0.f) ? fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3))
+                              : fminf(fminf(mx0, mx1), fminf(mx2, mx3));
+        if (FMHA_ABLATE & 2) mx = __uint_as_float(s[0][0]);
+
+        if (j == 0) {
+          m_ref = mx;
+        } else {
+          const float m_new = (c >= 0.f) ? fmaxf(m_ref, mx) : fminf(m_ref, mx);
+          // growth of the scaled maximum; NaN (inf - inf) compares false
+          const bool need = (m_new - m_ref) * c > kRescaleThreshold;
+          if (__any_sync(0xffffffffu, need)) {
+            // O_t is idle here: S_t(j) is committed after O_t += P_t V_(j-1) was issued
+            const float alpha = isinf(m_new) ? 1.f : fast_exp2((m_ref - m_new) * c);
+            l *= alpha;
+            m_ref = m_new;
 #pragma unroll
-        for (int qd = 0; qd < 4; ++qd) {
-          const int ch = cc * 4 + qd;  // 16-byte chunk (8 fp16) of the row
-          const uint32_t addr = o_smem + (ch >> 3) * T::kBoxBytes + row_in_tile * 128 +
-                                (((ch & 7) ^ (row_in_tile & 7)) << 4);
-          const uint32_t w0 = pack_half2(__uint_as_float(o[qd * 8 + 0]) * inv_l,
-                                         __uint_as_float(o[qd * 8 + 1]) * inv_l);
-          const uint32_t w1 = pack_half2(__uint_as_float(o[qd * 8 + 2]) * inv_l,
-                                         __uint_as_float(o[qd * 8 + 3]) * inv_l);
-          const uint32_t w2 = pack_half2(__uint_as_float(o[qd * 8 + 4]) * inv_l,
-                                         __uint_as_float(o[qd * 8 + 5]) * inv_l);
-          const uint32_t w3 = pack_half2(__uint_as_float(o[qd * 8 + 6]) * inv_l,
-                                         __uint_as_float(o[qd * 8 + 7]) * inv_l);
-          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(w0), "r"(w1),
-                       "r"(w2), "r"(w3)
-                       : "memory");
+            for (int cc = 0; cc < D / 32; ++cc) {
+              uint32_t o[32];
+              tmem_ld32(tO + cc * 32, o);
+              tmem_wait_ld();
+#pragma unroll
+              for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+              tmem_st32(tO + cc * 32, o);
+            }
+          }
         }
-      }
-      if (row < p.seqlen_q) {
-        const float lse = (l > 0.f) ? (m_ref * c + log2f(l)) * 0.6931471805599453f : -CUDART_INF_F;
-        p.lse[((size_t)z * p.heads + h) * p.seqlen_q + row] = lse;
-      }
-      fence_proxy_async_smem();
-      named_bar_sync(1 + t, 128);
-      if (row_in_tile == 0) {
+
+        if (tl) FMHA_TL(t, tl_base + j, 3);
+        const float neg_mc = isinf(m_ref) ? 0.f : -m_ref * c;
+        float l0 = 0.f, l1 = 0.f, l2 = 0.f, l3 = 0.f;
 #pragma unroll
-        for (int b = 0; b < T::kBoxes; ++b)
-          tma_store_4d(&tm_o, o_smem + b * T::kBoxBytes, b * 64, q0 + t * T::kBlockM, h, z);
-        tma_commit_group();
-        tma_wait_group<0>();
+        for (int hf = 0; hf < 2; ++hf) {  // 64 scores -> 32 packed columns of P at a time
+          uint32_t pk[32];
+#pragma unroll
+          for (int c2 = 0; c2 < 2; ++c2) {
+            const int cc = hf * 2 + c2;
+#pragma unroll
+            for (int i = 0; i < 32; i += 4) {
+              const float p0 = fast_exp2(fmaf(__uint_as_float(s[cc][i + 0]), c, neg_mc));
+              const float p1 = fast_exp2(fmaf(__uint_as_float(s[cc][i + 1]), c, neg_mc));
+              const float p2 = fast_exp2(fmaf(__uint_as_float(s[cc][i + 2]), c, neg_mc));
+              const float p3 = fast_exp2(fmaf(__uint_as_float(s[cc][i + 3]), c, neg_mc));
+              l0 += p0;
+              l1 += p1;
+              l2 += p2;
+              l3 += p3;
+              pk[c2 * 16 + (i >> 1) + 0] = pack_half2(p0, p1);
+              pk[c2 * 16 + (i >> 1) + 1] = pack_half2(p2, p3);
+            }
+          }
+          if (!(FMHA_ABLATE & 4)) tmem_st32(tS + hf * 32, pk);
+        }
+        l += (l0 + l1) + (l2 + l3);
+        if (tl) FMHA_TL(t, tl_base + j, 4);
+        tmem_wait_st();
+        tc_fence_before();
+        mbar_arrive(smem_u32(&bar_p_full[t]));
+        if (tl) FMHA_TL(t, tl_base + j, 5);
       }
-      if (tl) FMHA_TL(t, 31, 1);
+      if (tl) FMHA_TL(t, tl_base + 15, 6);
+
+      // ---- epilogue: O_t / l -> fp16 registers (tensor memory released) -> staging box -> TMA
+      //      store; LSE
+      if (tile_valid) {
+        uint32_t oh[D / 2];  // the output row, fp16 pairs
+        if (n > 0) {
+          mbar_wait(smem_u32(&bar_o_full[t]), o_cnt & 1, &abort_word, 10);
+          ++o_cnt;
+          tc_fence_after();
+          if (tl) FMHA_TL(t, tl_base + 15, 8);
+          const float inv_l = (l > 0.f) ? 1.f / l : 0.f;
+          uint32_t o[D / 32][32];
+#pragma unroll
+          for (int cc = 0; cc < D / 32; ++cc) tmem_ld32(tO + cc * 32, o[cc]);
+          tmem_wait_ld();
+          tc_fence_before();
+          mbar_arrive(smem_u32(&bar_o_read[t]));
+          if (tl) FMHA_TL(t, tl_base + 15, 9);
+#pragma unroll
+          for (int cc = 0; cc < D / 32; ++cc)
+#pragma unroll
+            for (int i = 0; i < 32; i += 2)
+              oh[cc * 16 + (i >> 1)] = pack_half2(__uint_as_float(o[cc][i]) * inv_l,
+                                                  __uint_as_float(o[cc][i + 1]) * inv_l);
+        } else {
+#pragma unroll
+          for (int i = 0; i < D / 2; ++i) oh[i] = 0u;
+        }
+        if (row < p.seqlen_q) {
+          const float lse =
+              (l > 0.f) ? (m_ref * c + log2f(l)) * 0.6931471805599453f : -CUDART_INF_F;
+          p.lse[((size_t)z * p.heads + h) * p.seqlen_q + row] = lse;
+        }
+        // through this group's staging tile and TMA stores (per-thread stores of whole rows are
+        // uncoalesced and clog the load/store pipe for everybody)
+        if (row_in_tile == 0 && stored) tma_wait_group_read<0>();  // previous item's store
+        named_bar_sync(1 + t, 128);
+#pragma unroll
+        for (int ch = 0; ch < D / 8; ++ch)  // 16-byte chunk (8 fp16) of this row
+          sts128(o_stage + (ch >> 3) * T::kBoxBytes + row_in_tile * 128 +
+                     (((ch & 7) ^ (row_in_tile & 7)) << 4),
+                 oh[ch * 4 + 0], oh[ch * 4 + 1], oh[ch * 4 + 2], oh[ch * 4 + 3]);
+        fence_proxy_async_smem();
+        named_bar_sync(1 + t, 128);
+        if (row_in_tile == 0) {
+#pragma unroll
+          for (int b = 0; b < T::kBoxes; ++b)
+            tma_store_4d(&tm_o, o_stage + b * T::kBoxBytes, b * 64, q0 + t * T::kBlockM, h, z);
+          tma_commit_group();
+        }
+        stored = true;
+      }
+      if (tl) FMHA_TL(t, tl_base + 15, 7);
+      tl_base += 16;
     }
+    if (row_in_tile == 0) tma_wait_group<0>();
   }
 
   // ---- teardown

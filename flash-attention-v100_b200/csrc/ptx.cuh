@@ -142,6 +142,12 @@ template <int N>
 __device__ __forceinline__ void tma_wait_group() {
   asm volatile("cp.async.bulk.wait_group %0;" ::"n"(N) : "memory");
 }
+// bring a tile into L2 only (no shared-memory destination, nothing to wait for)
+__device__ __forceinline__ void tma_prefetch_l2_4d(const void* tmap, int c0, int c1, int c2, int c3) {
+  asm volatile("cp.async.bulk.prefetch.tensor.4d.L2.global.tile [%0, {%1, %2, %3, %4}];" ::"l"(tmap),
+               "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+               : "memory");
+}
 __device__ __forceinline__ void tma_prefetch_desc(const void* tmap) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(tmap) : "memory");
 }
@@ -346,6 +352,14 @@ __device__ __forceinline__ uint32_t mul_half2(uint32_t a, uint32_t b) {
   uint32_t y;
   asm("mul.rn.f16x2 %0, %1, %2;" : "=r"(y) : "r"(a), "r"(b));
   return y;
+}
+__device__ __forceinline__ uint32_t add_half2(uint32_t a, uint32_t b) {
+  uint32_t y;
+  asm("add.rn.f16x2 %0, %1, %2;" : "=r"(y) : "r"(a), "r"(b));
+  return y;
+}
+__device__ __forceinline__ float2 half2_to_float2(uint32_t a) {
+  return __half22float2(*reinterpret_cast<const __half2*>(&a));
 }
 __device__ __forceinline__ uint32_t fma_half2(uint32_t a, uint32_t b, uint32_t c) {
   uint32_t y;
