@@ -20,7 +20,7 @@
 //   warps 0-3, 4-7  two compute groups: one thread per KV row, group g owns query columns
 //                   [64g, 64g+64) of the tile: P^T = exp2(S^T*c - lse2) (two exp2 per MUFU op,
 //                   fp16) and dS^T = P^T o (dP^T - D)
-//   warps 8-11      dQ group: one thread per query row; tensor memory -> registers -> per-warp
+//   warps 8-11      dQ group: one thread per query row; tensor memory -> registers ->
 //                   shared-memory staging -> TMA reduce-add into the fp32 dQ accumulator
 //                   (bulk async adds: no per-thread atomics in the load/store pipeline)
 //   warp 12         TMA producer (K, V once; Q_i through a 2-stage ring, dO_i single stage)
@@ -43,6 +43,7 @@ struct BwdKernelParams {
   const float* delta;   // fp32 (Z*H, seqlen_q_pad)
   float* dk_accum;      // optional fp32 (Z, seqlen_k, H, D) contiguous
   float* dv_accum;      // optional
+  long long accum_batch_stride;  // elements between batch entries of dk_accum / dv_accum
   int heads, seqlen_q, seqlen_k, seqlen_q_pad;
   int num_kv_blocks;    // ceil(seqlen_k / 128)
   float scale, scale_log2;
@@ -55,6 +56,8 @@ struct BwdKernelParams {
 constexpr int kBwdRegsIssue = 80;     // warps 12-15
 constexpr int kBwdRegsCompute = 120;  // warps 0-7
 constexpr int kBwdRegsDq = 128 + (128 - kBwdRegsIssue) + 2 * (128 - kBwdRegsCompute);  // warps 8-11
+static_assert(kBwdRegsIssue <= 128 && kBwdRegsCompute <= 128 && kBwdRegsDq >= 128,
+              "setmaxnreg.dec must not raise and .inc must not lower the 128 registers of the launch");
 
 template <int D>
 struct BwdTraits {
@@ -64,7 +67,7 @@ struct BwdTraits {
   static constexpr int kTileBytes = kBoxes * kBoxBytes;  // a 128 x D fp16 tile
   static constexpr int kDsBytes = 2 * kBoxBytes;         // dS^T: 128 x 128 fp16
   static constexpr int kQStages = 2;
-  static constexpr int kStageBytes = 4 * 2 * 4096;       // dQ staging: 2 x (32 x 32 fp32) per warp
+  static constexpr int kStageBytes = 2 * 16384;          // dQ staging: 2 x (128 rows x 32 fp32)
   static constexpr int kStatBytes = 256 * 4;             // lse2[128] + delta[128] of one tile
   static constexpr int kThreads = 512;  // 4 warpgroups; warps 14, 15 only take part in barriers
   // K, V, Q x2, dO, dS^T, dQ staging, statistics
@@ -110,7 +113,7 @@ __global__ void __launch_bounds__(512, 1)
   const uint32_t q_smem = v_smem + T::kTileBytes;                   // kQStages tiles
   const uint32_t do_smem = q_smem + T::kQStages * T::kTileBytes;    // one tile
   const uint32_t ds_smem = do_smem + T::kTileBytes;                 // dS^T
-  const uint32_t stg_smem = ds_smem + T::kDsBytes;                  // dQ staging, 2 x 4 KB per warp
+  const uint32_t stg_smem = ds_smem + T::kDsBytes;                  // dQ staging, 2 x 16 KB
   const uint32_t stat_smem = stg_smem + T::kStageBytes;             // statistics
 
   // ---- coordinates: consecutive CTAs = same head; early KV tiles (most query tiles) first
@@ -421,11 +424,8 @@ __global__ void __launch_bounds__(512, 1)
       // =========================== dQ group ===========================
       reg_alloc<kBwdRegsDq>();
       const uint32_t tDQ = tmem_base + lane_addr + T::kColDQ;
-      const uint32_t stage = stg_smem + quad * 8192;
-      const uint32_t my_row = stage + lane * 128;
       const bool tl = (r == 0);
       for (int n = 0; n < cnt; ++n) {
-        const int q0w = (i_begin + n) * T::kBlock + quad * 32;  // first query row of this warp
         if (tl) FMHA_TL(1, n, 0);
         if (!mbar_wait(smem_u32(&bar_dq_full), n & 1, &abort_word, 14)) break;
         tc_fence_after();
@@ -441,25 +441,29 @@ __global__ void __launch_bounds__(512, 1)
         if (tl) FMHA_TL(1, n, 2);
 #pragma unroll
         for (int cc = 0; cc < D / 32; ++cc) {
-          // buffer (cc & 1) was last used two reduce-adds ago: at most one group may still read
-          if (lane == 0) tma_wait_group_read<1>();
-          __syncwarp();
-          const uint32_t buf_row = my_row + (cc & 1) * 4096;
+          // One reduce-add per 32-column chunk for the whole 128-row tile (16 KB): few large
+          // bulk operations instead of many small ones.  Buffer (cc & 1) was last used two
+          // reduce-adds ago: at most one group may still be reading.
+          if (r == 0) tma_wait_group_read<1>();
+          named_bar_sync(2, 128);
+          const uint32_t buf_row = stg_smem + (cc & 1) * 16384 + r * 128;
 #pragma unroll
           for (int k4 = 0; k4 < 8; ++k4)
-            sts128(buf_row + ((k4 ^ (lane & 7)) << 4), acc[cc][k4 * 4 + 0], acc[cc][k4 * 4 + 1],
+            sts128(buf_row + ((k4 ^ (r & 7)) << 4), acc[cc][k4 * 4 + 0], acc[cc][k4 * 4 + 1],
                    acc[cc][k4 * 4 + 2], acc[cc][k4 * 4 + 3]);
           fence_proxy_async_smem();
-          __syncwarp();
-          if (lane == 0) {
-            tma_reduce_add_4d(&tm_dqacc, stage + (cc & 1) * 4096, cc * 32, q0w, h, z);
+          named_bar_sync(2, 128);
+          if (r == 0) {
+            tma_reduce_add_4d(&tm_dqacc, stg_smem + (cc & 1) * 16384, cc * 32,
+                              (i_begin + n) * T::kBlock, h, z);
             tma_commit_group();
           }
         }
         if (tl) FMHA_TL(1, n, 3);
       }
-      if (lane == 0) tma_wait_group<0>();
-      __syncwarp();
+      if (r == 0) tma_wait_group<0>();
+      named_bar_sync(2, 128);  // the staging area is idle again (the dV epilogue reuses nothing of it,
+                               // but the group leaves its loop together)
     }
 
     // ============ epilogue: dK (warps 0-3), dV (warps 8-11); warps 4-7 are done ============
@@ -474,7 +478,7 @@ __global__ void __launch_bounds__(512, 1)
       if (accum != nullptr) {
         // ring attention: add this block's contribution into the travelling fp32 buffer
         if (cnt > 0 && kvi < p.seqlen_k) {
-          float* dst = accum + (((size_t)z * p.seqlen_k + kvi) * p.heads + h) * D;
+          float* dst = accum + (size_t)z * p.accum_batch_stride + ((size_t)kvi * p.heads + h) * D;
 #pragma unroll
           for (int cc = 0; cc < D / 32; ++cc) {
             uint32_t a[32];

@@ -58,14 +58,14 @@ int make_tensor_map(CUtensorMap* map, const void* base, int Z, int N, int H, int
   return r == CUDA_SUCCESS ? FMHA_OK : FMHA_ERR_TENSOR_MAP;
 }
 
-// fp32 dQ accumulator (Z, N, H, D) contiguous -> 4-D map, box 32 x 32 x 1 x 1 (one warp's 32 query
+// fp32 dQ accumulator (Z, N, H, D) contiguous -> 4-D map, box 32 x 128 x 1 x 1 (a tile's 128 query
 // rows x 32 columns = 128-byte rows), 128-byte swizzle; used by TMA reduce-add
 int make_accum_map(CUtensorMap* map, float* base, int Z, int N, int H, int D) {
   EncodeTiledFn encode = get_encode_fn();
   if (encode == nullptr) return FMHA_ERR_NO_DEVICE;
   const cuuint64_t dims[4] = {(cuuint64_t)D, (cuuint64_t)N, (cuuint64_t)H, (cuuint64_t)Z};
   const cuuint64_t strides[3] = {(cuuint64_t)H * D * 4, (cuuint64_t)D * 4, (cuuint64_t)N * H * D * 4};
-  const cuuint32_t box[4] = {32, 32, 1, 1};
+  const cuuint32_t box[4] = {32, 128, 1, 1};
   const cuuint32_t estr[4] = {1, 1, 1, 1};
   const CUresult r = encode(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, base, dims, strides, box, estr,
                             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
@@ -197,6 +197,8 @@ int launch_bwd(const FmhaBwdParams* p, const BwdWorkspace& w, cudaStream_t strea
     kp.delta = w.delta;
     kp.dk_accum = p->dk_accum;
     kp.dv_accum = p->dv_accum;
+    kp.accum_batch_stride =
+        p->accum_batch_stride > 0 ? p->accum_batch_stride : (long long)Nk * H * D;
     kp.heads = H;
     kp.seqlen_q = Nq;
     kp.seqlen_k = Nk;
@@ -296,6 +298,29 @@ int fmha_bwd(const FmhaBwdParams* p, void* workspace, size_t workspace_bytes, vo
   if (!aligned16(workspace)) return FMHA_ERR_BAD_ALIGNMENT;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   return p->head_dim == 128 ? launch_bwd<128>(p, w, s) : launch_bwd<64>(p, w, s);
+}
+
+int fmha_bwd_convert_dq(const void* workspace, void* dq, FmhaStrides dq_strides, int32_t batch,
+                        int32_t heads, int32_t seqlen_q, int32_t head_dim, float scale,
+                        void* stream) {
+  if (workspace == nullptr || dq == nullptr) return FMHA_ERR_NULL_POINTER;
+  if (head_dim != 64 && head_dim != 128) return FMHA_ERR_BAD_HEAD_DIM;
+  if (batch <= 0 || heads <= 0 || seqlen_q <= 0) return FMHA_ERR_BAD_SHAPE;
+  if (!aligned16(workspace) || !aligned16(dq)) return FMHA_ERR_BAD_ALIGNMENT;
+  int rc = check_strides(dq_strides, seqlen_q, heads, batch);
+  if (rc) return rc;
+  const long long rows = (long long)batch * seqlen_q * heads;
+  const int rows_per_block = 256 / (head_dim / 8);
+  const unsigned grid = (unsigned)((rows + rows_per_block - 1) / rows_per_block);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const float* acc = static_cast<const float*>(workspace);
+  if (head_dim == 128)
+    fmha::fmha_bwd_convert_dq_kernel<128><<<grid, 256, 0, s>>>(acc, static_cast<__half*>(dq),
+                                                               to3(dq_strides), heads, seqlen_q, scale, rows);
+  else
+    fmha::fmha_bwd_convert_dq_kernel<64><<<grid, 256, 0, s>>>(acc, static_cast<__half*>(dq),
+                                                              to3(dq_strides), heads, seqlen_q, scale, rows);
+  return cudaGetLastError() == cudaSuccess ? FMHA_OK : FMHA_ERR_LAUNCH;
 }
 
 int fmha_merge(float* o_acc, float* lse_acc, const void* o_part, FmhaStrides o_part_strides,

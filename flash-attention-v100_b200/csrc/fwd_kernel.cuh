@@ -77,6 +77,8 @@ struct FwdTraits {
 
 constexpr int kFwdRegsIssue = 88;                                 // warps 8-11
 constexpr int kFwdRegsSoftmax = 168 + (168 - kFwdRegsIssue) / 2;  // warps 0-7: 208
+static_assert(kFwdRegsIssue <= 168 && kFwdRegsSoftmax >= 168 && kFwdRegsSoftmax % 8 == 0,
+              "setmaxnreg.dec must not raise and .inc must not lower the 168 registers of the launch");
 
 // lazy rescale threshold in the log2 domain: P may grow to 2^8 before O is rescaled
 constexpr float kRescaleThreshold = 8.0f;

@@ -24,7 +24,7 @@ FMHA_BWD_KEEP_WORKSPACE = 1
 FMHA_BWD_SKIP_DQ_CONVERT = 2
 
 EXPORTED_SYMBOLS = (
-    "fmha_fwd", "fmha_bwd_workspace_bytes", "fmha_bwd", "fmha_merge", "fmha_b200_forward",
+    "fmha_fwd", "fmha_bwd_workspace_bytes", "fmha_bwd", "fmha_bwd_convert_dq", "fmha_merge", "fmha_b200_forward",
     "fmha_b200_backward", "fmha_status_string", "fmha_version",
 )
 
@@ -52,6 +52,7 @@ class FmhaBwdParams(ctypes.Structure):
         ("o", ctypes.c_void_p), ("dout", ctypes.c_void_p), ("lse", ctypes.c_void_p),
         ("dq", ctypes.c_void_p), ("dk", ctypes.c_void_p), ("dv", ctypes.c_void_p),
         ("dk_accum", ctypes.c_void_p), ("dv_accum", ctypes.c_void_p),
+        ("accum_batch_stride", ctypes.c_int64),
         ("q_strides", FmhaStrides), ("k_strides", FmhaStrides), ("v_strides", FmhaStrides),
         ("o_strides", FmhaStrides), ("dout_strides", FmhaStrides),
         ("dq_strides", FmhaStrides), ("dk_strides", FmhaStrides), ("dv_strides", FmhaStrides),
@@ -82,6 +83,10 @@ def load_library() -> ctypes.CDLL:
     lib.fmha_bwd.restype = ctypes.c_int
     lib.fmha_bwd.argtypes = [ctypes.POINTER(FmhaBwdParams), ctypes.c_void_p, ctypes.c_size_t,
                              ctypes.c_void_p]
+    lib.fmha_bwd_convert_dq.restype = ctypes.c_int
+    lib.fmha_bwd_convert_dq.argtypes = [ctypes.c_void_p, ctypes.c_void_p, FmhaStrides, ctypes.c_int32,
+                                        ctypes.c_int32, ctypes.c_int32, ctypes.c_int32, ctypes.c_float,
+                                        ctypes.c_void_p]
     lib.fmha_merge.restype = ctypes.c_int
     lib.fmha_merge.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, FmhaStrides,
                                ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int32, ctypes.c_int32,
@@ -172,6 +177,13 @@ def bwd_params(q, k, v, o, dout, lse, dq, dk, dv, scale, causal, causal_shift=0,
     p.dv = None if dv is None else dv.data_ptr()
     p.dk_accum = None if dk_accum is None else dk_accum.data_ptr()
     p.dv_accum = None if dv_accum is None else dv_accum.data_ptr()
+    for acc in (dk_accum, dv_accum):
+        if acc is not None:
+            # (Z, N, H, D) fp32 with dense rows and heads; the batch stride is free
+            if acc.dtype != torch.float32 or acc.stride(3) != 1 or acc.stride(2) != acc.shape[3] or \
+                    acc.stride(1) != acc.shape[2] * acc.shape[3]:
+                raise RuntimeError("dk_accum / dv_accum must be fp32 (Z, N, H, D) with dense rows and heads")
+            p.accum_batch_stride = acc.stride(0)
     p.q_strides, p.k_strides, p.v_strides = _strides(q), _strides(k), _strides(v)
     p.dout_strides = _strides(dout)
     if o is not None:
@@ -220,6 +232,16 @@ def bwd(q, k, v, o, dout, lse, scale: float, causal: bool = False, causal_shift:
                                        workspace.numel() * workspace.element_size(),
                                        _stream(stream)), "fmha_bwd")
     return dq, dk, dv
+
+
+def bwd_convert_dq(workspace, dq, scale: float, stream=None):
+    """dq (fp16, strided) = scale * the fp32 dQ accumulator at the start of ``workspace``."""
+    Z, N, H, D = dq.shape
+    with torch.cuda.device(dq.device):
+        _check(load_library().fmha_bwd_convert_dq(ctypes.c_void_p(workspace.data_ptr()), _ptr(dq),
+                                                  _strides(dq), Z, H, N, D, float(scale),
+                                                  _stream(stream)), "fmha_bwd_convert_dq")
+    return dq
 
 
 def merge(o_acc, lse_acc, o_part, lse_part, o_out=None, stream=None):

@@ -82,8 +82,12 @@ typedef struct {
   void* dq;         /* (Z, seqlen_q, H, D) fp16, written */
   void* dk;         /* (Z, seqlen_k, H, D) fp16, written (may be NULL if dk_accum is set) */
   void* dv;         /* (Z, seqlen_k, H, D) fp16, written (may be NULL if dv_accum is set) */
-  float* dk_accum;  /* optional fp32 (Z, seqlen_k, H, D) contiguous: dK is ADDED into it */
-  float* dv_accum;  /* optional fp32 (Z, seqlen_k, H, D) contiguous: dV is ADDED into it */
+  float* dk_accum;  /* optional fp32 (Z, seqlen_k, H, D): dK is ADDED into it */
+  float* dv_accum;  /* optional fp32 (Z, seqlen_k, H, D): dV is ADDED into it */
+  /* element stride between batch entries of dk_accum / dv_accum; 0 = dense
+   * (seqlen_k * H * D).  Rows and heads are dense.  Lets a row range of a larger buffer be
+   * the target (ring attention adds into the first half of a travelling block). */
+  int64_t accum_batch_stride;
   FmhaStrides q_strides, k_strides, v_strides, o_strides, dout_strides;
   FmhaStrides dq_strides, dk_strides, dv_strides;
   int32_t batch, heads, seqlen_q, seqlen_k, head_dim;
@@ -117,6 +121,14 @@ size_t fmha_bwd_workspace_bytes(const FmhaBwdParams* p);
  * together with the D computation of flash_attn_v100/flash_attn_interface.py:43-44 and the
  * zero-fill of :84. */
 int fmha_bwd(const FmhaBwdParams* p, void* workspace, size_t workspace_bytes, void* stream);
+
+/* dQ = fp16(scale * accumulator) from a backward workspace, for callers that ran fmha_bwd with
+ * FMHA_BWD_SKIP_DQ_CONVERT (several calls accumulating into one workspace).  The sizes must be
+ * those the workspace was used with.  Replaces the reference's in-place fp16 atomics
+ * (kernel/fused_mha_kernel.cu:543,693). */
+int fmha_bwd_convert_dq(const void* workspace, void* dq, FmhaStrides dq_strides, int32_t batch,
+                        int32_t heads, int32_t seqlen_q, int32_t head_dim, float scale,
+                        void* stream);
 
 /* Ring-attention merge of a partial result into running fp32 accumulators, in place:
  *   lse' = logaddexp(lse_acc, lse_part);  o_acc = e^(lse_acc-lse') o_acc + e^(lse_part-lse') o_part
