@@ -7,6 +7,7 @@
 #include <cuda_runtime.h>
 
 #include <algorithm>
+#include <atomic>
 #include <cmath>
 #include <cstdint>
 #include <cstring>
@@ -239,6 +240,38 @@ FmhaStrides dense_strides(int n, int head, int k) {
   return s;
 }
 
+// ---------------------------------------------------------------------------------------
+// Built-in scratch for fmha_bwd_static_scratch: part of the device image, so it exists on every
+// GPU that loads the library and costs no allocation call at run time.
+// In HOST code the name below is only a handle for cudaGetSymbolAddress: it is not a device
+// address and must never be handed to a kernel.
+// ---------------------------------------------------------------------------------------
+static __device__ __align__(256) unsigned char g_fmha_static_scratch[FMHA_STATIC_SCRATCH_BYTES];
+
+constexpr int kMaxDevices = 64;
+std::atomic<void*> g_static_scratch_addr[kMaxDevices];  // per device, filled on first use
+
+// Device address of the scratch area on the CURRENT device, or nullptr (rc set) on failure.
+void* static_scratch_for_current_device(int* rc) {
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) {
+    *rc = FMHA_ERR_NO_DEVICE;
+    return nullptr;
+  }
+  void* ptr = g_static_scratch_addr[dev].load(std::memory_order_acquire);
+  if (ptr == nullptr) {
+    // once per device, with that device current; the address differs from device to device
+    if (cudaGetSymbolAddress(&ptr, g_fmha_static_scratch) != cudaSuccess || ptr == nullptr) {
+      (void)cudaGetLastError();
+      *rc = FMHA_ERR_NO_DEVICE;
+      return nullptr;
+    }
+    g_static_scratch_addr[dev].store(ptr, std::memory_order_release);
+  }
+  *rc = FMHA_OK;
+  return ptr;
+}
+
 }  // namespace
 
 extern "C" {
@@ -298,6 +331,21 @@ int fmha_bwd(const FmhaBwdParams* p, void* workspace, size_t workspace_bytes, vo
   if (!aligned16(workspace)) return FMHA_ERR_BAD_ALIGNMENT;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   return p->head_dim == 128 ? launch_bwd<128>(p, w, s) : launch_bwd<64>(p, w, s);
+}
+
+int fmha_bwd_static_scratch(const FmhaBwdParams* p, void* stream) {
+  if (p == nullptr) return FMHA_ERR_NULL_POINTER;
+  // the shared area cannot carry an accumulator over from an earlier call
+  if (p->flags & FMHA_BWD_KEEP_WORKSPACE) return FMHA_ERR_WORKSPACE;
+  if (p->batch <= 0 || p->heads <= 0 || p->seqlen_q <= 0 || p->head_dim <= 0)
+    return FMHA_ERR_BAD_SHAPE;
+  const size_t need = fmha_bwd_workspace_bytes(p);
+  if (need == 0 || need > (size_t)FMHA_STATIC_SCRATCH_BYTES) return FMHA_ERR_TOO_LARGE;
+  int rc = FMHA_OK;
+  void* scratch = static_scratch_for_current_device(&rc);
+  if (scratch == nullptr) return rc;
+  // same validation, kernels and launch order as the caller-workspace entry point
+  return fmha_bwd(p, scratch, (size_t)FMHA_STATIC_SCRATCH_BYTES, stream);
 }
 
 int fmha_bwd_convert_dq(const void* workspace, void* dq, FmhaStrides dq_strides, int32_t batch,

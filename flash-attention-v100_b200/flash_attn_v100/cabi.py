@@ -24,7 +24,7 @@ FMHA_BWD_KEEP_WORKSPACE = 1
 FMHA_BWD_SKIP_DQ_CONVERT = 2
 
 EXPORTED_SYMBOLS = (
-    "fmha_fwd", "fmha_bwd_workspace_bytes", "fmha_bwd", "fmha_bwd_convert_dq", "fmha_merge", "fmha_b200_forward",
+    "fmha_fwd", "fmha_bwd_workspace_bytes", "fmha_bwd", "fmha_bwd_static_scratch", "fmha_bwd_convert_dq", "fmha_merge", "fmha_b200_forward",
     "fmha_b200_backward", "fmha_status_string", "fmha_version",
 )
 
@@ -83,6 +83,8 @@ def load_library() -> ctypes.CDLL:
     lib.fmha_bwd.restype = ctypes.c_int
     lib.fmha_bwd.argtypes = [ctypes.POINTER(FmhaBwdParams), ctypes.c_void_p, ctypes.c_size_t,
                              ctypes.c_void_p]
+    lib.fmha_bwd_static_scratch.restype = ctypes.c_int
+    lib.fmha_bwd_static_scratch.argtypes = [ctypes.POINTER(FmhaBwdParams), ctypes.c_void_p]
     lib.fmha_bwd_convert_dq.restype = ctypes.c_int
     lib.fmha_bwd_convert_dq.argtypes = [ctypes.c_void_p, ctypes.c_void_p, FmhaStrides, ctypes.c_int32,
                                         ctypes.c_int32, ctypes.c_int32, ctypes.c_int32, ctypes.c_float,
@@ -232,6 +234,20 @@ def bwd(q, k, v, o, dout, lse, scale: float, causal: bool = False, causal_shift:
                                        workspace.numel() * workspace.element_size(),
                                        _stream(stream)), "fmha_bwd")
     return dq, dk, dv
+
+
+STATIC_SCRATCH_BYTES = 32 << 20
+
+
+def bwd_static_scratch(q, k, v, o, dout, lse, dq, dk, dv, scale: float, causal: bool = False,
+                       causal_shift: int = 0, status=None, stream=None) -> int:
+    """``fmha_bwd_static_scratch``: backward whose workspace is the 32 MiB area built into the
+    library, for hosts that must not allocate device memory.  The caller passes every input and
+    output (nothing is allocated here either) and gets the raw status code back."""
+    _require_cuda_half(q, k, v, o, dout, dq, dk, dv)
+    p = bwd_params(q, k, v, o, dout, lse, dq, dk, dv, scale, causal, causal_shift, None, None, 0, status)
+    with torch.cuda.device(q.device):
+        return int(load_library().fmha_bwd_static_scratch(ctypes.byref(p), _stream(stream)))
 
 
 def bwd_convert_dq(workspace, dq, scale: float, stream=None):

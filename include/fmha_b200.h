@@ -122,6 +122,37 @@ size_t fmha_bwd_workspace_bytes(const FmhaBwdParams* p);
  * zero-fill of :84. */
 int fmha_bwd(const FmhaBwdParams* p, void* workspace, size_t workspace_bytes, void* stream);
 
+/* Capacity in bytes of the scratch area built into the library for fmha_bwd_static_scratch. */
+#define FMHA_STATIC_SCRATCH_BYTES (32u << 20)
+
+/* Backward without a caller workspace and without any allocation: the same computation and the
+ * same results as fmha_bwd, with the workspace taken from a fixed FMHA_STATIC_SCRATCH_BYTES
+ * (32 MiB) area that is part of the library's device image.  It has no counterpart in the
+ * reference (which keeps no scratch: fp16 atomics in place, kernel/fused_mha_kernel.cu:543,693).
+ *
+ * It is meant for hosts that cannot obtain device memory at the moment they need a backward
+ * pass: a serving or training process that handed all free HBM to its own pool at start-up, so
+ * that a cudaMalloc for our workspace would fail or force the pool to shrink; a plugin called
+ * from a latency-critical section where the device-wide synchronisation hidden in
+ * cudaMalloc/cudaFree is not acceptable; an embedding runtime whose policy forbids a library
+ * to allocate on its own.  Such a caller still passes every input and output buffer; only the
+ * workspace comes from the library.
+ *
+ *  - Limit: fmha_bwd_workspace_bytes(p) must not exceed FMHA_STATIC_SCRATCH_BYTES, otherwise
+ *    FMHA_ERR_TOO_LARGE is returned and nothing is launched (e.g. Z*N*H*D <= ~8.3M elements).
+ *  - Cost: every GPU on which the library is loaded holds the 32 MiB until the process exits,
+ *    whether or not this entry point is ever called.
+ *  - The first call on each device looks up the device address of the area (a host-side
+ *    query, no allocation).  Make that first call outside any stream capture.
+ *  - All calls on a device share the one area and it keeps whatever the last call left; each
+ *    call re-initialises the parts it needs (dQ accumulator zeroed, statistics rewritten), so
+ *    stale contents are harmless, but two calls that overlap on the GPU (different streams,
+ *    or different host threads without ordering) race on it.  Serialise them on one stream.
+ *  - FMHA_BWD_KEEP_WORKSPACE is rejected with FMHA_ERR_WORKSPACE: a shared area cannot carry
+ *    state from one call to the next.
+ */
+int fmha_bwd_static_scratch(const FmhaBwdParams* p, void* stream);
+
 /* dQ = fp16(scale * accumulator) from a backward workspace, for callers that ran fmha_bwd with
  * FMHA_BWD_SKIP_DQ_CONVERT (several calls accumulating into one workspace).  The sizes must be
  * those the workspace was used with.  Replaces the reference's in-place fp16 atomics
