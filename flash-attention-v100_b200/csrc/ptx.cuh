@@ -1,5 +1,5 @@
 // Thin inline-PTX wrappers for the sm_100a primitives the attention kernels use:
-// mbarrier, TMA tensor copies (load / store / reduce-add, never with cluster multicast),
+// mbarrier, TMA tensor copies (load / store / reduce-add, each issued by one CTA for itself),
 // tcgen05 (TMEM allocation, MMA issue, commit, TMEM load/store) and the UMMA
 // shared-memory / instruction descriptors.
 //

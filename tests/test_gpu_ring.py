@@ -1,0 +1,105 @@
+"""GPU tests of the multi-GPU layer's building blocks (1 GPU) and of ring attention itself
+(2 GPUs, NCCL; skipped where fewer devices are visible)."""
+import os
+import socket
+import sys
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from oracle import attention_oracle as oracle
+from tests import helpers
+from tests.conftest import PKG
+
+pytestmark = pytest.mark.gpu
+sys.path.insert(0, PKG)
+
+
+def test_merge_kernel_matches_oracle_merge():
+    """fmha_merge: two partial results over disjoint key halves merged through LSE equal the
+    attention over all keys."""
+    from flash_attn_v100 import cabi
+
+    q, k, v, _ = oracle.make_inputs(2, 256, 3, 128, seed=5, n_k=512)
+    qd, kd, vd = q.cuda(), k.cuda(), v.cuda()
+    o_acc = torch.zeros((2, 256, 3, 128), dtype=torch.float32, device="cuda")
+    lse_acc = torch.full((2, 3, 256), float("-inf"), device="cuda")
+    for lo in (0, 256):
+        o_p, l_p = cabi.fwd(qd, kd[:, lo:lo + 256], vd[:, lo:lo + 256], 0.1, False)
+        cabi.merge(o_acc, lse_acc, o_p, l_p)
+    ref_o, ref_lse = oracle.attention_forward(q, k, v, 0.1, False)
+    assert oracle.max_abs(o_acc.cpu(), ref_o) <= helpers.TOL_O_MAX_ABS
+    assert oracle.max_abs(lse_acc.cpu(), ref_lse) <= helpers.TOL_LSE_MAX_ABS
+
+
+def test_backward_accumulates_over_key_blocks_into_fp32_buffers():
+    """Ring-style backward on one GPU: two key blocks, dQ accumulated in one workspace over both
+    calls, dK/dV added into row ranges of fp32 buffers (batch stride != dense), dQ converted at
+    the end by fmha_bwd_convert_dq."""
+    from flash_attn_v100 import cabi
+
+    Z, Nq, H, D, Nk = 2, 256, 2, 64, 384
+    q, k, v, dout = oracle.make_inputs(Z, Nq, H, D, seed=6, n_k=Nk)
+    ref = oracle.attention_fwd_bwd(q, k, v, dout, 0.15, False)
+    qd, kd, vd, dod = q.cuda(), k.cuda(), v.cuda(), dout.cuda()
+    out, lse = cabi.fwd(qd, kd, vd, 0.15, False)
+    ws = torch.empty(cabi.bwd_workspace_bytes(Z, Nq, H, D), dtype=torch.uint8, device="cuda")
+    dk_acc = torch.zeros((Z, Nk, H, D), dtype=torch.float32, device="cuda")
+    dv_acc = torch.zeros_like(dk_acc)
+    flags = cabi.FMHA_BWD_SKIP_DQ_CONVERT
+    for lo, hi in ((0, 128), (128, 384)):
+        cabi.bwd(qd, kd[:, lo:hi], vd[:, lo:hi], out, dod, lse, 0.15, False, dq=None,
+                 dk_accum=dk_acc[:, lo:hi], dv_accum=dv_acc[:, lo:hi], workspace=ws, flags=flags)
+        flags |= cabi.FMHA_BWD_KEEP_WORKSPACE
+    dq = torch.empty_like(qd)
+    cabi.bwd_convert_dq(ws, dq, 0.15)
+    got = (out.cpu(), lse.cpu(), dq.cpu(), dk_acc.cpu(), dv_acc.cpu())
+    helpers.check_against_oracle(got, ref, "blockwise backward")
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _ring_worker(rank, world, port, causal, out_dir):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    try:
+        from flash_attn_v100 import distributed as fd
+
+        Z, N, H, D = 1, 512 * world, 4, 128
+        q, k, v, dout = oracle.make_inputs(Z, N, H, D, seed=9)
+        ql, kl, vl, dol = (fd.zigzag_split(t, rank, world).cuda().requires_grad_(i < 3)
+                           for i, t in enumerate((q, k, v, dout)))
+        out = fd.ring_flash_attn_func(ql, kl, vl, 0.1, causal)
+        out.backward(dol)
+        torch.cuda.synchronize()
+        torch.save(dict(out=out.detach().cpu(), dq=ql.grad.cpu(), dk=kl.grad.cpu(), dv=vl.grad.cpu()),
+                   os.path.join(out_dir, f"rank{rank}.pt"))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("causal", [True, False])
+def test_ring_attention_on_gpus(causal, tmp_path):
+    """Zig-zag ring attention over NCCL send/recv against the oracle on the full sequence.
+    World size = visible GPUs (2, 4 or 8), world size 1 exercises the same code path without a
+    peer."""
+    from flash_attn_v100 import distributed as fd
+
+    world = torch.cuda.device_count()
+    world = 8 if world >= 8 else 4 if world >= 4 else 2 if world >= 2 else 1
+    mp.spawn(_ring_worker, args=(world, _free_port(), causal, str(tmp_path)), nprocs=world, join=True)
+    parts = [torch.load(os.path.join(tmp_path, f"rank{r}.pt")) for r in range(world)]
+    Z, N, H, D = 1, 512 * world, 4, 128
+    q, k, v, dout = oracle.make_inputs(Z, N, H, D, seed=9)
+    ref_out, _, ref_dq, ref_dk, ref_dv = oracle.attention_fwd_bwd(q, k, v, dout, 0.1, causal)
+    got = {key: fd.zigzag_merge([p[key] for p in parts]) for key in ("out", "dq", "dk", "dv")}
+    assert oracle.max_abs(got["out"].float(), ref_out) <= helpers.TOL_O_MAX_ABS
+    for key, ref in (("dq", ref_dq), ("dk", ref_dk), ("dv", ref_dv)):
+        assert oracle.rel_l2(got[key].float(), ref) <= helpers.TOL_GRAD_REL_L2, key
