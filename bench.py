@@ -52,6 +52,8 @@ WORKLOADS = {
     "cfg4_per_gpu_z8": (8, 16, 512, 64, False, 0.125),
     "cfg4_full_z64": (64, 16, 512, 64, False, 0.125),
     "ref_test_shape": (2, 40, 2048, 128, True, 0.1),
+    # BASELINE config 5: the whole sequence is sharded over the GPUs (zig-zag ring attention)
+    "cfg5_ring_causal": (1, 32, 32768, 128, True, 128 ** -0.5),
 }
 DEFAULT_WORKLOAD = "cfg3_causal"
 METRIC = "attention fwd+bwd TFLOPS (algorithmic), whole job"
@@ -213,6 +215,69 @@ def time_events(fn, iters, torch):
     return start.elapsed_time(end) / iters
 
 
+def run_ring(args):
+    """BASELINE config 5: one long causal sequence sharded over all ranks (zig-zag), K/V blocks and
+    fp32 dK/dV rotating over NCCL send/recv, merged through LSE.  Strong scaling: the total work
+    is fixed, value = whole-sequence algorithmic FLOPs / max-over-ranks device time."""
+    import torch
+    import torch.distributed as dist
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world == 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        os.environ.setdefault("MASTER_PORT", "29533")
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    from flash_attn_v100 import distributed as fd
+
+    Z, H, N, D, causal, scale = WORKLOADS[args.workload]
+    c = N // (2 * world)
+    g = torch.Generator(device=dev).manual_seed(rank)
+    ql, kl, vl, dol = (torch.randn((Z, 2 * c, H, D), generator=g, device=dev, dtype=torch.float32).half()
+                       for _ in range(4))
+    be = fd.CudaBackend()
+
+    def step():
+        out, lse = fd.ring_attention_forward(ql, kl, vl, scale, causal, None, be)
+        fd.ring_attention_backward(ql, kl, vl, out, lse, dol, scale, causal, None, be)
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    torch.cuda.synchronize()
+    dist.barrier()
+    sampler = ClockSampler(local_rank) if rank == 0 else None
+    if sampler:
+        sampler.start()
+    ms = time_events(step, args.steps, torch)
+    dist.barrier()
+    torch.cuda.synchronize()
+    t = torch.tensor([ms], dtype=torch.float64, device=dev)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = float(t.item())
+    clocks = sampler.stop() if sampler else None
+    if rank == 0:
+        fl = flops(Z, H, N, D, causal, False) + flops(Z, H, N, D, causal, True)
+        peaks = measured_peaks()
+        kv_hop = 2 * Z * 2 * c * H * D * 2
+        print(json.dumps({
+            "metric": METRIC, "value": fl / (ms * 1e-3) / 1e12, "unit": "TFLOPS", "n_gpus": world,
+            "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms,
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "dtype": "f16 (fp32 accumulate)", "data": "synthetic",
+            "config": {"workload": args.workload, "Z": Z, "H": H, "N": N, "D": D, "causal": causal,
+                       "parallelism": f"zig-zag ring attention x{world} (NCCL send/recv)",
+                       "rows_per_gpu": 2 * c, "kv_bytes_per_hop": kv_hop,
+                       "dkdv_bytes_per_hop": 2 * kv_hop},
+            "per_gpu_tflops": fl / (ms * 1e-3) / 1e12 / world,
+            "per_gpu_frac_of_measured_peak": fl / (ms * 1e-3) / 1e12 / world / peaks["tflops_sustained"],
+            "gpu_launches": None, "clocks": clocks}), flush=True)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
 def run_ours(args):
     import torch
     import torch.distributed as dist
@@ -231,7 +296,11 @@ def run_ours(args):
     from oracle import attention_oracle as oracle
 
     Z, H, N, D, causal, scale = WORKLOADS[args.workload]
-    # every rank draws its own batch (seed = rank): weak scaling, no communication
+    # BASELINE config 4 fixes the total batch (Z=64) and splits it over the GPUs: strong scaling
+    strong = args.workload == "cfg4_full_z64" and world > 1
+    if strong:
+        Z //= world
+    # every rank draws its own batch (seed = rank): no communication
     hq, hk, hv, hdo = (t.pin_memory() for t in oracle.make_inputs(Z, N, H, D, seed=rank))
     q, k, v, dout = (t.to(dev) for t in (hq, hk, hv, hdo))
     out = torch.empty_like(q)
@@ -322,7 +391,7 @@ def run_ours(args):
             "metric": METRIC,
             "value": world * (f_fwd + f_bwd) / (ms_step * 1e-3) / 1e12,
             "unit": "TFLOPS", "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
-            "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong" if strong else "weak", "vs_baseline": None,
             "dtype": "f16 (fp32 accumulate)", "data": "synthetic",
             "config": {"workload": args.workload, "Z_per_gpu": Z, "H": H, "N": N, "D": D, "causal": causal,
                        "scale": scale, "parallelism": f"batch-sharded x{world}, no collective",
@@ -367,6 +436,8 @@ def main():
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
+    elif args.workload.startswith("cfg5_ring"):
+        run_ring(args)
     else:
         run_ours(args)
 
