@@ -6,17 +6,18 @@
 // is 256 query rows (two 128-row tiles) of one (batch, head), processed against the KV sequence
 // in 128-row tiles:
 //
-//   warp 8      TMA producer for K_0, V_0, K_1, V_1, ... through a ring of shared-memory slots
+//   warp 16     TMA producer for K_0, V_0, K_1, V_1, ... through a ring of shared-memory slots
 //               (full / empty mbarriers per slot); runs ahead into the next item as slots free
-//   warp 10     TMA producer for the two Q tiles of an item, as soon as the previous item's
+//   warp 18     TMA producer for the two Q tiles of an item, as soon as the previous item's
 //               last S = Q K^T has released them
-//   warp 9      MMA issuer: S_t = Q_t K_j^T (both operands in shared memory) and
+//   warp 17     MMA issuer: S_t = Q_t K_j^T (both operands in shared memory) and
 //               O_t += P_t V_j (P_t read from tensor memory), accumulators in tensor memory.
 //               The whole warp runs the loop so that descriptors stay in uniform registers;
 //               one elected lane issues.
-//   warps 0-3   softmax of query tile 0: one thread per row, S_0 read with tcgen05.ld, online
-//               exp2 softmax, P_0 written back over S_0 as fp16, lazy O_0 rescale, epilogue
-//   warps 4-7   the same for query tile 1
+//   warps 0-7   softmax of query tile 0: two threads per row (64 score columns each), S_0 read
+//               with tcgen05.ld, online exp2 softmax, P_0 written back over S_0 as fp16, lazy
+//               O_0 rescale, epilogue
+//   warps 8-15  the same for query tile 1
 //
 // While one softmax group works on its tile the tensor pipe runs the other tile's MMAs, and
 // while the groups run an item's epilogue the producer and the MMA warp already start the next
@@ -67,7 +68,7 @@ struct FwdTraits {
   static constexpr int kBoxBytes = 128 * 128;  // 128 rows x 128 bytes
   static constexpr int kTileBytes = kBoxes * kBoxBytes;
   static constexpr int kStages = (D == 128) ? 3 : 6;
-  static constexpr int kThreads = 384;  // softmax 0, softmax 1, {TMA, MMA, 2 idle} warpgroups
+  static constexpr int kThreads = 640;  // 16 softmax warps (2 tiles x 2 column halves), 4 issue warps
   // Q tiles, K/V ring, one output staging tile per softmax group
   static constexpr int kSmemBytes = 1024 + (kTilesM + kStages + 2) * kTileBytes;
   static constexpr int kTmemCols = 512;
@@ -75,10 +76,22 @@ struct FwdTraits {
   static constexpr uint32_t kIdescPV = umma_idesc_f16(128, D, 0, 1);
 };
 
-constexpr int kFwdRegsIssue = 88;                                 // warps 8-11
-constexpr int kFwdRegsSoftmax = 168 + (168 - kFwdRegsIssue) / 2;  // warps 0-7: 208
-static_assert(kFwdRegsIssue <= 168 && kFwdRegsSoftmax >= 168 && kFwdRegsSoftmax % 8 == 0,
-              "setmaxnreg.dec must not raise and .inc must not lower the 168 registers of the launch");
+constexpr int kKvWarp = 16, kMmaWarp = 17, kQWarp = 18;
+// 640 threads start at 96 registers each.  The issuing warpgroup (warps 16-19) gives up 32 per
+// thread, which lets the four softmax warpgroups grow by 8.
+// pairs out of every 4 whose exponential is a polynomial on the FMA pipe (the rest use MUFU)
+#ifndef FMHA_FWD_POLY_PAIRS
+#define FMHA_FWD_POLY_PAIRS 1
+#endif
+constexpr int kFwdPolyPairs = FMHA_FWD_POLY_PAIRS;
+constexpr int kFwdRegsLaunch = 96, kFwdRegsIssue = 64, kFwdRegsSoftmax = 104;
+static_assert(kFwdRegsIssue <= kFwdRegsLaunch && kFwdRegsSoftmax >= kFwdRegsLaunch,
+              "setmaxnreg.dec must not raise and .inc must not lower the launch allocation");
+// setmaxnreg.inc waits until the registers are there, and the pool it draws from is what the CTA
+// was launched with (threads x launch registers), not the whole register file: asking for more
+// than the other warpgroups give back blocks for ever.
+static_assert(kFwdRegsSoftmax * 512 + kFwdRegsIssue * 128 <= kFwdRegsLaunch * 640,
+              "setmaxnreg.inc would wait for registers that no warpgroup releases");
 
 // lazy rescale threshold in the log2 domain: P may grow to 2^8 before O is rescaled
 constexpr float kRescaleThreshold = 8.0f;
@@ -134,7 +147,7 @@ __device__ __forceinline__ void fwd_item_extent(const FwdKernelParams& p, int q0
 }
 
 template <int D>
-__global__ void __launch_bounds__(384, 1)
+__global__ void __launch_bounds__(640, 1)
     fmha_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                     const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_o,
                     const FwdKernelParams p) {
@@ -148,6 +161,7 @@ __global__ void __launch_bounds__(384, 1)
   __shared__ uint64_t bar_p_full[2];
   __shared__ uint64_t bar_o_full[2];
   __shared__ uint64_t bar_o_read[2];   // the softmax group has O_t in registers: O_t reusable
+  __shared__ float row_xch[2][128];    // per tile: row statistics passed between the two halves
   __shared__ uint32_t tmem_base_slot;
   __shared__ int abort_word;
   __shared__ int skip_cta;
@@ -178,13 +192,13 @@ __global__ void __launch_bounds__(384, 1)
       mbar_init(smem_u32(&bar_q_full[t]), 1);
       mbar_init(smem_u32(&bar_q_free[t]), 1);
       mbar_init(smem_u32(&bar_s_full[t]), 1);
-      mbar_init(smem_u32(&bar_p_full[t]), 128);
+      mbar_init(smem_u32(&bar_p_full[t]), 256);
       mbar_init(smem_u32(&bar_o_full[t]), 1);
-      mbar_init(smem_u32(&bar_o_read[t]), 128);
+      mbar_init(smem_u32(&bar_o_read[t]), 256);
     }
     fence_barrier_init();
   }
-  if (warp == 9) {
+  if (warp == kMmaWarp) {
     tmem_alloc(smem_u32(&tmem_base_slot), T::kTmemCols);
     tmem_relinquish();
   }
@@ -196,12 +210,9 @@ __global__ void __launch_bounds__(384, 1)
   FwdWorkIter work(blockIdx.x, gridDim.x, p.num_q_blocks, p.num_heads_total);
   int zh, qb;
 
-  // Register budget: 384 threads leave 168 per thread.  The producer / MMA warpgroup hands part
-  // of its share to the softmax warpgroups, whose threads hold a 128-column row of S.  Each
-  // setmaxnreg sits at the top of its warpgroup's own branch.
-  if (warp >= 8) {
+  if (warp >= 16) {
     reg_dealloc<kFwdRegsIssue>();
-    if (warp == 8) {
+    if (warp == kKvWarp) {
       // =========================== TMA producer (converged warp, elected issue) ==========
       if (elect_one()) {
         tma_prefetch_desc(&tm_q);
@@ -238,7 +249,7 @@ __global__ void __launch_bounds__(384, 1)
           __syncwarp();
         }
       }
-    } else if (warp == 10) {
+    } else if (warp == kQWarp) {
       // =========================== Q producer ===========================
       // its own warp, so that waiting for the Q buffers of the running item never holds back
       // the K/V prefetch of the next one
@@ -285,7 +296,7 @@ __global__ void __launch_bounds__(384, 1)
           __syncwarp();
         }
       }
-    } else if (warp == 9) {
+    } else if (warp == kMmaWarp) {
       // =========================== MMA issuer (converged warp, elected issue) ============
       // All 32 lanes run the loop so that addresses and descriptors live in uniform registers;
       // a loop run by one lane only makes every operand a per-thread value that has to be moved
@@ -409,21 +420,33 @@ __global__ void __launch_bounds__(384, 1)
   } else {
     // =========================== softmax / epilogue ===========================
     reg_alloc<kFwdRegsSoftmax>();
-    const int t = warp >> 2;    // query tile of this warpgroup
-    const int quad = warp & 3;  // TMEM lane quadrant of this warp
+    // Two threads per query row (warps t*8 + hf*4 + quad: tile t, column half hf, TMEM lane
+    // quadrant quad), each owning 64 of the 128 score columns.  One warp per scheduler issues at
+    // most every other cycle; with two warps of the active tile on every scheduler the pass over
+    // a tile is bound by the MUFU unit instead of by instruction issue.
+    const int t = warp >> 3;         // query tile
+    const int hf = (warp >> 2) & 1;  // column half of this thread
+    const int quad = warp & 3;       // TMEM lane quadrant of this warp
     const int row_in_tile = quad * 32 + lane;
     const uint32_t lane_addr = uint32_t(quad * 32) << 16;
-    const uint32_t tS = tmem_base + lane_addr + t * 128;
-    const uint32_t tO = tmem_base + lane_addr + 256 + t * D;
+    const uint32_t tS = tmem_base + lane_addr + t * 128 + hf * 64;          // my 64 score columns
+    const uint32_t tP = tmem_base + lane_addr + t * 128 + hf * 32;          // my 32 packed P columns
+    const uint32_t tO = tmem_base + lane_addr + 256 + t * D + hf * (D / 2); // my D/2 output columns
     const uint32_t o_stage = ostage_smem + t * T::kTileBytes;
-    bool stored = false;  // a TMA store of this group may still be reading the staging box
+    const uint32_t xch = smem_u32(&row_xch[t][row_in_tile]);  // fp32 view: row sums
+    // 16-bit view of the same words: row references, one slot per thread of the row
+    const uint32_t xch_mine = smem_u32(&row_xch[t][0]) + (hf * 128 + row_in_tile) * 2;
+    const uint32_t xch_other = smem_u32(&row_xch[t][0]) + ((hf ^ 1) * 128 + row_in_tile) * 2;
+    const uint32_t bar_id = 1 + t;               // named barrier of this tile's 256 threads
+    const uint32_t pair_bar = 3 + t * 4 + quad;  // named barrier of the two warps sharing my rows
+    bool stored = false;  // a TMA store of this tile may still be reading the staging tile
     const float c = p.scale_log2;
     // a masked score must give exp2(s * c - m * c) = 0 whatever the sign of c
     const float mask_val = (c >= 0.f) ? -CUDART_INF_F : CUDART_INF_F;
-    const bool tl = (lane == 0 && quad == 0);
-    uint32_t s_cnt = 0;   // S_t tiles consumed so far (phase of s_full[t])
-    uint32_t o_cnt = 0;   // O_t tiles read so far (phase of o_full[t])
-    int tl_base = 0;      // timeline slot offset of the current item (debug builds)
+    const bool tl = (lane == 0 && quad == 0 && hf == 0);
+    uint32_t s_cnt = 0;  // S_t tiles consumed so far (phase of s_full[t])
+    uint32_t o_cnt = 0;  // O_t tiles read so far (phase of o_full[t])
+    int tl_base = 0;     // timeline slot offset of the current item (debug builds)
 
     while (work.next(zh, qb)) {
       const int z = zh / p.heads, h = zh % p.heads;
@@ -439,61 +462,78 @@ __global__ void __launch_bounds__(384, 1)
       const int row_limit = (int)lim_ll;  // last visible key of this row (-1 = none)
 
       float m_ref = mask_val;  // reference score of the running softmax (raw, unscaled)
-      float l = 0.f;           // running sum of exp2((s - m_ref) * c)
+      float l = 0.f;           // this thread's share of the running sum of exp2((s - m_ref) * c)
 
       for (int j = 0; j < n; ++j, ++s_cnt) {
         if (tl) FMHA_TL(t, tl_base + j, 0);
-        // on a time-out keep going: every later wait returns at once, and all 128 threads of
-        // the group still meet at the named barriers of the epilogue
+        // on a time-out keep going: every later wait returns at once, and all threads of the
+        // tile still meet at the named barriers
         mbar_wait(smem_u32(&bar_s_full[t]), s_cnt & 1, &abort_word, 9);
         tc_fence_after();
         if (tl) FMHA_TL(t, tl_base + j, 1);
-        uint32_t s[4][32];
+        uint32_t s[2][32];
         tmem_ld32(tS + 0, s[0]);
         tmem_ld32(tS + 32, s[1]);
-        tmem_ld32(tS + 64, s[2]);
-        tmem_ld32(tS + 96, s[3]);
         tmem_wait_ld();
         if (tl) FMHA_TL(t, tl_base + j, 2);
 
-        const int lim = row_limit - j * T::kBlockN;  // columns > lim of this tile are masked
-        if (lim < T::kBlockN - 1) {
+        // columns > lim of this tile are masked (lim counted within my 64 columns)
+        const int lim = row_limit - j * T::kBlockN - hf * 64;
+        if (lim < 63) {
 #pragma unroll
-          for (int cc = 0; cc < 4; ++cc)
+          for (int cc = 0; cc < 2; ++cc)
 #pragma unroll
             for (int i = 0; i < 32; ++i)
               if (cc * 32 + i > lim) s[cc][i] = __float_as_uint(mask_val);
         }
 
-        // row extreme: max of s when c >= 0, min when c < 0, so that m * c = max(s * c)
+        // extreme of my 64 scores: max when c >= 0, min when c < 0, so that m * c = max(s * c)
         float mx0 = __uint_as_float(s[0][0]), mx1 = __uint_as_float(s[1][0]);
-        float mx2 = __uint_as_float(s[2][0]), mx3 = __uint_as_float(s[3][0]);
         if (c >= 0.f) {
+          mx0 = fmaxf(mx0, __uint_as_float(s[0][1]));
+          mx1 = fmaxf(mx1, __uint_as_float(s[1][1]));
 #pragma unroll
-          for (int i = 1; i < 32; ++i) {
-            mx0 = fmaxf(mx0, __uint_as_float(s[0][i]));
-            mx1 = fmaxf(mx1, __uint_as_float(s[1][i]));
-            mx2 = fmaxf(mx2, __uint_as_float(s[2][i]));
-            mx3 = fmaxf(mx3, __uint_as_float(s[3][i]));
+          for (int i = 2; i < 32; i += 2) {
+            mx0 = max3(mx0, __uint_as_float(s[0][i]), __uint_as_float(s[0][i + 1]));
+            mx1 = max3(mx1, __uint_as_float(s[1][i]), __uint_as_float(s[1][i + 1]));
           }
         } else {
+          mx0 = fminf(mx0, __uint_as_float(s[0][1]));
+          mx1 = fminf(mx1, __uint_as_float(s[1][1]));
 #pragma unroll
-          for (int i = 1; i < 32; ++i) {
-            mx0 = fminf(mx0, __uint_as_float(s[0][i]));
-            mx1 = fminf(mx1, __uint_as_float(s[1][i]));
-            mx2 = fminf(mx2, __uint_as_float(s[2][i]));
-            mx3 = fminf(mx3, __uint_as_float(s[3][i]));
+          for (int i = 2; i < 32; i += 2) {
+            mx0 = min3(mx0, __uint_as_float(s[0][i]), __uint_as_float(s[0][i + 1]));
+            mx1 = min3(mx1, __uint_as_float(s[1][i]), __uint_as_float(s[1][i + 1]));
           }
         }
-        float mx = (c >= 0.f) ? fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3))
-                              : fminf(fminf(mx0, mx1), fminf(mx2, mx3));
-        if (FMHA_ABLATE & 2) mx = __uint_as_float(s[0][0]);
+        float mx = (c >= 0.f) ? fmaxf(mx0, mx1) : fminf(mx0, mx1);
+        // The row reference has to be the same number in both threads of the row, but not the
+        // exact extreme: anything between the extreme and a little beyond it will do.  Each
+        // thread rounds its value away from the scores to 16 bits, the two swap them through
+        // shared memory, and both take the extreme of the same two numbers.
+        // The barrier of the pair also orders half 0's tcgen05.ld of S columns 32..63 before
+        // half 1 overwrites them with its packed P.  The slot is reused every tile: the partner
+        // has read it before it arrives on p_full, which the next S tile is ordered after.
+        {
+          uint32_t b = __float_as_uint(mx);
+          const bool grow = ((b >> 31) == 0u) == (c >= 0.f);  // larger magnitude = away
+          b = (grow ? b + 0xffffu : b) & 0xffff0000u;
+          asm volatile("st.shared.u16 [%0], %1;" ::"r"(xch_mine), "h"((uint16_t)(b >> 16))
+                       : "memory");
+          named_bar_sync(pair_bar, 64);
+          uint16_t o16;
+          asm volatile("ld.shared.u16 %0, [%1];" : "=h"(o16) : "r"(xch_other) : "memory");
+          const float other = __uint_as_float((uint32_t)o16 << 16);
+          mx = __uint_as_float(b);
+          mx = (c >= 0.f) ? fmaxf(mx, other) : fminf(mx, other);
+        }
 
         if (j == 0) {
           m_ref = mx;
         } else {
           const float m_new = (c >= 0.f) ? fmaxf(m_ref, mx) : fminf(m_ref, mx);
-          // growth of the scaled maximum; NaN (inf - inf) compares false
+          // growth of the scaled maximum; NaN (inf - inf) compares false.  Both threads of a
+          // row see the same numbers, and both half-warps hold the same rows: same decision.
           const bool need = (m_new - m_ref) * c > kRescaleThreshold;
           if (__any_sync(0xffffffffu, need)) {
             // O_t is idle here: S_t(j) is committed after O_t += P_t V_(j-1) was issued
@@ -501,43 +541,48 @@ __global__ void __launch_bounds__(384, 1)
             l *= alpha;
             m_ref = m_new;
 #pragma unroll
-            for (int cc = 0; cc < D / 32; ++cc) {
-              uint32_t o[32];
-              tmem_ld32(tO + cc * 32, o);
+            for (int cc = 0; cc < D / 32; ++cc) {  // my half of the output columns
+              uint32_t o[16];
+              tmem_ld16(tO + cc * 16, o);
               tmem_wait_ld();
 #pragma unroll
-              for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
-              tmem_st32(tO + cc * 32, o);
+              for (int i = 0; i < 16; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+              tmem_st16(tO + cc * 16, o);
             }
           }
         }
 
         if (tl) FMHA_TL(t, tl_base + j, 3);
         const float neg_mc = isinf(m_ref) ? 0.f : -m_ref * c;
-        float l0 = 0.f, l1 = 0.f, l2 = 0.f, l3 = 0.f;
+        const uint64_t c2 = pack2f(c, c), nm2 = pack2f(neg_mc, neg_mc);
+        uint64_t la = pack2f(0.f, 0.f), lb = pack2f(0.f, 0.f);
 #pragma unroll
-        for (int hf = 0; hf < 2; ++hf) {  // 64 scores -> 32 packed columns of P at a time
-          uint32_t pk[32];
+        for (int cc = 0; cc < 2; ++cc) {  // 32 scores -> 16 packed columns of P at a time
+          uint32_t pk[16];
 #pragma unroll
-          for (int c2 = 0; c2 < 2; ++c2) {
-            const int cc = hf * 2 + c2;
-#pragma unroll
-            for (int i = 0; i < 32; i += 4) {
-              const float p0 = fast_exp2(fmaf(__uint_as_float(s[cc][i + 0]), c, neg_mc));
-              const float p1 = fast_exp2(fmaf(__uint_as_float(s[cc][i + 1]), c, neg_mc));
-              const float p2 = fast_exp2(fmaf(__uint_as_float(s[cc][i + 2]), c, neg_mc));
-              const float p3 = fast_exp2(fmaf(__uint_as_float(s[cc][i + 3]), c, neg_mc));
-              l0 += p0;
-              l1 += p1;
-              l2 += p2;
-              l3 += p3;
-              pk[c2 * 16 + (i >> 1) + 0] = pack_half2(p0, p1);
-              pk[c2 * 16 + (i >> 1) + 1] = pack_half2(p2, p3);
+          for (int i = 0; i < 32; i += 2) {
+            const uint64_t x2 = fma2(pack2(s[cc][i], s[cc][i + 1]), c2, nm2);
+            uint64_t p2;
+            // kFwdPolyPairs of every 4 pairs go through the FMA pipe instead of the MUFU unit
+            if (((i >> 1) & 3) < kFwdPolyPairs) {
+              p2 = poly_exp2_pair(x2);
+            } else {
+              uint32_t x0, x1;
+              unpack2(x2, x0, x1);
+              p2 = pack2f(fast_exp2(__uint_as_float(x0)), fast_exp2(__uint_as_float(x1)));
             }
+            if (i & 2) lb = add2(lb, p2); else la = add2(la, p2);
+            uint32_t p0, p1;
+            unpack2(p2, p0, p1);
+            pk[i >> 1] = pack_half2(__uint_as_float(p0), __uint_as_float(p1));
           }
-          if (!(FMHA_ABLATE & 4)) tmem_st32(tS + hf * 32, pk);
+          tmem_st16(tP + cc * 16, pk);
         }
-        l += (l0 + l1) + (l2 + l3);
+        {
+          uint32_t a0, a1;
+          unpack2(add2(la, lb), a0, a1);
+          l += __uint_as_float(a0) + __uint_as_float(a1);
+        }
         if (tl) FMHA_TL(t, tl_base + j, 4);
         tmem_wait_st();
         tc_fence_before();
@@ -546,50 +591,70 @@ __global__ void __launch_bounds__(384, 1)
       }
       if (tl) FMHA_TL(t, tl_base + 15, 6);
 
-      // ---- epilogue: O_t / l -> fp16 registers (tensor memory released) -> staging box -> TMA
-      //      store; LSE
+      // ---- epilogue: my half of O_t / l -> fp16 registers (tensor memory released) ->
+      //      staging tile -> TMA store; LSE
       if (tile_valid) {
-        uint32_t oh[D / 2];  // the output row, fp16 pairs
         if (n > 0) {
+          // O_t complete.  It also tells that every thread of the tile is through its last
+          // exchange of row references, whose 16-bit slots the row sums below reuse.
           mbar_wait(smem_u32(&bar_o_full[t]), o_cnt & 1, &abort_word, 10);
           ++o_cnt;
           tc_fence_after();
           if (tl) FMHA_TL(t, tl_base + 15, 8);
+        }
+        // the row sum: half 1 hands its share to half 0, which hands the total back
+        if (hf == 1) asm volatile("st.shared.f32 [%0], %1;" ::"r"(xch), "f"(l) : "memory");
+        named_bar_sync(bar_id, 256);
+        if (hf == 0) {
+          float other;
+          asm volatile("ld.shared.f32 %0, [%1];" : "=f"(other) : "r"(xch) : "memory");
+          l += other;
+          asm volatile("st.shared.f32 [%0], %1;" ::"r"(xch), "f"(l) : "memory");
+        }
+        named_bar_sync(bar_id, 256);
+        if (hf == 1) asm volatile("ld.shared.f32 %0, [%1];" : "=f"(l) : "r"(xch) : "memory");
+
+        uint32_t oh[D / 4];  // my half of the output row, fp16 pairs
+        if (n > 0) {
           const float inv_l = (l > 0.f) ? 1.f / l : 0.f;
-          uint32_t o[D / 32][32];
 #pragma unroll
-          for (int cc = 0; cc < D / 32; ++cc) tmem_ld32(tO + cc * 32, o[cc]);
-          tmem_wait_ld();
-          tc_fence_before();
-          mbar_arrive(smem_u32(&bar_o_read[t]));
-          if (tl) FMHA_TL(t, tl_base + 15, 9);
-#pragma unroll
-          for (int cc = 0; cc < D / 32; ++cc)
+          for (int cc = 0; cc < D / 64; ++cc) {  // 32 columns at a time keeps the registers low
+            uint32_t o[32];
+            tmem_ld32(tO + cc * 32, o);
+            tmem_wait_ld();
+            if (cc == D / 64 - 1) {  // O_t is in registers: the next item may overwrite it
+              tc_fence_before();
+              mbar_arrive(smem_u32(&bar_o_read[t]));
+              if (tl) FMHA_TL(t, tl_base + 15, 9);
+            }
 #pragma unroll
             for (int i = 0; i < 32; i += 2)
-              oh[cc * 16 + (i >> 1)] = pack_half2(__uint_as_float(o[cc][i]) * inv_l,
-                                                  __uint_as_float(o[cc][i + 1]) * inv_l);
+              oh[cc * 16 + (i >> 1)] = pack_half2(__uint_as_float(o[i]) * inv_l,
+                                                  __uint_as_float(o[i + 1]) * inv_l);
+          }
         } else {
 #pragma unroll
-          for (int i = 0; i < D / 2; ++i) oh[i] = 0u;
+          for (int i = 0; i < D / 4; ++i) oh[i] = 0u;
         }
-        if (row < p.seqlen_q) {
+        if (hf == 0 && row < p.seqlen_q) {
           const float lse =
               (l > 0.f) ? (m_ref * c + log2f(l)) * 0.6931471805599453f : -CUDART_INF_F;
           p.lse[((size_t)z * p.heads + h) * p.seqlen_q + row] = lse;
         }
-        // through this group's staging tile and TMA stores (per-thread stores of whole rows are
+        // through the staging tile and TMA stores (per-thread stores of whole rows are
         // uncoalesced and clog the load/store pipe for everybody)
-        if (row_in_tile == 0 && stored) tma_wait_group_read<0>();  // previous item's store
-        named_bar_sync(1 + t, 128);
+        if (row_in_tile == 0 && hf == 0 && stored) tma_wait_group_read<0>();  // previous item
+        named_bar_sync(bar_id, 256);
 #pragma unroll
-        for (int ch = 0; ch < D / 8; ++ch)  // 16-byte chunk (8 fp16) of this row
-          sts128(o_stage + (ch >> 3) * T::kBoxBytes + row_in_tile * 128 +
-                     (((ch & 7) ^ (row_in_tile & 7)) << 4),
+        for (int ch = 0; ch < D / 16; ++ch) {  // my 16-byte chunks (8 fp16 each)
+          const int gch = hf * (D / 16) + ch;  // chunk index within the whole row
+          sts128(o_stage + (gch >> 3) * T::kBoxBytes + row_in_tile * 128 +
+                     (((gch & 7) ^ (row_in_tile & 7)) << 4),
                  oh[ch * 4 + 0], oh[ch * 4 + 1], oh[ch * 4 + 2], oh[ch * 4 + 3]);
+        }
         fence_proxy_async_smem();
-        named_bar_sync(1 + t, 128);
-        if (row_in_tile == 0) {
+        named_bar_sync(bar_id, 256);
+        if (row_in_tile == 0 && hf == 0) {
 #pragma unroll
           for (int b = 0; b < T::kBoxes; ++b)
             tma_store_4d(&tm_o, o_stage + b * T::kBoxBytes, b * 64, q0 + t * T::kBlockM, h, z);
@@ -600,7 +665,7 @@ __global__ void __launch_bounds__(384, 1)
       if (tl) FMHA_TL(t, tl_base + 15, 7);
       tl_base += 16;
     }
-    if (row_in_tile == 0) tma_wait_group<0>();
+    if (row_in_tile == 0 && hf == 0) tma_wait_group<0>();
   }
 
   // ---- teardown
@@ -611,7 +676,7 @@ __global__ void __launch_bounds__(384, 1)
     // let copies that may still be in flight land before the shared memory is released
     for (int i = 0; i < 64; ++i) __nanosleep(1000);
   }
-  if (warp == 9) {
+  if (warp == kMmaWarp) {
     tc_fence_after();
     tmem_dealloc(tmem_base, T::kTmemCols);
   }

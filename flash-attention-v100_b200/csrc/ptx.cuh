@@ -217,6 +217,28 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32
       : "memory");
 }
 
+// 16-column variants (a thread that owns half a row keeps fewer values in flight)
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+        "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
+        "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+      :
+      : "r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]),
+        "r"(r[7]), "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]),
+        "r"(r[14]), "r"(r[15])
+      : "memory");
+}
+
 // ---------------------------------------------------------------------------------
 // UMMA descriptors (fp16 operands, fp32 accumulate, dense, cta_group::1, M = 128)
 // ---------------------------------------------------------------------------------
@@ -341,6 +363,83 @@ __device__ __forceinline__ float fast_exp2(float x) {
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 #endif
+}
+// exp2 on the FMA / ALU pipes (no MUFU): x = n + f with n = floor(x) from a round-down add of
+// 1.5 * 2^23, 2^f by a cubic (relative error 7.5e-5, far below the fp16 rounding P gets anyway),
+// 2^n by adding n into the exponent field.  Used for a fraction of the softmax exponentials so
+// that the 16-per-clock MUFU unit is not the only pipe doing them.  x is clamped to >= -126
+// (masked -inf scores give 2^-126, which rounds to 0 in fp16).
+__device__ __forceinline__ float poly_exp2(float x) {
+  x = fmaxf(x, -126.f);
+  float t;
+  asm("add.rm.ftz.f32 %0, %1, %2;" : "=f"(t) : "f"(x), "f"(12582912.f));
+  const float f = x - (t - 12582912.f);
+  float p = fmaf(f, 0.0780244917f, 0.2260672003f);
+  p = fmaf(p, f, 0.6958335042f);
+  p = fmaf(p, f, 0.9999251962f);
+  return __int_as_float(__float_as_int(p) + (__float_as_int(t) << 23));
+}
+// ---- packed pairs of fp32 (one instruction works on two values; sm_100 f32x2 forms) ----
+__device__ __forceinline__ uint64_t pack2(uint32_t lo, uint32_t hi) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "r"(lo), "r"(hi));
+  return r;
+}
+__device__ __forceinline__ uint64_t pack2f(float lo, float hi) {
+  return pack2(__float_as_uint(lo), __float_as_uint(hi));
+}
+__device__ __forceinline__ void unpack2(uint64_t v, uint32_t& lo, uint32_t& hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=r"(lo), "=r"(hi) : "l"(v));
+}
+__device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+  return d;
+}
+__device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
+  uint64_t d;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+__device__ __forceinline__ uint64_t sub2(uint64_t a, uint64_t b) {
+  uint64_t d;
+  asm("sub.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+__device__ __forceinline__ uint64_t add2_rm(uint64_t a, uint64_t b) {
+  uint64_t d;
+  asm("add.rm.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+// three-input maximum / minimum
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+__device__ __forceinline__ float min3(float a, float b, float c) {
+  float d;
+  asm("min.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+// poly_exp2 on a packed pair; the result is the packed pair of 2^x
+__device__ __forceinline__ uint64_t poly_exp2_pair(uint64_t x2) {
+  uint32_t x0, x1;
+  unpack2(x2, x0, x1);
+  x2 = pack2f(fmaxf(__uint_as_float(x0), -126.f), fmaxf(__uint_as_float(x1), -126.f));
+  const uint64_t magic = pack2f(12582912.f, 12582912.f);
+  const uint64_t t2 = add2_rm(x2, magic);
+  const uint64_t f2 = sub2(x2, sub2(t2, magic));
+  uint64_t p2 = fma2(f2, pack2f(0.0780244917f, 0.0780244917f), pack2f(0.2260672003f, 0.2260672003f));
+  p2 = fma2(p2, f2, pack2f(0.6958335042f, 0.6958335042f));
+  p2 = fma2(p2, f2, pack2f(0.9999251962f, 0.9999251962f));
+  uint32_t p0, p1, t0, t1;
+  unpack2(p2, p0, p1);
+  unpack2(t2, t0, t1);
+  // 2^n: n sits in the low mantissa bits of t; n * 2^23 added into the exponent field
+  p0 += t0 << 23;
+  p1 += t1 << 23;
+  return pack2(p0, p1);
 }
 // two exp2 per MUFU operation, fp16 in and out (inputs here are <= ~0, results in [0, 1])
 __device__ __forceinline__ uint32_t exp2_half2(uint32_t x) {
