@@ -38,10 +38,10 @@ EncodeTiledFn get_encode_fn() {
   return fn;
 }
 
-// fp16 (Z, N, H, D) tensor with element strides -> 4-D map (D, N, H, Z), box 64 x 128 x 1 x 1,
-// 128-byte swizzle, zero fill outside the tensor
+// fp16 (Z, N, H, D) tensor with element strides -> 4-D map (D, N, H, Z), box 64 x box_rows x 1
+// x 1, 128-byte swizzle, zero fill outside the tensor
 int make_tensor_map(CUtensorMap* map, const void* base, int Z, int N, int H, int D,
-                    const FmhaStrides& s) {
+                    const FmhaStrides& s, unsigned box_rows = 128) {
   EncodeTiledFn encode = get_encode_fn();
   if (encode == nullptr) return FMHA_ERR_NO_DEVICE;
   // a stride of a size-1 dimension is never used for addressing; make it well-formed
@@ -50,7 +50,7 @@ int make_tensor_map(CUtensorMap* map, const void* base, int Z, int N, int H, int
   const int64_t batch = (Z > 1) ? s.batch : row * N;
   const cuuint64_t dims[4] = {(cuuint64_t)D, (cuuint64_t)N, (cuuint64_t)H, (cuuint64_t)Z};
   const cuuint64_t strides[3] = {(cuuint64_t)row * 2, (cuuint64_t)head * 2, (cuuint64_t)batch * 2};
-  const cuuint32_t box[4] = {64, 128, 1, 1};
+  const cuuint32_t box[4] = {64, box_rows, 1, 1};
   const cuuint32_t estr[4] = {1, 1, 1, 1};
   const CUresult r = encode(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4, const_cast<void*>(base), dims,
                             strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
@@ -134,8 +134,11 @@ int launch_fwd(const FmhaFwdParams* p, cudaStream_t stream) {
   CUtensorMap tq, tk, tv, to;
   int rc;
   if ((rc = make_tensor_map(&tq, p->q, p->batch, p->seqlen_q, p->heads, D, p->q_strides))) return rc;
-  if ((rc = make_tensor_map(&tk, p->k, p->batch, p->seqlen_k, p->heads, D, p->k_strides))) return rc;
-  if ((rc = make_tensor_map(&tv, p->v, p->batch, p->seqlen_k, p->heads, D, p->v_strides))) return rc;
+  // K and V are loaded in half tiles of kStepN rows
+  if ((rc = make_tensor_map(&tk, p->k, p->batch, p->seqlen_k, p->heads, D, p->k_strides, T::kStepN)))
+    return rc;
+  if ((rc = make_tensor_map(&tv, p->v, p->batch, p->seqlen_k, p->heads, D, p->v_strides, T::kStepN)))
+    return rc;
   if ((rc = make_tensor_map(&to, p->o, p->batch, p->seqlen_q, p->heads, D, p->o_strides))) return rc;
   fmha::FwdKernelParams kp;
   kp.lse = p->lse;

@@ -4,28 +4,33 @@
 // same mathematics (online softmax over KV tiles, running max / sum, O rescale), none of its
 // structure.  The kernel is PERSISTENT: one CTA per SM walks a list of work items; a work item
 // is 256 query rows (two 128-row tiles) of one (batch, head), processed against the KV sequence
-// in 128-row tiles:
+// in 128-row tiles, each consumed in two 64-row halves ("steps"):
 //
-//   warp 16     TMA producer for K_0, V_0, K_1, V_1, ... through a ring of shared-memory slots
+//   warp 8      TMA producer for K_0, V_0, K_1, V_1, ... through a ring of shared-memory slots
 //               (full / empty mbarriers per slot); runs ahead into the next item as slots free
-//   warp 18     TMA producer for the two Q tiles of an item, as soon as the previous item's
+//   warp 10     TMA producer for the two Q tiles of an item, as soon as the previous item's
 //               last S = Q K^T has released them
-//   warp 17     MMA issuer: S_t = Q_t K_j^T (both operands in shared memory) and
-//               O_t += P_t V_j (P_t read from tensor memory), accumulators in tensor memory.
-//               The whole warp runs the loop so that descriptors stay in uniform registers;
-//               one elected lane issues.
-//   warps 0-7   softmax of query tile 0: two threads per row (64 score columns each), S_0 read
-//               with tcgen05.ld, online exp2 softmax, P_0 written back over S_0 as fp16, lazy
-//               O_0 rescale, epilogue
-//   warps 8-15  the same for query tile 1
+//   warp 9      MMA issuer: S_t(h) = Q_t K(h)^T (128 x 64, both operands in shared memory) and
+//               O_t += P_t(h) V(h) (P_t read from tensor memory), accumulators in tensor
+//               memory.  The whole warp runs the loop so that descriptors stay in uniform
+//               registers; one elected lane issues.
+//   warps 0-3   softmax of query tile 0: one thread per row, S_0(h) read with tcgen05.ld,
+//               online exp2 softmax, P_0(h) written back over S_0(h) as fp16, lazy O_0
+//               rescale, epilogue
+//   warps 4-7   the same for query tile 1
 //
-// While one softmax group works on its tile the tensor pipe runs the other tile's MMAs, and
-// while the groups run an item's epilogue the producer and the MMA warp already start the next
+// S_t is double buffered in tensor memory: while the softmax group works on S_t(h), the tensor
+// pipe already holds or computes S_t(h+1), so the group never waits for the latency of an MMA
+// round trip, and the MMA warp only ever waits for P.  The price is N = 64 per S MMA, which the
+// tensor pipe runs at 3/4 of the rate of N = 128.
+//
+// While the groups run an item's epilogue the producer and the MMA warp already start the next
 // item (its Q / K loads and first S = Q K^T), so that the load latency at the head of an item
 // and the store at its tail are hidden.
 //
-// Tensor memory (512 columns): S_0 [0,128) S_1 [128,256) O_0 [256,256+D) O_1 [256+D,256+2D);
-// P_t aliases the first 64 columns of S_t (two fp16 per 32-bit column).
+// Tensor memory (512 columns): S_t buffer b at [t * 128 + b * 64, + 64); O_0 [256, 256 + D),
+// O_1 [256 + D, 256 + 2 D); P_t(h) aliases the first 32 columns of the S_t buffer it came from
+// (two fp16 per 32-bit column).
 //
 // Shared memory: rows of 64 fp16 (128 bytes) in the TMA / UMMA 128-byte swizzle.  A 128 x D
 // tile is D/64 boxes of 128 x 64, box b at byte offset b * 16384.  Per softmax group one
@@ -63,35 +68,33 @@ template <int D>
 struct FwdTraits {
   static constexpr int kBlockM = 128;  // rows per query tile
   static constexpr int kTilesM = 2;    // query tiles per work item
-  static constexpr int kBlockN = 128;  // rows per KV tile
+  static constexpr int kBlockN = 128;  // rows per KV tile (one TMA load)
+  static constexpr int kStepN = 64;    // KV rows per S = Q K^T / softmax / O += P V step
   static constexpr int kBoxes = D / 64;
   static constexpr int kBoxBytes = 128 * 128;  // 128 rows x 128 bytes
   static constexpr int kTileBytes = kBoxes * kBoxBytes;
-  static constexpr int kStages = (D == 128) ? 3 : 6;
-  static constexpr int kThreads = 640;  // 16 softmax warps (2 tiles x 2 column halves), 4 issue warps
+  // K and V travel in half tiles of kStepN rows: the same shared memory holds twice as many
+  // ring slots, each released as soon as its step is done, so loads run several steps ahead
+  static constexpr int kHalfBoxBytes = kStepN * 128;  // 64 rows x 128 bytes
+  static constexpr int kHalfTileBytes = kBoxes * kHalfBoxBytes;
+  static constexpr int kStages = (D == 128) ? 6 : 12;
+  static constexpr int kThreads = 384;  // softmax 0, softmax 1, {TMA, MMA, 2 idle} warpgroups
   // Q tiles, K/V ring, one output staging tile per softmax group
-  static constexpr int kSmemBytes = 1024 + (kTilesM + kStages + 2) * kTileBytes;
+  static constexpr int kSmemBytes = 1024 + (kTilesM + 2) * kTileBytes + kStages * kHalfTileBytes;
   static constexpr int kTmemCols = 512;
-  static constexpr uint32_t kIdescQK = umma_idesc_f16(128, kBlockN, 0, 0);
+  static constexpr uint32_t kIdescQK = umma_idesc_f16(128, kStepN, 0, 0);
   static constexpr uint32_t kIdescPV = umma_idesc_f16(128, D, 0, 1);
 };
 
-constexpr int kKvWarp = 16, kMmaWarp = 17, kQWarp = 18;
-// 640 threads start at 96 registers each.  The issuing warpgroup (warps 16-19) gives up 32 per
-// thread, which lets the four softmax warpgroups grow by 8.
 // pairs out of every 4 whose exponential is a polynomial on the FMA pipe (the rest use MUFU)
 #ifndef FMHA_FWD_POLY_PAIRS
-#define FMHA_FWD_POLY_PAIRS 1
+#define FMHA_FWD_POLY_PAIRS 0
 #endif
 constexpr int kFwdPolyPairs = FMHA_FWD_POLY_PAIRS;
-constexpr int kFwdRegsLaunch = 96, kFwdRegsIssue = 64, kFwdRegsSoftmax = 104;
-static_assert(kFwdRegsIssue <= kFwdRegsLaunch && kFwdRegsSoftmax >= kFwdRegsLaunch,
-              "setmaxnreg.dec must not raise and .inc must not lower the launch allocation");
-// setmaxnreg.inc waits until the registers are there, and the pool it draws from is what the CTA
-// was launched with (threads x launch registers), not the whole register file: asking for more
-// than the other warpgroups give back blocks for ever.
-static_assert(kFwdRegsSoftmax * 512 + kFwdRegsIssue * 128 <= kFwdRegsLaunch * 640,
-              "setmaxnreg.inc would wait for registers that no warpgroup releases");
+constexpr int kFwdRegsIssue = 88;                                 // warps 8-11
+constexpr int kFwdRegsSoftmax = 168 + (168 - kFwdRegsIssue) / 2;  // warps 0-7: 208
+static_assert(kFwdRegsIssue <= 168 && kFwdRegsSoftmax >= 168 && kFwdRegsSoftmax % 8 == 0,
+              "setmaxnreg.dec must not raise and .inc must not lower the 168 registers of the launch");
 
 // lazy rescale threshold in the log2 domain: P may grow to 2^8 before O is rescaled
 constexpr float kRescaleThreshold = 8.0f;
@@ -147,7 +150,7 @@ __device__ __forceinline__ void fwd_item_extent(const FwdKernelParams& p, int q0
 }
 
 template <int D>
-__global__ void __launch_bounds__(640, 1)
+__global__ void __launch_bounds__(384, 1)
     fmha_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                     const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_o,
                     const FwdKernelParams p) {
@@ -157,11 +160,14 @@ __global__ void __launch_bounds__(640, 1)
   __shared__ uint64_t bar_q_free[2];   // the last S_t = Q_t K^T of the item is done: Q_t reusable
   __shared__ uint64_t bar_kv_full[T::kStages];
   __shared__ uint64_t bar_kv_empty[T::kStages];
-  __shared__ uint64_t bar_s_full[2];
-  __shared__ uint64_t bar_p_full[2];
+  __shared__ uint64_t bar_s_full[2][2];  // [tile][buffer]
+  __shared__ uint64_t bar_pv_done[2];    // O_t += P_t(h) V(h) has completed
+  // One barrier per S/P buffer: a softmax warp may be a step ahead of its neighbours, and its
+  // arrival for step h+1 must not be counted towards step h.  Per buffer that cannot happen:
+  // the buffer's next S only exists after everybody's P of this step has been consumed.
+  __shared__ uint64_t bar_p_full[2][2];  // [tile][buffer]
   __shared__ uint64_t bar_o_full[2];
   __shared__ uint64_t bar_o_read[2];   // the softmax group has O_t in registers: O_t reusable
-  __shared__ float row_xch[2][128];    // per tile: row statistics passed between the two halves
   __shared__ uint32_t tmem_base_slot;
   __shared__ int abort_word;
   __shared__ int skip_cta;
@@ -180,25 +186,29 @@ __global__ void __launch_bounds__(640, 1)
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const uint32_t q_smem = smem_base;                                    // 2 query tiles
   const uint32_t ring_smem = smem_base + T::kTilesM * T::kTileBytes;    // K/V ring
-  const uint32_t ostage_smem = ring_smem + T::kStages * T::kTileBytes;  // 2 output tiles
+  const uint32_t ostage_smem = ring_smem + T::kStages * T::kHalfTileBytes;  // 2 output tiles
 
   // ---- set-up: barriers (thread 0), tensor memory (warp 9)
   if (threadIdx.x == 0) {
     for (int s = 0; s < T::kStages; ++s) {
       mbar_init(smem_u32(&bar_kv_full[s]), 1);
-      mbar_init(smem_u32(&bar_kv_empty[s]), 1);
+      mbar_init(smem_u32(&bar_kv_empty[s]), 2);  // one release by each MMA warp
     }
     for (int t = 0; t < 2; ++t) {
       mbar_init(smem_u32(&bar_q_full[t]), 1);
       mbar_init(smem_u32(&bar_q_free[t]), 1);
-      mbar_init(smem_u32(&bar_s_full[t]), 1);
-      mbar_init(smem_u32(&bar_p_full[t]), 256);
+      mbar_init(smem_u32(&bar_s_full[t][0]), 1);
+      mbar_init(smem_u32(&bar_s_full[t][1]), 1);
+      mbar_init(smem_u32(&bar_pv_done[t]), 1);
+      // one arrival per softmax warp: 128 arrivals on one word are 128 serialised atomics
+      mbar_init(smem_u32(&bar_p_full[t][0]), 4);
+      mbar_init(smem_u32(&bar_p_full[t][1]), 4);
       mbar_init(smem_u32(&bar_o_full[t]), 1);
-      mbar_init(smem_u32(&bar_o_read[t]), 256);
+      mbar_init(smem_u32(&bar_o_read[t]), 4);
     }
     fence_barrier_init();
   }
-  if (warp == kMmaWarp) {
+  if (warp == 9) {
     tmem_alloc(smem_u32(&tmem_base_slot), T::kTmemCols);
     tmem_relinquish();
   }
@@ -210,9 +220,12 @@ __global__ void __launch_bounds__(640, 1)
   FwdWorkIter work(blockIdx.x, gridDim.x, p.num_q_blocks, p.num_heads_total);
   int zh, qb;
 
-  if (warp >= 16) {
+  // Register budget: 384 threads leave 168 per thread.  The producer / MMA warpgroup hands part
+  // of its share to the softmax warpgroups, whose threads hold a 128-column row of S.  Each
+  // setmaxnreg sits at the top of its warpgroup's own branch.
+  if (warp >= 8) {
     reg_dealloc<kFwdRegsIssue>();
-    if (warp == kKvWarp) {
+    if (warp == 8) {
       // =========================== TMA producer (converged warp, elected issue) ==========
       if (elect_one()) {
         tma_prefetch_desc(&tm_q);
@@ -227,7 +240,10 @@ __global__ void __launch_bounds__(640, 1)
         const int q0 = qb * (T::kBlockM * T::kTilesM);
         int n_kv[2];
         fwd_item_extent<D>(p, q0, n_kv);
-        const int n_loads = 2 * max(n_kv[0], n_kv[1]);  // K_0, V_0, K_1, V_1, ...
+        // half tiles in the order the MMA warp needs them: K(0) K(1) | V(0) K(2) | V(1) K(3) |
+        // ... | V(nh-2) | V(nh-1)
+        const int nh = 2 * max(n_kv[0], n_kv[1]);
+        const int n_loads = 2 * nh;
         for (int it = 0; it < n_loads; ++it, ++kv_it) {
           const uint32_t slot = kv_it % T::kStages;
           const uint32_t round = kv_it / T::kStages;
@@ -236,20 +252,31 @@ __global__ void __launch_bounds__(640, 1)
             ok = false;
             break;
           }
+          bool is_v;
+          int half_idx;
+          if (it < 2) {
+            is_v = false;
+            half_idx = it;
+          } else if (it == n_loads - 1) {
+            is_v = true;
+            half_idx = nh - 1;
+          } else {
+            is_v = (it & 1) == 0;
+            half_idx = is_v ? (it - 2) / 2 : (it - 3) / 2 + 2;
+          }
           if (elect_one()) {
             const uint32_t fbar = smem_u32(&bar_kv_full[slot]);
-            mbar_arrive_expect_tx(fbar, T::kTileBytes);
-            const CUtensorMap* tm = (it & 1) ? &tm_v : &tm_k;
-            const int row = (it >> 1) * T::kBlockN;
+            mbar_arrive_expect_tx(fbar, T::kHalfTileBytes);
+            const CUtensorMap* tm = is_v ? &tm_v : &tm_k;
 #pragma unroll
             for (int b = 0; b < T::kBoxes; ++b)
-              tma_load_4d(ring_smem + slot * T::kTileBytes + b * T::kBoxBytes, tm, fbar, b * 64,
-                          row, h, z);
+              tma_load_4d(ring_smem + slot * T::kHalfTileBytes + b * T::kHalfBoxBytes, tm, fbar,
+                          b * 64, half_idx * T::kStepN, h, z);
           }
           __syncwarp();
         }
       }
-    } else if (warp == kQWarp) {
+    } else if (warp == 10) {
       // =========================== Q producer ===========================
       // its own warp, so that waiting for the Q buffers of the running item never holds back
       // the K/V prefetch of the next one
@@ -268,7 +295,6 @@ __global__ void __launch_bounds__(640, 1)
             ok = false;
             break;
           }
-          FMHA_TL(2, (int)items * 16 + 13, t);
           if (elect_one()) {
             const uint32_t qbar = smem_u32(&bar_q_full[t]);
             mbar_arrive_expect_tx(qbar, T::kTileBytes);
@@ -296,157 +322,179 @@ __global__ void __launch_bounds__(640, 1)
           __syncwarp();
         }
       }
-    } else if (warp == kMmaWarp) {
-      // =========================== MMA issuer (converged warp, elected issue) ============
+    } else if (warp == 9 || warp == 11) {
+      // =========================== MMA issuers, one warp per query tile ===================
+      // Two issuers, because the tensor pipe queues very little: whenever a single issuer sat in
+      // a barrier wait between two blocks of MMAs the pipe ran dry.  With one warp per tile the
+      // other warp's MMAs fill those gaps.
+      // (converged warp, elected issue)
       // All 32 lanes run the loop so that addresses and descriptors live in uniform registers;
       // a loop run by one lane only makes every operand a per-thread value that has to be moved
       // to a uniform register before each tcgen05.mma, and the issue rate falls below the
       // tensor pipe's 64 cycles per 128x128x16 MMA.
       const uint32_t q_lo0 = umma_desc_lo(q_smem, kLboKMajor);
-      auto issue_qk = [&](int t, uint32_t k_addr) {
-        const uint32_t d = tmem_base + t * 128;
+      // S_t buffer `buf` = Q_t K(h)^T, K(h) = the half tile at k_addr
+      auto issue_qk = [&](int t, int buf, uint32_t k_addr) {
+        const uint32_t d = tmem_base + t * 128 + buf * T::kStepN;
         const uint32_t a_lo = q_lo0 + ((t * T::kTileBytes) >> 4);
         const uint32_t b_lo = umma_desc_lo(k_addr, kLboKMajor);
 #pragma unroll
         for (int ks = 0; ks < D / 16; ++ks) {
-          const uint32_t off = ((ks >> 2) * T::kBoxBytes + (ks & 3) * 32) >> 4;
-          umma_ss_elect(d, a_lo + off, b_lo + off, T::kIdescQK, ks > 0 ? 1u : 0u);
+          const uint32_t a_off = ((ks >> 2) * T::kBoxBytes + (ks & 3) * 32) >> 4;
+          const uint32_t b_off = ((ks >> 2) * T::kHalfBoxBytes + (ks & 3) * 32) >> 4;
+          umma_ss_elect(d, a_lo + a_off, b_lo + b_off, T::kIdescQK, ks > 0 ? 1u : 0u);
         }
       };
-      auto issue_pv = [&](int t, uint32_t v_addr, bool accumulate) {
+      // O_t (+)= P_t (in S_t buffer `buf`) V(h), V(h) = the half tile at v_addr; its 64-column
+      // boxes are kHalfBoxBytes apart
+      auto issue_pv = [&](int t, int buf, uint32_t v_addr, bool accumulate) {
         const uint32_t d = tmem_base + 256 + t * D;
-        const uint32_t a = tmem_base + t * 128;
-        const uint32_t b_lo = umma_desc_lo(v_addr, kLboMnMajor);
+        const uint32_t a = tmem_base + t * 128 + buf * T::kStepN;
+        const uint32_t b_lo = umma_desc_lo(v_addr, T::kHalfBoxBytes);
 #pragma unroll
-        for (int ks = 0; ks < T::kBlockN / 16; ++ks)
+        for (int ks = 0; ks < T::kStepN / 16; ++ks)
           umma_ts_elect(d, a + ks * 8, b_lo + ((ks * 2048) >> 4), T::kIdescPV,
                         (accumulate || ks > 0) ? 1u : 0u);
       };
-      uint32_t items = 0, kv_it = 0;
-      int tl_base = 0;  // timeline slot offset of the current item (debug builds)
-      uint32_t p_cnt[2] = {0, 0};  // P_t tiles consumed so far (phase of p_full[t])
-      uint32_t o_cnt[2] = {0, 0};  // items in which tile t produced an O_t (phase of o_read[t])
-      bool ok = true;
-      // first S_t = Q_t K_0^T of an item (slot0 holds K_0), with the item's bookkeeping
-      auto first_qk = [&](int t, int n_t, uint32_t slot0) {
-        if (n_t > 0) {
-          issue_qk(t, ring_smem + slot0 * T::kTileBytes);
-          umma_commit_elect(smem_u32(&bar_s_full[t]));
-        }
-        // with at most one KV tile this was the item's last use of Q_t
-        if (n_t <= 1) umma_commit_elect(smem_u32(&bar_q_free[t]));
+      auto kv_addr = [&](uint32_t it) { return ring_smem + (it % T::kStages) * T::kHalfTileBytes; };
+      auto kv_wait = [&](uint32_t it, int who) {
+        return mbar_wait_warp(smem_u32(&bar_kv_full[it % T::kStages]), (it / T::kStages) & 1,
+                              &abort_word, who);
       };
+      auto kv_release = [&](uint32_t it) {
+        umma_commit_elect(smem_u32(&bar_kv_empty[it % T::kStages]));
+      };
+      const int t = (warp == 9) ? 0 : 1;  // the query tile this warp issues for
+      uint32_t items = 0, kv_it = 0;  // kv_it: half tiles consumed before this item
+      int tl_base = 0;     // timeline slot offset of the current item (debug builds)
+      uint32_t p_cnt = 0;  // P_t steps consumed so far (even at item boundaries)
+      uint32_t o_cnt = 0;  // items in which tile t produced an O_t (phase of o_read[t])
+      bool ok = true;
       while (ok && work.next(zh, qb)) {
         const int q0 = qb * (T::kBlockM * T::kTilesM);
         int n_kv[2];
         fwd_item_extent<D>(p, q0, n_kv);
         const int n_max = max(n_kv[0], n_kv[1]);
         if (n_max == 0) continue;
+        const int nh = 2 * n_kv[t];  // steps of this tile
+        const int nhm = 2 * n_max;   // steps of the item (the K/V ring serves both tiles)
         {
-          const uint32_t slot0 = kv_it % T::kStages;
+          // the first two S_t of the item, one per buffer, from K(0) and K(1)
+          ok = ok && mbar_wait_warp(smem_u32(&bar_q_full[t]), items & 1, &abort_word, 3);
 #pragma unroll
-          for (int t = 0; t < 2; ++t) {
-            ok = ok && mbar_wait_warp(smem_u32(&bar_q_full[t]), items & 1, &abort_word, 3) &&
-                 mbar_wait_warp(smem_u32(&bar_kv_full[slot0]), (kv_it / T::kStages) & 1,
-                                &abort_word, 4);
+          for (int b = 0; b < 2; ++b) {
+            ok = ok && kv_wait(kv_it + b, 4);
             if (!ok) break;
             tc_fence_after();
-            first_qk(t, n_kv[t], slot0);
-          }
-          if (!ok) break;
-          umma_commit_elect(smem_u32(&bar_kv_empty[slot0]));
-        }
-        for (int j = 0; ok && j < n_max; ++j) {
-          const uint32_t it_v = kv_it + 2 * j + 1;
-          const uint32_t slot_v = it_v % T::kStages;
-          if (!mbar_wait_warp(smem_u32(&bar_kv_full[slot_v]), (it_v / T::kStages) & 1, &abort_word,
-                              5)) {
-            ok = false;
-            break;
-          }
-          const bool have_next = (j + 1 < n_max);
-          const uint32_t it_k = it_v + 1;
-          const uint32_t slot_k = it_k % T::kStages;
-          bool k_ready = false;
-#pragma unroll
-          for (int t = 0; t < 2; ++t) {
-            if (j < n_kv[t]) {
-              FMHA_TL(2, tl_base + j, t * 4 + 0);
-              if (!mbar_wait_warp(smem_u32(&bar_p_full[t]), p_cnt[t] & 1, &abort_word, 6)) {
-                ok = false;
-                break;
-              }
-              ++p_cnt[t];
-              // the first O_t += of an item overwrites O_t: the previous item's epilogue must
-              // have read it out of tensor memory
-              if (j == 0 && o_cnt[t] > 0 &&
-                  !mbar_wait_warp(smem_u32(&bar_o_read[t]), (o_cnt[t] - 1) & 1, &abort_word, 7)) {
-                ok = false;
-                break;
-              }
-              tc_fence_after();
-              FMHA_TL(2, tl_base + j, t * 4 + 1);
-              issue_pv(t, ring_smem + slot_v * T::kTileBytes, j > 0);
-              FMHA_TL(2, tl_base + j, t * 4 + 2);
-              if (j + 1 < n_kv[t]) {
-                if (!k_ready) {
-                  if (!mbar_wait_warp(smem_u32(&bar_kv_full[slot_k]), (it_k / T::kStages) & 1,
-                                      &abort_word, 8)) {
-                    ok = false;
-                    break;
-                  }
-                  tc_fence_after();
-                  k_ready = true;
-                }
-                issue_qk(t, ring_smem + slot_k * T::kTileBytes);
-                umma_commit_elect(smem_u32(&bar_s_full[t]));
-                if (j + 2 == n_kv[t]) umma_commit_elect(smem_u32(&bar_q_free[t]));
-              } else {
-                umma_commit_elect(smem_u32(&bar_o_full[t]));
-                ++o_cnt[t];
-              }
-              FMHA_TL(2, tl_base + j, t * 4 + 3);
+            if (nh > 0) {
+              issue_qk(t, b, kv_addr(kv_it + b));
+              umma_commit_elect(smem_u32(&bar_s_full[t][b]));
             }
           }
           if (!ok) break;
-          umma_commit_elect(smem_u32(&bar_kv_empty[slot_v]));
-          if (have_next) umma_commit_elect(smem_u32(&bar_kv_empty[slot_k]));
+          // with at most one KV tile these were the item's last uses of Q_t
+          if (nh <= 2) umma_commit_elect(smem_u32(&bar_q_free[t]));
+          kv_release(kv_it);
+          kv_release(kv_it + 1);
         }
-        kv_it += 2 * n_max;
+        for (int h = 0; ok && h < nhm; ++h) {
+          const int buf = h & 1;
+          // position of V(h) and K(h+2) in the item's load order
+          const uint32_t it_v = kv_it + 2 + 2 * h - (h == nhm - 1 ? 1 : 0);
+          const uint32_t it_k = kv_it + 3 + 2 * h;
+          const bool have_k = (h + 2 < nhm);
+          bool all_ready = false;
+          // a slot is only released after it was seen full, used or not: otherwise this warp
+          // could release the same slot twice within one round of the ring
+          {
+            // the step's three waits (V(h), P_t(h), K(h+2)) in one go when all are ready, as
+            // they normally are; the bounded waits below then return at their first probe
+            const uint32_t bv = smem_u32(&bar_kv_full[it_v % T::kStages]);
+            const uint32_t pv = (it_v / T::kStages) & 1;
+            const bool use_p = h < nh, use_k = have_k;
+            const uint32_t bp = use_p ? smem_u32(&bar_p_full[t][buf]) : bv;
+            const uint32_t pp = use_p ? ((p_cnt >> 1) & 1) : pv;
+            const uint32_t bk = use_k ? smem_u32(&bar_kv_full[it_k % T::kStages]) : bv;
+            const uint32_t pk = use_k ? ((it_k / T::kStages) & 1) : pv;
+            all_ready = __all_sync(0xffffffffu, mbar_try_wait3(bv, pv, bp, pp, bk, pk));
+          }
+          if (!all_ready && !kv_wait(it_v, 5)) {
+            ok = false;
+            break;
+          }
+          if (h < nh) {
+            FMHA_TL(2, tl_base + h, t * 4 + 0);
+            if (!all_ready &&
+                !mbar_wait_warp(smem_u32(&bar_p_full[t][buf]), (p_cnt >> 1) & 1, &abort_word, 6)) {
+              ok = false;
+              break;
+            }
+            ++p_cnt;
+            // the first O_t += of an item overwrites O_t: the previous item's epilogue must
+            // have read it out of tensor memory
+            if (h == 0 && o_cnt > 0 &&
+                !mbar_wait_warp(smem_u32(&bar_o_read[t]), (o_cnt - 1) & 1, &abort_word, 7)) {
+              ok = false;
+              break;
+            }
+            tc_fence_after();
+            FMHA_TL(2, tl_base + h, t * 4 + 1);
+            issue_pv(t, buf, kv_addr(it_v), h > 0);
+            umma_commit_elect(smem_u32(&bar_pv_done[t]));
+            FMHA_TL(2, tl_base + h, t * 4 + 2);
+            if (h + 2 < nh) {
+              // S_t(h+2) goes where P_t(h) was; the tensor pipe runs one warp's MMAs in order
+              if (!all_ready) {
+                if (!kv_wait(it_k, 8)) {
+                  ok = false;
+                  break;
+                }
+                tc_fence_after();
+              }
+              issue_qk(t, buf, kv_addr(it_k));
+              umma_commit_elect(smem_u32(&bar_s_full[t][buf]));
+              if (h + 3 == nh) umma_commit_elect(smem_u32(&bar_q_free[t]));
+            } else {
+              if (have_k && !all_ready && !kv_wait(it_k, 8)) {
+                ok = false;
+                break;
+              }
+              if (h + 1 == nh) {
+                umma_commit_elect(smem_u32(&bar_o_full[t]));
+                ++o_cnt;
+              }
+            }
+            FMHA_TL(2, tl_base + h, t * 4 + 3);
+          } else if (have_k && !all_ready && !kv_wait(it_k, 8)) {
+            ok = false;
+            break;
+          }
+          kv_release(it_v);
+          if (have_k) kv_release(it_k);
+        }
+        kv_it += 2 * nhm;
         ++items;
-        tl_base += 16;
+        tl_base += 64;
       }
     }
   } else {
     // =========================== softmax / epilogue ===========================
     reg_alloc<kFwdRegsSoftmax>();
-    // Two threads per query row (warps t*8 + hf*4 + quad: tile t, column half hf, TMEM lane
-    // quadrant quad), each owning 64 of the 128 score columns.  One warp per scheduler issues at
-    // most every other cycle; with two warps of the active tile on every scheduler the pass over
-    // a tile is bound by the MUFU unit instead of by instruction issue.
-    const int t = warp >> 3;         // query tile
-    const int hf = (warp >> 2) & 1;  // column half of this thread
-    const int quad = warp & 3;       // TMEM lane quadrant of this warp
+    const int t = warp >> 2;    // query tile of this warpgroup
+    const int quad = warp & 3;  // TMEM lane quadrant of this warp
     const int row_in_tile = quad * 32 + lane;
     const uint32_t lane_addr = uint32_t(quad * 32) << 16;
-    const uint32_t tS = tmem_base + lane_addr + t * 128 + hf * 64;          // my 64 score columns
-    const uint32_t tP = tmem_base + lane_addr + t * 128 + hf * 32;          // my 32 packed P columns
-    const uint32_t tO = tmem_base + lane_addr + 256 + t * D + hf * (D / 2); // my D/2 output columns
+    const uint32_t tS = tmem_base + lane_addr + t * 128;
+    const uint32_t tO = tmem_base + lane_addr + 256 + t * D;
     const uint32_t o_stage = ostage_smem + t * T::kTileBytes;
-    const uint32_t xch = smem_u32(&row_xch[t][row_in_tile]);  // fp32 view: row sums
-    // 16-bit view of the same words: row references, one slot per thread of the row
-    const uint32_t xch_mine = smem_u32(&row_xch[t][0]) + (hf * 128 + row_in_tile) * 2;
-    const uint32_t xch_other = smem_u32(&row_xch[t][0]) + ((hf ^ 1) * 128 + row_in_tile) * 2;
-    const uint32_t bar_id = 1 + t;               // named barrier of this tile's 256 threads
-    const uint32_t pair_bar = 3 + t * 4 + quad;  // named barrier of the two warps sharing my rows
-    bool stored = false;  // a TMA store of this tile may still be reading the staging tile
+    bool stored = false;  // a TMA store of this group may still be reading the staging box
     const float c = p.scale_log2;
     // a masked score must give exp2(s * c - m * c) = 0 whatever the sign of c
     const float mask_val = (c >= 0.f) ? -CUDART_INF_F : CUDART_INF_F;
-    const bool tl = (lane == 0 && quad == 0 && hf == 0);
-    uint32_t s_cnt = 0;  // S_t tiles consumed so far (phase of s_full[t])
-    uint32_t o_cnt = 0;  // O_t tiles read so far (phase of o_full[t])
-    int tl_base = 0;     // timeline slot offset of the current item (debug builds)
+    const bool tl = (lane == 0 && quad == 0);
+    uint32_t step = 0;    // steps of this tile so far, over all items (even at item boundaries)
+    uint32_t o_cnt = 0;   // O_t tiles read so far (phase of o_full[t])
+    int tl_base = 0;      // timeline slot offset of the current item (debug builds)
 
     while (work.next(zh, qb)) {
       const int z = zh / p.heads, h = zh % p.heads;
@@ -462,24 +510,25 @@ __global__ void __launch_bounds__(640, 1)
       const int row_limit = (int)lim_ll;  // last visible key of this row (-1 = none)
 
       float m_ref = mask_val;  // reference score of the running softmax (raw, unscaled)
-      float l = 0.f;           // this thread's share of the running sum of exp2((s - m_ref) * c)
+      float l = 0.f;           // running sum of exp2((s - m_ref) * c)
 
-      for (int j = 0; j < n; ++j, ++s_cnt) {
-        if (tl) FMHA_TL(t, tl_base + j, 0);
-        // on a time-out keep going: every later wait returns at once, and all threads of the
-        // tile still meet at the named barriers
-        mbar_wait(smem_u32(&bar_s_full[t]), s_cnt & 1, &abort_word, 9);
+      for (int hs = 0; hs < 2 * n; ++hs, ++step) {
+        const uint32_t buf = step & 1;  // == hs & 1
+        const uint32_t tSb = tS + buf * T::kStepN;
+        if (tl) FMHA_TL(t, tl_base + hs, 0);
+        // on a time-out keep going: every later wait returns at once, and all 128 threads of
+        // the group still meet at the named barriers of the epilogue
+        mbar_wait(smem_u32(&bar_s_full[t][buf]), (step >> 1) & 1, &abort_word, 9);
         tc_fence_after();
-        if (tl) FMHA_TL(t, tl_base + j, 1);
+        if (tl) FMHA_TL(t, tl_base + hs, 1);
         uint32_t s[2][32];
-        tmem_ld32(tS + 0, s[0]);
-        tmem_ld32(tS + 32, s[1]);
+        tmem_ld32(tSb + 0, s[0]);
+        tmem_ld32(tSb + 32, s[1]);
         tmem_wait_ld();
-        if (tl) FMHA_TL(t, tl_base + j, 2);
+        if (tl) FMHA_TL(t, tl_base + hs, 2);
 
-        // columns > lim of this tile are masked (lim counted within my 64 columns)
-        const int lim = row_limit - j * T::kBlockN - hf * 64;
-        if (lim < 63) {
+        const int lim = row_limit - hs * T::kStepN;  // columns > lim of this step are masked
+        if (lim < T::kStepN - 1) {
 #pragma unroll
           for (int cc = 0; cc < 2; ++cc)
 #pragma unroll
@@ -487,7 +536,7 @@ __global__ void __launch_bounds__(640, 1)
               if (cc * 32 + i > lim) s[cc][i] = __float_as_uint(mask_val);
         }
 
-        // extreme of my 64 scores: max when c >= 0, min when c < 0, so that m * c = max(s * c)
+        // row extreme: max of s when c >= 0, min when c < 0, so that m * c = max(s * c)
         float mx0 = __uint_as_float(s[0][0]), mx1 = __uint_as_float(s[1][0]);
         if (c >= 0.f) {
           mx0 = fmaxf(mx0, __uint_as_float(s[0][1]));
@@ -507,58 +556,41 @@ __global__ void __launch_bounds__(640, 1)
           }
         }
         float mx = (c >= 0.f) ? fmaxf(mx0, mx1) : fminf(mx0, mx1);
-        // The row reference has to be the same number in both threads of the row, but not the
-        // exact extreme: anything between the extreme and a little beyond it will do.  Each
-        // thread rounds its value away from the scores to 16 bits, the two swap them through
-        // shared memory, and both take the extreme of the same two numbers.
-        // The barrier of the pair also orders half 0's tcgen05.ld of S columns 32..63 before
-        // half 1 overwrites them with its packed P.  The slot is reused every tile: the partner
-        // has read it before it arrives on p_full, which the next S tile is ordered after.
-        {
-          uint32_t b = __float_as_uint(mx);
-          const bool grow = ((b >> 31) == 0u) == (c >= 0.f);  // larger magnitude = away
-          b = (grow ? b + 0xffffu : b) & 0xffff0000u;
-          asm volatile("st.shared.u16 [%0], %1;" ::"r"(xch_mine), "h"((uint16_t)(b >> 16))
-                       : "memory");
-          named_bar_sync(pair_bar, 64);
-          uint16_t o16;
-          asm volatile("ld.shared.u16 %0, [%1];" : "=h"(o16) : "r"(xch_other) : "memory");
-          const float other = __uint_as_float((uint32_t)o16 << 16);
-          mx = __uint_as_float(b);
-          mx = (c >= 0.f) ? fmaxf(mx, other) : fminf(mx, other);
-        }
+        if (FMHA_ABLATE & 2) mx = __uint_as_float(s[0][0]);
 
-        if (j == 0) {
+        if (hs == 0) {
           m_ref = mx;
         } else {
           const float m_new = (c >= 0.f) ? fmaxf(m_ref, mx) : fminf(m_ref, mx);
-          // growth of the scaled maximum; NaN (inf - inf) compares false.  Both threads of a
-          // row see the same numbers, and both half-warps hold the same rows: same decision.
+          // growth of the scaled maximum; NaN (inf - inf) compares false
           const bool need = (m_new - m_ref) * c > kRescaleThreshold;
           if (__any_sync(0xffffffffu, need)) {
-            // O_t is idle here: S_t(j) is committed after O_t += P_t V_(j-1) was issued
+            // O_t may still be accumulating the previous step: wait for that MMA.  The next
+            // one is not issued before this thread has arrived on p_full.
+            mbar_wait(smem_u32(&bar_pv_done[t]), (step - 1) & 1, &abort_word, 11);
+            tc_fence_after();
             const float alpha = isinf(m_new) ? 1.f : fast_exp2((m_ref - m_new) * c);
             l *= alpha;
             m_ref = m_new;
 #pragma unroll
-            for (int cc = 0; cc < D / 32; ++cc) {  // my half of the output columns
-              uint32_t o[16];
-              tmem_ld16(tO + cc * 16, o);
+            for (int cc = 0; cc < D / 32; ++cc) {
+              uint32_t o[32];
+              tmem_ld32(tO + cc * 32, o);
               tmem_wait_ld();
 #pragma unroll
-              for (int i = 0; i < 16; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
-              tmem_st16(tO + cc * 16, o);
+              for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+              tmem_st32(tO + cc * 32, o);
             }
           }
         }
 
-        if (tl) FMHA_TL(t, tl_base + j, 3);
+        if (tl) FMHA_TL(t, tl_base + hs, 3);
         const float neg_mc = isinf(m_ref) ? 0.f : -m_ref * c;
         const uint64_t c2 = pack2f(c, c), nm2 = pack2f(neg_mc, neg_mc);
         uint64_t la = pack2f(0.f, 0.f), lb = pack2f(0.f, 0.f);
+        uint32_t pk[32];  // 64 scores -> 32 packed columns of P
 #pragma unroll
-        for (int cc = 0; cc < 2; ++cc) {  // 32 scores -> 16 packed columns of P at a time
-          uint32_t pk[16];
+        for (int cc = 0; cc < 2; ++cc) {
 #pragma unroll
           for (int i = 0; i < 32; i += 2) {
             const uint64_t x2 = fma2(pack2(s[cc][i], s[cc][i + 1]), c2, nm2);
@@ -574,87 +606,69 @@ __global__ void __launch_bounds__(640, 1)
             if (i & 2) lb = add2(lb, p2); else la = add2(la, p2);
             uint32_t p0, p1;
             unpack2(p2, p0, p1);
-            pk[i >> 1] = pack_half2(__uint_as_float(p0), __uint_as_float(p1));
+            pk[cc * 16 + (i >> 1)] = pack_half2(__uint_as_float(p0), __uint_as_float(p1));
           }
-          tmem_st16(tP + cc * 16, pk);
         }
+        if (!(FMHA_ABLATE & 4)) tmem_st32(tSb, pk);
         {
           uint32_t a0, a1;
           unpack2(add2(la, lb), a0, a1);
           l += __uint_as_float(a0) + __uint_as_float(a1);
         }
-        if (tl) FMHA_TL(t, tl_base + j, 4);
+        if (tl) FMHA_TL(t, tl_base + hs, 4);
         tmem_wait_st();
         tc_fence_before();
-        mbar_arrive(smem_u32(&bar_p_full[t]));
-        if (tl) FMHA_TL(t, tl_base + j, 5);
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(&bar_p_full[t][buf]));
+        if (tl) FMHA_TL(t, tl_base + hs, 5);
       }
-      if (tl) FMHA_TL(t, tl_base + 15, 6);
+      if (tl) FMHA_TL(t, tl_base + 31, 6);
 
-      // ---- epilogue: my half of O_t / l -> fp16 registers (tensor memory released) ->
-      //      staging tile -> TMA store; LSE
+      // ---- epilogue: O_t / l -> fp16 registers (tensor memory released) -> staging box -> TMA
+      //      store; LSE
       if (tile_valid) {
+        uint32_t oh[D / 2];  // the output row, fp16 pairs
         if (n > 0) {
-          // O_t complete.  It also tells that every thread of the tile is through its last
-          // exchange of row references, whose 16-bit slots the row sums below reuse.
           mbar_wait(smem_u32(&bar_o_full[t]), o_cnt & 1, &abort_word, 10);
           ++o_cnt;
           tc_fence_after();
-          if (tl) FMHA_TL(t, tl_base + 15, 8);
-        }
-        // the row sum: half 1 hands its share to half 0, which hands the total back
-        if (hf == 1) asm volatile("st.shared.f32 [%0], %1;" ::"r"(xch), "f"(l) : "memory");
-        named_bar_sync(bar_id, 256);
-        if (hf == 0) {
-          float other;
-          asm volatile("ld.shared.f32 %0, [%1];" : "=f"(other) : "r"(xch) : "memory");
-          l += other;
-          asm volatile("st.shared.f32 [%0], %1;" ::"r"(xch), "f"(l) : "memory");
-        }
-        named_bar_sync(bar_id, 256);
-        if (hf == 1) asm volatile("ld.shared.f32 %0, [%1];" : "=f"(l) : "r"(xch) : "memory");
-
-        uint32_t oh[D / 4];  // my half of the output row, fp16 pairs
-        if (n > 0) {
+          if (tl) FMHA_TL(t, tl_base + 31, 8);
           const float inv_l = (l > 0.f) ? 1.f / l : 0.f;
+          uint32_t o[D / 32][32];
 #pragma unroll
-          for (int cc = 0; cc < D / 64; ++cc) {  // 32 columns at a time keeps the registers low
-            uint32_t o[32];
-            tmem_ld32(tO + cc * 32, o);
-            tmem_wait_ld();
-            if (cc == D / 64 - 1) {  // O_t is in registers: the next item may overwrite it
-              tc_fence_before();
-              mbar_arrive(smem_u32(&bar_o_read[t]));
-              if (tl) FMHA_TL(t, tl_base + 15, 9);
-            }
+          for (int cc = 0; cc < D / 32; ++cc) tmem_ld32(tO + cc * 32, o[cc]);
+          tmem_wait_ld();
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(smem_u32(&bar_o_read[t]));
+          if (tl) FMHA_TL(t, tl_base + 31, 9);
+#pragma unroll
+          for (int cc = 0; cc < D / 32; ++cc)
 #pragma unroll
             for (int i = 0; i < 32; i += 2)
-              oh[cc * 16 + (i >> 1)] = pack_half2(__uint_as_float(o[i]) * inv_l,
-                                                  __uint_as_float(o[i + 1]) * inv_l);
-          }
+              oh[cc * 16 + (i >> 1)] = pack_half2(__uint_as_float(o[cc][i]) * inv_l,
+                                                  __uint_as_float(o[cc][i + 1]) * inv_l);
         } else {
 #pragma unroll
-          for (int i = 0; i < D / 4; ++i) oh[i] = 0u;
+          for (int i = 0; i < D / 2; ++i) oh[i] = 0u;
         }
-        if (hf == 0 && row < p.seqlen_q) {
+        if (row < p.seqlen_q) {
           const float lse =
               (l > 0.f) ? (m_ref * c + log2f(l)) * 0.6931471805599453f : -CUDART_INF_F;
           p.lse[((size_t)z * p.heads + h) * p.seqlen_q + row] = lse;
         }
-        // through the staging tile and TMA stores (per-thread stores of whole rows are
+        // through this group's staging tile and TMA stores (per-thread stores of whole rows are
         // uncoalesced and clog the load/store pipe for everybody)
-        if (row_in_tile == 0 && hf == 0 && stored) tma_wait_group_read<0>();  // previous item
-        named_bar_sync(bar_id, 256);
+        if (row_in_tile == 0 && stored) tma_wait_group_read<0>();  // previous item's store
+        named_bar_sync(1 + t, 128);
 #pragma unroll
-        for (int ch = 0; ch < D / 16; ++ch) {  // my 16-byte chunks (8 fp16 each)
-          const int gch = hf * (D / 16) + ch;  // chunk index within the whole row
-          sts128(o_stage + (gch >> 3) * T::kBoxBytes + row_in_tile * 128 +
-                     (((gch & 7) ^ (row_in_tile & 7)) << 4),
+        for (int ch = 0; ch < D / 8; ++ch)  // 16-byte chunk (8 fp16) of this row
+          sts128(o_stage + (ch >> 3) * T::kBoxBytes + row_in_tile * 128 +
+                     (((ch & 7) ^ (row_in_tile & 7)) << 4),
                  oh[ch * 4 + 0], oh[ch * 4 + 1], oh[ch * 4 + 2], oh[ch * 4 + 3]);
-        }
         fence_proxy_async_smem();
-        named_bar_sync(bar_id, 256);
-        if (row_in_tile == 0 && hf == 0) {
+        named_bar_sync(1 + t, 128);
+        if (row_in_tile == 0) {
 #pragma unroll
           for (int b = 0; b < T::kBoxes; ++b)
             tma_store_4d(&tm_o, o_stage + b * T::kBoxBytes, b * 64, q0 + t * T::kBlockM, h, z);
@@ -662,10 +676,10 @@ __global__ void __launch_bounds__(640, 1)
         }
         stored = true;
       }
-      if (tl) FMHA_TL(t, tl_base + 15, 7);
-      tl_base += 16;
+      if (tl) FMHA_TL(t, tl_base + 31, 7);
+      tl_base += 64;
     }
-    if (row_in_tile == 0 && hf == 0) tma_wait_group<0>();
+    if (row_in_tile == 0) tma_wait_group<0>();
   }
 
   // ---- teardown
@@ -676,7 +690,7 @@ __global__ void __launch_bounds__(640, 1)
     // let copies that may still be in flight land before the shared memory is released
     for (int i = 0; i < 64; ++i) __nanosleep(1000);
   }
-  if (warp == kMmaWarp) {
+  if (warp == 9) {
     tc_fence_after();
     tmem_dealloc(tmem_base, T::kTmemCols);
   }

@@ -335,6 +335,25 @@ __device__ __forceinline__ void umma_ts_elect(uint32_t d_tmem, uint32_t a_tmem, 
 __device__ __forceinline__ void umma_commit_elect(uint32_t bar) {
   if (elect_one()) umma_commit(bar);
 }
+// Three barriers tested with the three probes in flight together: a probe that finds its phase
+// complete still costs a round trip through the shared-memory pipe, and three in a row cost
+// three.  Returns true when all three phases are complete.
+__device__ __forceinline__ bool mbar_try_wait3(uint32_t bar0, uint32_t par0, uint32_t bar1,
+                                               uint32_t par1, uint32_t bar2, uint32_t par2) {
+  uint32_t r0, r1, r2;
+  asm volatile(
+      "{\n\t.reg .pred p0, p1, p2;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p0, [%3], %4;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p1, [%5], %6;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p2, [%7], %8;\n\t"
+      "selp.u32 %0, 1, 0, p0;\n\t"
+      "selp.u32 %1, 1, 0, p1;\n\t"
+      "selp.u32 %2, 1, 0, p2;\n\t}"
+      : "=r"(r0), "=r"(r1), "=r"(r2)
+      : "r"(bar0), "r"(par0), "r"(bar1), "r"(par1), "r"(bar2), "r"(par2)
+      : "memory");
+  return (r0 & r1 & r2) != 0;
+}
 // bounded wait by a whole converged warp, with a warp-uniform result
 __device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity,
                                                volatile int* abort_word, int who) {
