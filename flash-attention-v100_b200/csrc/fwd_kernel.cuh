@@ -6,14 +6,17 @@
 // is 256 query rows (two 128-row tiles) of one (batch, head), processed against the KV sequence
 // in 128-row tiles, each consumed in two 64-row halves ("steps"):
 //
-//   warp 8      TMA producer for K_0, V_0, K_1, V_1, ... through a ring of shared-memory slots
-//               (full / empty mbarriers per slot); runs ahead into the next item as slots free
+//   warp 8      TMA producer for K and V, in half tiles of 64 rows, through a ring of
+//               shared-memory slots (full / empty mbarriers per slot); a slot holds what one
+//               step consumes, V(h) and K(h+2); runs ahead into the next item as slots free
 //   warp 10     TMA producer for the two Q tiles of an item, as soon as the previous item's
 //               last S = Q K^T has released them
-//   warp 9      MMA issuer: S_t(h) = Q_t K(h)^T (128 x 64, both operands in shared memory) and
-//               O_t += P_t(h) V(h) (P_t read from tensor memory), accumulators in tensor
-//               memory.  The whole warp runs the loop so that descriptors stay in uniform
-//               registers; one elected lane issues.
+//   warps 9, 11 MMA issuers, one per query tile t: S_t(h) = Q_t K(h)^T (128 x 64, both operands
+//               in shared memory) and O_t += P_t(h) V(h) (P_t read from tensor memory),
+//               accumulators in tensor memory.  The whole warp runs the loop so that
+//               descriptors stay in uniform registers; one elected lane issues.  Two issuers
+//               because the tensor pipe queues very little: with one, every barrier wait
+//               between two blocks of MMAs let the pipe run dry.
 //   warps 0-3   softmax of query tile 0: one thread per row, S_0(h) read with tcgen05.ld,
 //               online exp2 softmax, P_0(h) written back over S_0(h) as fp16, lazy O_0
 //               rescale, epilogue
@@ -21,7 +24,7 @@
 //
 // S_t is double buffered in tensor memory: while the softmax group works on S_t(h), the tensor
 // pipe already holds or computes S_t(h+1), so the group never waits for the latency of an MMA
-// round trip, and the MMA warp only ever waits for P.  The price is N = 64 per S MMA, which the
+// round trip, and the MMA warps only ever wait for P.  The price is N = 64 per S MMA, which the
 // tensor pipe runs at 3/4 of the rate of N = 128.
 //
 // While the groups run an item's epilogue the producer and the MMA warp already start the next
@@ -33,8 +36,9 @@
 // (two fp16 per 32-bit column).
 //
 // Shared memory: rows of 64 fp16 (128 bytes) in the TMA / UMMA 128-byte swizzle.  A 128 x D
-// tile is D/64 boxes of 128 x 64, box b at byte offset b * 16384.  Per softmax group one
-// extra tile stages the output for the TMA store.
+// tile is D/64 boxes of 128 x 64, box b at byte offset b * 16384 (a 64-row half tile of K or V:
+// boxes of 64 x 64, 8192 bytes apart).  Per softmax group one extra tile stages the output for
+// the TMA store.
 //
 // Work items are paired (heaviest with lightest query block of a head) into super-items of
 // equal cost, and super-items are dealt round-robin to the CTAs: balanced without a global
@@ -77,10 +81,13 @@ struct FwdTraits {
   // ring slots, each released as soon as its step is done, so loads run several steps ahead
   static constexpr int kHalfBoxBytes = kStepN * 128;  // 64 rows x 128 bytes
   static constexpr int kHalfTileBytes = kBoxes * kHalfBoxBytes;
-  static constexpr int kStages = (D == 128) ? 6 : 12;
+  // a ring slot holds the two half tiles one step consumes: V(h) and K(h+2) (one barrier pair
+  // and one release per step); the slot of an item's head holds K(0) and K(1)
+  static constexpr int kSlotBytes = 2 * kHalfTileBytes;
+  static constexpr int kStages = (D == 128) ? 3 : 6;
   static constexpr int kThreads = 384;  // softmax 0, softmax 1, {TMA, MMA, 2 idle} warpgroups
   // Q tiles, K/V ring, one output staging tile per softmax group
-  static constexpr int kSmemBytes = 1024 + (kTilesM + 2) * kTileBytes + kStages * kHalfTileBytes;
+  static constexpr int kSmemBytes = 1024 + (kTilesM + 2) * kTileBytes + kStages * kSlotBytes;
   static constexpr int kTmemCols = 512;
   static constexpr uint32_t kIdescQK = umma_idesc_f16(128, kStepN, 0, 0);
   static constexpr uint32_t kIdescPV = umma_idesc_f16(128, D, 0, 1);
@@ -161,7 +168,7 @@ __global__ void __launch_bounds__(384, 1)
   __shared__ uint64_t bar_kv_full[T::kStages];
   __shared__ uint64_t bar_kv_empty[T::kStages];
   __shared__ uint64_t bar_s_full[2][2];  // [tile][buffer]
-  __shared__ uint64_t bar_pv_done[2];    // O_t += P_t(h) V(h) has completed
+  __shared__ uint64_t bar_pv_done[2];    // one of the last two O_t += of an item has completed
   // One barrier per S/P buffer: a softmax warp may be a step ahead of its neighbours, and its
   // arrival for step h+1 must not be counted towards step h.  Per buffer that cannot happen:
   // the buffer's next S only exists after everybody's P of this step has been consumed.
@@ -186,7 +193,7 @@ __global__ void __launch_bounds__(384, 1)
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const uint32_t q_smem = smem_base;                                    // 2 query tiles
   const uint32_t ring_smem = smem_base + T::kTilesM * T::kTileBytes;    // K/V ring
-  const uint32_t ostage_smem = ring_smem + T::kStages * T::kHalfTileBytes;  // 2 output tiles
+  const uint32_t ostage_smem = ring_smem + T::kStages * T::kSlotBytes;  // 2 output tiles
 
   // ---- set-up: barriers (thread 0), tensor memory (warp 9)
   if (threadIdx.x == 0) {
@@ -233,17 +240,17 @@ __global__ void __launch_bounds__(384, 1)
         tma_prefetch_desc(&tm_v);
       }
       __syncwarp();
-      uint32_t kv_it = 0;  // K/V tiles loaded so far (ring slot and phase)
+      uint32_t kv_it = 0;  // ring slots loaded so far (slot index and phase)
       bool ok = true;
       while (ok && work.next(zh, qb)) {
         const int z = zh / p.heads, h = zh % p.heads;
         const int q0 = qb * (T::kBlockM * T::kTilesM);
         int n_kv[2];
         fwd_item_extent<D>(p, q0, n_kv);
-        // half tiles in the order the MMA warp needs them: K(0) K(1) | V(0) K(2) | V(1) K(3) |
-        // ... | V(nh-2) | V(nh-1)
+        // slot loads in the order the MMA warps consume them:
+        //   [K(0) K(1)]  [V(0) K(2)]  [V(1) K(3)]  ...  [V(nh-3) K(nh-1)]  [V(nh-2)]  [V(nh-1)]
         const int nh = 2 * max(n_kv[0], n_kv[1]);
-        const int n_loads = 2 * nh;
+        const int n_loads = nh > 0 ? nh + 1 : 0;
         for (int it = 0; it < n_loads; ++it, ++kv_it) {
           const uint32_t slot = kv_it % T::kStages;
           const uint32_t round = kv_it / T::kStages;
@@ -252,26 +259,24 @@ __global__ void __launch_bounds__(384, 1)
             ok = false;
             break;
           }
-          bool is_v;
-          int half_idx;
-          if (it < 2) {
-            is_v = false;
-            half_idx = it;
-          } else if (it == n_loads - 1) {
-            is_v = true;
-            half_idx = nh - 1;
-          } else {
-            is_v = (it & 1) == 0;
-            half_idx = is_v ? (it - 2) / 2 : (it - 3) / 2 + 2;
-          }
+          // first and second half tile of the slot (-1 = none)
+          const int k_first = (it == 0) ? 0 : -1;               // K half in the first place
+          const int v_first = (it == 0) ? -1 : it - 1;          // V(h), h = it - 1
+          const int k_second = (it == 0) ? 1 : (it + 1 < nh ? it + 1 : -1);  // K(h+2)
           if (elect_one()) {
             const uint32_t fbar = smem_u32(&bar_kv_full[slot]);
-            mbar_arrive_expect_tx(fbar, T::kHalfTileBytes);
-            const CUtensorMap* tm = is_v ? &tm_v : &tm_k;
+            const uint32_t base = ring_smem + slot * T::kSlotBytes;
+            mbar_arrive_expect_tx(fbar, (k_second >= 0 ? 2 : 1) * T::kHalfTileBytes);
 #pragma unroll
-            for (int b = 0; b < T::kBoxes; ++b)
-              tma_load_4d(ring_smem + slot * T::kHalfTileBytes + b * T::kHalfBoxBytes, tm, fbar,
-                          b * 64, half_idx * T::kStepN, h, z);
+            for (int b = 0; b < T::kBoxes; ++b) {
+              if (k_first >= 0)
+                tma_load_4d(base + b * T::kHalfBoxBytes, &tm_k, fbar, b * 64, k_first * T::kStepN, h, z);
+              else
+                tma_load_4d(base + b * T::kHalfBoxBytes, &tm_v, fbar, b * 64, v_first * T::kStepN, h, z);
+              if (k_second >= 0)
+                tma_load_4d(base + T::kHalfTileBytes + b * T::kHalfBoxBytes, &tm_k, fbar, b * 64,
+                            k_second * T::kStepN, h, z);
+            }
           }
           __syncwarp();
         }
@@ -356,7 +361,7 @@ __global__ void __launch_bounds__(384, 1)
           umma_ts_elect(d, a + ks * 8, b_lo + ((ks * 2048) >> 4), T::kIdescPV,
                         (accumulate || ks > 0) ? 1u : 0u);
       };
-      auto kv_addr = [&](uint32_t it) { return ring_smem + (it % T::kStages) * T::kHalfTileBytes; };
+      auto kv_addr = [&](uint32_t it) { return ring_smem + (it % T::kStages) * T::kSlotBytes; };
       auto kv_wait = [&](uint32_t it, int who) {
         return mbar_wait_warp(smem_u32(&bar_kv_full[it % T::kStages]), (it / T::kStages) & 1,
                               &abort_word, who);
@@ -365,7 +370,7 @@ __global__ void __launch_bounds__(384, 1)
         umma_commit_elect(smem_u32(&bar_kv_empty[it % T::kStages]));
       };
       const int t = (warp == 9) ? 0 : 1;  // the query tile this warp issues for
-      uint32_t items = 0, kv_it = 0;  // kv_it: half tiles consumed before this item
+      uint32_t items = 0, kv_it = 0;  // kv_it: ring slots consumed before this item
       int tl_base = 0;     // timeline slot offset of the current item (debug builds)
       uint32_t p_cnt = 0;  // P_t steps consumed so far (even at item boundaries)
       uint32_t o_cnt = 0;  // items in which tile t produced an O_t (phase of o_read[t])
@@ -379,46 +384,36 @@ __global__ void __launch_bounds__(384, 1)
         const int nh = 2 * n_kv[t];  // steps of this tile
         const int nhm = 2 * n_max;   // steps of the item (the K/V ring serves both tiles)
         {
-          // the first two S_t of the item, one per buffer, from K(0) and K(1)
-          ok = ok && mbar_wait_warp(smem_u32(&bar_q_full[t]), items & 1, &abort_word, 3);
+          // the first two S_t of the item, one per buffer, from K(0) and K(1) in the head slot
+          ok = ok && mbar_wait_warp(smem_u32(&bar_q_full[t]), items & 1, &abort_word, 3) &&
+               kv_wait(kv_it, 4);
+          if (!ok) break;
+          tc_fence_after();
+          if (nh > 0) {
 #pragma unroll
-          for (int b = 0; b < 2; ++b) {
-            ok = ok && kv_wait(kv_it + b, 4);
-            if (!ok) break;
-            tc_fence_after();
-            if (nh > 0) {
-              issue_qk(t, b, kv_addr(kv_it + b));
+            for (int b = 0; b < 2; ++b) {
+              issue_qk(t, b, kv_addr(kv_it) + b * T::kHalfTileBytes);
               umma_commit_elect(smem_u32(&bar_s_full[t][b]));
             }
           }
-          if (!ok) break;
           // with at most one KV tile these were the item's last uses of Q_t
           if (nh <= 2) umma_commit_elect(smem_u32(&bar_q_free[t]));
           kv_release(kv_it);
-          kv_release(kv_it + 1);
         }
         for (int h = 0; ok && h < nhm; ++h) {
           const int buf = h & 1;
-          // position of V(h) and K(h+2) in the item's load order
-          const uint32_t it_v = kv_it + 2 + 2 * h - (h == nhm - 1 ? 1 : 0);
-          const uint32_t it_k = kv_it + 3 + 2 * h;
-          const bool have_k = (h + 2 < nhm);
-          bool all_ready = false;
-          // a slot is only released after it was seen full, used or not: otherwise this warp
-          // could release the same slot twice within one round of the ring
-          {
-            // the step's three waits (V(h), P_t(h), K(h+2)) in one go when all are ready, as
-            // they normally are; the bounded waits below then return at their first probe
-            const uint32_t bv = smem_u32(&bar_kv_full[it_v % T::kStages]);
-            const uint32_t pv = (it_v / T::kStages) & 1;
-            const bool use_p = h < nh, use_k = have_k;
-            const uint32_t bp = use_p ? smem_u32(&bar_p_full[t][buf]) : bv;
-            const uint32_t pp = use_p ? ((p_cnt >> 1) & 1) : pv;
-            const uint32_t bk = use_k ? smem_u32(&bar_kv_full[it_k % T::kStages]) : bv;
-            const uint32_t pk = use_k ? ((it_k / T::kStages) & 1) : pv;
-            all_ready = __all_sync(0xffffffffu, mbar_try_wait3(bv, pv, bp, pp, bk, pk));
-          }
-          if (!all_ready && !kv_wait(it_v, 5)) {
+          const uint32_t it_s = kv_it + 1 + h;  // the slot with V(h) and K(h+2)
+          // The step's two waits (its slot, P_t(h)) with both probes in flight together; when
+          // both are ready, as they normally are, the bounded waits below are skipped.  A slot
+          // is only released after it was seen full, used or not: otherwise this warp could
+          // release the same slot twice within one round of the ring.
+          const uint32_t bs = smem_u32(&bar_kv_full[it_s % T::kStages]);
+          const uint32_t ps = (it_s / T::kStages) & 1;
+          const bool use_p = h < nh;
+          const uint32_t bp = use_p ? smem_u32(&bar_p_full[t][buf]) : bs;
+          const uint32_t pp = use_p ? ((p_cnt >> 1) & 1) : ps;
+          const bool all_ready = __all_sync(0xffffffffu, mbar_try_wait3(bs, ps, bp, pp, bs, ps));
+          if (!all_ready && !kv_wait(it_s, 5)) {
             ok = false;
             break;
           }
@@ -439,40 +434,27 @@ __global__ void __launch_bounds__(384, 1)
             }
             tc_fence_after();
             FMHA_TL(2, tl_base + h, t * 4 + 1);
-            issue_pv(t, buf, kv_addr(it_v), h > 0);
-            umma_commit_elect(smem_u32(&bar_pv_done[t]));
+            issue_pv(t, buf, kv_addr(it_s), h > 0);
             FMHA_TL(2, tl_base + h, t * 4 + 2);
             if (h + 2 < nh) {
-              // S_t(h+2) goes where P_t(h) was; the tensor pipe runs one warp's MMAs in order
-              if (!all_ready) {
-                if (!kv_wait(it_k, 8)) {
-                  ok = false;
-                  break;
-                }
-                tc_fence_after();
-              }
-              issue_qk(t, buf, kv_addr(it_k));
+              // S_t(h+2) goes where P_t(h) was; the tensor pipe runs one warp's MMAs in order.
+              // Its commit also tells the softmax group that O_t += P_t(h) V(h) is complete.
+              issue_qk(t, buf, kv_addr(it_s) + T::kHalfTileBytes);
               umma_commit_elect(smem_u32(&bar_s_full[t][buf]));
               if (h + 3 == nh) umma_commit_elect(smem_u32(&bar_q_free[t]));
             } else {
-              if (have_k && !all_ready && !kv_wait(it_k, 8)) {
-                ok = false;
-                break;
-              }
+              // no S follows: the completion of this O_t += gets a barrier of its own
+              umma_commit_elect(smem_u32(&bar_pv_done[t]));
               if (h + 1 == nh) {
                 umma_commit_elect(smem_u32(&bar_o_full[t]));
                 ++o_cnt;
               }
             }
             FMHA_TL(2, tl_base + h, t * 4 + 3);
-          } else if (have_k && !all_ready && !kv_wait(it_k, 8)) {
-            ok = false;
-            break;
           }
-          kv_release(it_v);
-          if (have_k) kv_release(it_k);
+          kv_release(it_s);
         }
-        kv_it += 2 * nhm;
+        kv_it += nhm + 1;
         ++items;
         tl_base += 64;
       }
@@ -567,7 +549,13 @@ __global__ void __launch_bounds__(384, 1)
           if (__any_sync(0xffffffffu, need)) {
             // O_t may still be accumulating the previous step: wait for that MMA.  The next
             // one is not issued before this thread has arrived on p_full.
-            mbar_wait(smem_u32(&bar_pv_done[t]), (step - 1) & 1, &abort_word, 11);
+            // That is known from the commit of S_t(hs+1), issued right behind it, or, for
+            // the last step of an item (no S follows the last two O_t +=, which complete
+            // bar_pv_done twice per item), from the first of those two completions.
+            if (hs + 1 < 2 * n)
+              mbar_wait(smem_u32(&bar_s_full[t][buf ^ 1]), ((step + 1) >> 1) & 1, &abort_word, 11);
+            else
+              mbar_wait(smem_u32(&bar_pv_done[t]), 0, &abort_word, 11);
             tc_fence_after();
             const float alpha = isinf(m_new) ? 1.f : fast_exp2((m_ref - m_new) * c);
             l *= alpha;
