@@ -217,27 +217,6 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32
       : "memory");
 }
 
-// 16-column variants (a thread that owns half a row keeps fewer values in flight)
-__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
-      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
-        "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
-        "=r"(r[14]), "=r"(r[15])
-      : "r"(taddr)
-      : "memory");
-}
-__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16]) {
-  asm volatile(
-      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
-      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
-      :
-      : "r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]),
-        "r"(r[7]), "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]),
-        "r"(r[14]), "r"(r[15])
-      : "memory");
-}
 
 // ---------------------------------------------------------------------------------
 // UMMA descriptors (fp16 operands, fp32 accumulate, dense, cta_group::1, M = 128)
@@ -383,21 +362,6 @@ __device__ __forceinline__ float fast_exp2(float x) {
   return y;
 #endif
 }
-// exp2 on the FMA / ALU pipes (no MUFU): x = n + f with n = floor(x) from a round-down add of
-// 1.5 * 2^23, 2^f by a cubic (relative error 7.5e-5, far below the fp16 rounding P gets anyway),
-// 2^n by adding n into the exponent field.  Used for a fraction of the softmax exponentials so
-// that the 16-per-clock MUFU unit is not the only pipe doing them.  x is clamped to >= -126
-// (masked -inf scores give 2^-126, which rounds to 0 in fp16).
-__device__ __forceinline__ float poly_exp2(float x) {
-  x = fmaxf(x, -126.f);
-  float t;
-  asm("add.rm.ftz.f32 %0, %1, %2;" : "=f"(t) : "f"(x), "f"(12582912.f));
-  const float f = x - (t - 12582912.f);
-  float p = fmaf(f, 0.0780244917f, 0.2260672003f);
-  p = fmaf(p, f, 0.6958335042f);
-  p = fmaf(p, f, 0.9999251962f);
-  return __int_as_float(__float_as_int(p) + (__float_as_int(t) << 23));
-}
 // ---- packed pairs of fp32 (one instruction works on two values; sm_100 f32x2 forms) ----
 __device__ __forceinline__ uint64_t pack2(uint32_t lo, uint32_t hi) {
   uint64_t r;
@@ -441,7 +405,12 @@ __device__ __forceinline__ float min3(float a, float b, float c) {
   asm("min.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
   return d;
 }
-// poly_exp2 on a packed pair; the result is the packed pair of 2^x
+// exp2 on the FMA / ALU pipes (no MUFU): x = n + f with n = floor(x) from a round-down add of
+// 1.5 * 2^23, 2^f by a cubic (relative error 7.5e-5, far below the fp16 rounding P gets anyway),
+// 2^n by adding n into the exponent field.  An option of the forward kernel (FMHA_FWD_POLY_PAIRS) for a
+// fraction of the softmax exponentials, off by default.  x is clamped to >= -126
+// (masked -inf scores give 2^-126, which rounds to 0 in fp16).
+// Works on a packed pair; the result is the packed pair of 2^x.
 __device__ __forceinline__ uint64_t poly_exp2_pair(uint64_t x2) {
   uint32_t x0, x1;
   unpack2(x2, x0, x1);
@@ -470,14 +439,6 @@ __device__ __forceinline__ uint32_t mul_half2(uint32_t a, uint32_t b) {
   uint32_t y;
   asm("mul.rn.f16x2 %0, %1, %2;" : "=r"(y) : "r"(a), "r"(b));
   return y;
-}
-__device__ __forceinline__ uint32_t add_half2(uint32_t a, uint32_t b) {
-  uint32_t y;
-  asm("add.rn.f16x2 %0, %1, %2;" : "=r"(y) : "r"(a), "r"(b));
-  return y;
-}
-__device__ __forceinline__ float2 half2_to_float2(uint32_t a) {
-  return __half22float2(*reinterpret_cast<const __half2*>(&a));
 }
 __device__ __forceinline__ uint32_t fma_half2(uint32_t a, uint32_t b, uint32_t c) {
   uint32_t y;
