@@ -340,16 +340,27 @@ def run_ours(args):
     ms_step = float(t.item())
     assert int(status.item()) == 0, f"kernel status word {int(status.item()):#x}"
 
-    # ---- per-kernel timing (each timed alone, 10 back-to-back launches after 3 warm-ups)
+    # ---- per-kernel timing, in place: the four kernels of a step in their normal order, an
+    # event between each two (timed alone in a loop of its own a kernel runs at another SM clock
+    # under the power cap, and the parts would not add up to the step)
     iters = 10
     both = cabi.FMHA_BWD_KEEP_WORKSPACE | cabi.FMHA_BWD_SKIP_DQ_CONVERT
-    ms_fwd = time_events(fwd, iters, torch)
-    ms_bwd = time_events(bwd, iters, torch)
-    ms_bwd_main = time_events(lambda: bwd(both), iters, torch)
-    ms_bwd_pre_main = time_events(lambda: bwd(cabi.FMHA_BWD_SKIP_DQ_CONVERT), iters, torch)
-    ms_pre = max(ms_bwd_pre_main - ms_bwd_main, 1e-6)
-    ms_cvt = max(ms_bwd - ms_bwd_pre_main, 1e-6)
-    bwd()  # leave dq consistent
+    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(5)] for _ in range(iters)]
+    torch.cuda.synchronize()
+    for e in ev:
+        e[0].record()
+        fwd()
+        e[1].record()
+        bwd(cabi.FMHA_BWD_PREPROCESS_ONLY)
+        e[2].record()
+        bwd(both)
+        e[3].record()
+        cabi.bwd_convert_dq(ws, dq, scale)
+        e[4].record()
+    torch.cuda.synchronize()
+    ms_fwd, ms_pre, ms_bwd_main, ms_cvt = (
+        sum(e[i].elapsed_time(e[i + 1]) for e in ev) / iters for i in range(4))
+    ms_bwd = ms_pre + ms_bwd_main + ms_cvt
 
     # ---- end to end through the public API with host buffers
     h_out, h_dq, h_dk, h_dv = (torch.empty_like(hq).pin_memory() for _ in range(4))
@@ -414,7 +425,7 @@ def run_ours(args):
             "e2e": {"value": world * (f_fwd + f_bwd) / (ms_e2e * 1e-3) / 1e12, "unit": "TFLOPS",
                     "ms_per_step": ms_e2e, "h2d_bytes_per_step": 4 * tensor_bytes,
                     "d2h_bytes_per_step": 4 * tensor_bytes, "api": "flash_attn_v100.flash_attn_func + backward"},
-            "gpu_launches": 4 * args.steps,
+            "gpu_launches": 4 * args.steps,  # fwd, bwd preprocess, bwd main, bwd convert per step
             "clocks": clocks,
         }
         if world == 1 and not args.no_cpu_baseline:

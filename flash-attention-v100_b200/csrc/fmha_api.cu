@@ -179,6 +179,7 @@ int launch_bwd(const FmhaBwdParams* p, const BwdWorkspace& w, cudaStream_t strea
         to3(p->dout_strides), p->lse, w.dq_accum, w.lse2, w.delta, H, Nq, Nq_pad, rows);
     if (cudaGetLastError() != cudaSuccess) return FMHA_ERR_LAUNCH;
   }
+  if (p->flags & FMHA_BWD_PREPROCESS_ONLY) return FMHA_OK;
 
   {
     CUtensorMap tq, tk, tv, tdo, tdk, tdv, tacc;
@@ -306,7 +307,9 @@ int fmha_bwd(const FmhaBwdParams* p, void* workspace, size_t workspace_bytes, vo
       p->lse == nullptr)
     return FMHA_ERR_NULL_POINTER;
   const bool keep = (p->flags & FMHA_BWD_KEEP_WORKSPACE) != 0;
-  const bool skip_convert = (p->flags & FMHA_BWD_SKIP_DQ_CONVERT) != 0;
+  const bool pre_only = (p->flags & FMHA_BWD_PREPROCESS_ONLY) != 0;
+  const bool skip_convert = pre_only || (p->flags & FMHA_BWD_SKIP_DQ_CONVERT) != 0;
+  if (keep && pre_only) return FMHA_ERR_WORKSPACE;
   if (!keep && p->o == nullptr) return FMHA_ERR_NULL_POINTER;
   if (!skip_convert && p->dq == nullptr) return FMHA_ERR_NULL_POINTER;
   if (p->dk_accum == nullptr && p->dk == nullptr) return FMHA_ERR_NULL_POINTER;
@@ -339,7 +342,7 @@ int fmha_bwd(const FmhaBwdParams* p, void* workspace, size_t workspace_bytes, vo
 int fmha_bwd_static_scratch(const FmhaBwdParams* p, void* stream) {
   if (p == nullptr) return FMHA_ERR_NULL_POINTER;
   // the shared area cannot carry an accumulator over from an earlier call
-  if (p->flags & FMHA_BWD_KEEP_WORKSPACE) return FMHA_ERR_WORKSPACE;
+  if (p->flags & (FMHA_BWD_KEEP_WORKSPACE | FMHA_BWD_PREPROCESS_ONLY)) return FMHA_ERR_WORKSPACE;
   if (p->batch <= 0 || p->heads <= 0 || p->seqlen_q <= 0 || p->head_dim <= 0)
     return FMHA_ERR_BAD_SHAPE;
   const size_t need = fmha_bwd_workspace_bytes(p);

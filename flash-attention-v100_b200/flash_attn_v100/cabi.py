@@ -22,6 +22,7 @@ _LIB_PATH = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file_
 FMHA_OK = 0
 FMHA_BWD_KEEP_WORKSPACE = 1
 FMHA_BWD_SKIP_DQ_CONVERT = 2
+FMHA_BWD_PREPROCESS_ONLY = 4
 
 EXPORTED_SYMBOLS = (
     "fmha_fwd", "fmha_bwd_workspace_bytes", "fmha_bwd", "fmha_bwd_static_scratch", "fmha_bwd_convert_dq", "fmha_merge", "fmha_b200_forward",
@@ -219,7 +220,7 @@ def bwd(q, k, v, o, dout, lse, scale: float, causal: bool = False, causal_shift:
     passed in; with ``dk_accum`` / ``dv_accum`` (fp32) the fp16 dK / dV are not produced."""
     _require_cuda_half(q, k, v, o, dout, dq, dk, dv)
     Z, Nq, H, D = q.shape
-    if dq is None and not (flags & FMHA_BWD_SKIP_DQ_CONVERT):
+    if dq is None and not (flags & (FMHA_BWD_SKIP_DQ_CONVERT | FMHA_BWD_PREPROCESS_ONLY)):
         dq = torch.empty_like(q)
     if dk is None and dk_accum is None:
         dk = torch.empty_like(k)

@@ -96,13 +96,19 @@ typedef struct {
   int32_t causal_shift;
   /* ring attention: 0 = normal (compute D, zero the fp32 dQ accumulator, convert dQ to fp16);
    * bit 0 set = do not zero the dQ accumulator nor recompute D (workspace carries both over
-   * from an earlier call); bit 1 set = do not convert dQ (a later call will). */
+   * from an earlier call); bit 1 set = do not convert dQ (a later call will); bit 2 set = run
+   * the preprocess step only. */
   int32_t flags;
   int32_t* status;
 } FmhaBwdParams;
 
 #define FMHA_BWD_KEEP_WORKSPACE 1
 #define FMHA_BWD_SKIP_DQ_CONVERT 2
+/* Only prepare the workspace (D, the rescaled LSE, zeroed dQ accumulator) and return; the
+ * gradients come from a later call with FMHA_BWD_KEEP_WORKSPACE.  For callers that have O and dO
+ * before the first K/V block arrives, and for timing the three kernels of a backward pass one by
+ * one.  Not combinable with FMHA_BWD_KEEP_WORKSPACE (FMHA_ERR_WORKSPACE). */
+#define FMHA_BWD_PREPROCESS_ONLY 4
 
 /* Forward: O = softmax(scale * Q K^T [+ causal mask]) V and LSE.
  * Replaces fused_mha_forward (include/fused_mha.h:1-2, kernel/fused_mha_kernel.cu:891-902). */
@@ -148,8 +154,8 @@ int fmha_bwd(const FmhaBwdParams* p, void* workspace, size_t workspace_bytes, vo
  *    call re-initialises the parts it needs (dQ accumulator zeroed, statistics rewritten), so
  *    stale contents are harmless, but two calls that overlap on the GPU (different streams,
  *    or different host threads without ordering) race on it.  Serialise them on one stream.
- *  - FMHA_BWD_KEEP_WORKSPACE is rejected with FMHA_ERR_WORKSPACE: a shared area cannot carry
- *    state from one call to the next.
+ *  - FMHA_BWD_KEEP_WORKSPACE and FMHA_BWD_PREPROCESS_ONLY are rejected with FMHA_ERR_WORKSPACE: a
+ *    shared area cannot carry state from one call to the next.
  */
 int fmha_bwd_static_scratch(const FmhaBwdParams* p, void* stream);
 

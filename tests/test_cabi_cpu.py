@@ -94,6 +94,10 @@ def test_backward_workspace_size_and_validation(built_library):
         s.batch, s.row, s.head = 32 * 64, 64, 64
     assert lib.fmha_bwd(ctypes.byref(p), None, 0, None) == 6       # workspace missing
     assert lib.fmha_bwd(ctypes.byref(p), 0x2000, 16, None) == 6    # workspace too small
+    # "keep the workspace" and "only prepare the workspace" contradict each other
+    p.flags = cabi.FMHA_BWD_KEEP_WORKSPACE | cabi.FMHA_BWD_PREPROCESS_ONLY
+    assert lib.fmha_bwd(ctypes.byref(p), 0x2000, 1 << 30, None) == 6
+    p.flags = 0
     p.head_dim = 100
     assert lib.fmha_bwd(ctypes.byref(p), 0x2000, 1 << 30, None) == 2
 

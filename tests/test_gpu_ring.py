@@ -59,6 +59,32 @@ def test_backward_accumulates_over_key_blocks_into_fp32_buffers():
     helpers.check_against_oracle(got, ref, "blockwise backward")
 
 
+def test_backward_in_three_separate_calls_matches_one_call():
+    """Preprocess only, then the fused kernel on the kept workspace, then the dQ conversion: the
+    same bits as one fmha_bwd call (dK/dV bitwise, dQ up to the order of its fp32 additions)."""
+    from flash_attn_v100 import cabi
+
+    Z, N, H, D = 2, 384, 3, 128
+    q, k, v, dout = oracle.make_inputs(Z, N, H, D, seed=12)
+    qd, kd, vd, dod = q.cuda(), k.cuda(), v.cuda(), dout.cuda()
+    out, lse = cabi.fwd(qd, kd, vd, 0.09, True)
+    dq1, dk1, dv1 = cabi.bwd(qd, kd, vd, out, dod, lse, 0.09, True)
+    ws = torch.empty(cabi.bwd_workspace_bytes(Z, N, H, D), dtype=torch.uint8, device="cuda")
+    dk2, dv2 = torch.empty_like(kd), torch.empty_like(vd)
+    cabi.bwd(qd, kd, vd, out, dod, lse, 0.09, True, dk=dk2, dv=dv2, workspace=ws,
+             flags=cabi.FMHA_BWD_PREPROCESS_ONLY)
+    cabi.bwd(qd, kd, vd, out, dod, lse, 0.09, True, dk=dk2, dv=dv2, workspace=ws,
+             flags=cabi.FMHA_BWD_KEEP_WORKSPACE | cabi.FMHA_BWD_SKIP_DQ_CONVERT)
+    dq2 = cabi.bwd_convert_dq(ws, torch.empty_like(qd), 0.09)
+    assert torch.equal(dk1, dk2) and torch.equal(dv1, dv2)
+    assert oracle.rel_l2(dq2.cpu().float(), dq1.cpu().float()) <= 1e-3
+    # the static-scratch entry point cannot keep state between calls and refuses the flag
+    p = cabi.bwd_params(qd, kd, vd, out, dod, lse, dq2, dk2, dv2, 0.09, True, 0, None, None,
+                        cabi.FMHA_BWD_PREPROCESS_ONLY, None)
+    import ctypes
+    assert cabi.load_library().fmha_bwd_static_scratch(ctypes.byref(p), None) == 6
+
+
 def _free_port():
     with socket.socket() as s:
         s.bind(("127.0.0.1", 0))
