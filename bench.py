@@ -418,7 +418,7 @@ def run_ours(args):
                 "bwd_convert_ms": ms_cvt,
                 "frac_of_nominal_2250": {"fwd": f_fwd / ms_fwd / 1e9 / 2250.0, "bwd": f_bwd / ms_bwd / 1e9 / 2250.0},
             },
-            "roofline": {"kernel": "fmha_bwd_kernel<128> (fused dK/dV/dQ)", "bound": "tensor",
+            "roofline": {"kernel": f"fmha_bwd_kernel<{D}> (fused dK/dV/dQ)", "bound": "tensor",
                          "achieved": achieved, "peak": peaks["tflops"], "unit": "TFLOP/s",
                          "frac": achieved / peaks["tflops"], "peak_source": peaks["source"] + " (burst)",
                          "traffic": NCU_TRAFFIC_BYTES.get(args.workload)},
