@@ -109,7 +109,7 @@ __global__ void __launch_bounds__(256)
     fmha_merge_kernel(float* __restrict__ o_acc, float* __restrict__ lse_acc,
                       const __half* __restrict__ o_part, Strides3 sp,
                       const float* __restrict__ lse_part, __half* __restrict__ o_out, int heads,
-                      int rows, long long total_rows) {
+                      int rows, int acc_rows, int row_offset, long long total_rows) {
   constexpr int kGroup = D / 8;
   constexpr int kRowsPerBlock = 256 / kGroup;
   const int part = threadIdx.x % kGroup;
@@ -118,14 +118,16 @@ __global__ void __launch_bounds__(256)
   float la = 0.f, lb = 0.f, ln = 0.f;
   long long stat_idx = 0;
   if (active) {
-    // row_id enumerates (z, q, h), the layout of o_acc
+    // row_id enumerates (z, q, h) of the partial result; it covers rows [row_offset,
+    // row_offset + rows) of the accumulators, which have acc_rows rows
     const int h = (int)(row_id % heads);
     const long long zq = row_id / heads;
     const int q = (int)(zq % rows);
     const int z = (int)(zq / rows);
-    stat_idx = ((long long)z * heads + h) * rows + q;
+    const long long acc_row = ((long long)z * acc_rows + row_offset + q) * heads + h;
+    stat_idx = ((long long)z * heads + h) * acc_rows + row_offset + q;
     la = lse_acc[stat_idx];
-    lb = lse_part[stat_idx];
+    lb = lse_part[((long long)z * heads + h) * rows + q];
     const float mx = fmaxf(la, lb);
     float wa = 0.f, wb = 0.f;
     ln = -CUDART_INF_F;
@@ -136,7 +138,7 @@ __global__ void __launch_bounds__(256)
       wb = eb * inv;
       ln = mx + __logf(ea + eb);
     }
-    float4* acc = reinterpret_cast<float4*>(o_acc + row_id * D + part * 8);
+    float4* acc = reinterpret_cast<float4*>(o_acc + acc_row * D + part * 8);
     const float4 a0 = acc[0], a1 = acc[1];
     const uint4 up =
         *reinterpret_cast<const uint4*>(o_part + z * sp.batch + q * sp.row + h * sp.head + part * 8);
@@ -148,7 +150,7 @@ __global__ void __launch_bounds__(256)
     acc[0] = make_float4(f[0], f[1], f[2], f[3]);
     acc[1] = make_float4(f[4], f[5], f[6], f[7]);
     if (o_out != nullptr)
-      *reinterpret_cast<uint4*>(o_out + row_id * D + part * 8) = pack8(f);
+      *reinterpret_cast<uint4*>(o_out + acc_row * D + part * 8) = pack8(f);
   }
   // every thread of a row has read lse_acc before its first thread overwrites it
   __syncwarp();

@@ -377,13 +377,15 @@ int fmha_bwd_convert_dq(const void* workspace, void* dq, FmhaStrides dq_strides,
   return cudaGetLastError() == cudaSuccess ? FMHA_OK : FMHA_ERR_LAUNCH;
 }
 
-int fmha_merge(float* o_acc, float* lse_acc, const void* o_part, FmhaStrides o_part_strides,
-               const float* lse_part, void* o_out, int32_t batch, int32_t heads, int32_t rows,
-               int32_t head_dim, void* stream) {
+int fmha_merge_rows(float* o_acc, float* lse_acc, const void* o_part, FmhaStrides o_part_strides,
+                    const float* lse_part, void* o_out, int32_t batch, int32_t heads, int32_t rows,
+                    int32_t acc_rows, int32_t row_offset, int32_t head_dim, void* stream) {
   if (o_acc == nullptr || lse_acc == nullptr || o_part == nullptr || lse_part == nullptr)
     return FMHA_ERR_NULL_POINTER;
   if (head_dim != 64 && head_dim != 128) return FMHA_ERR_BAD_HEAD_DIM;
-  if (batch <= 0 || heads <= 0 || rows <= 0) return FMHA_ERR_BAD_SHAPE;
+  if (batch <= 0 || heads <= 0 || rows <= 0 || row_offset < 0 ||
+      (long long)row_offset + rows > (long long)acc_rows)
+    return FMHA_ERR_BAD_SHAPE;
   if (!aligned16(o_acc) || !aligned16(o_part) || !aligned16(o_out)) return FMHA_ERR_BAD_ALIGNMENT;
   int rc = check_strides(o_part_strides, rows, heads, batch);
   if (rc) return rc;
@@ -394,12 +396,19 @@ int fmha_merge(float* o_acc, float* lse_acc, const void* o_part, FmhaStrides o_p
   if (head_dim == 128)
     fmha::fmha_merge_kernel<128><<<grid, 256, 0, s>>>(
         o_acc, lse_acc, static_cast<const __half*>(o_part), to3(o_part_strides), lse_part,
-        static_cast<__half*>(o_out), heads, rows, total);
+        static_cast<__half*>(o_out), heads, rows, acc_rows, row_offset, total);
   else
     fmha::fmha_merge_kernel<64><<<grid, 256, 0, s>>>(
         o_acc, lse_acc, static_cast<const __half*>(o_part), to3(o_part_strides), lse_part,
-        static_cast<__half*>(o_out), heads, rows, total);
+        static_cast<__half*>(o_out), heads, rows, acc_rows, row_offset, total);
   return cudaGetLastError() == cudaSuccess ? FMHA_OK : FMHA_ERR_LAUNCH;
+}
+
+int fmha_merge(float* o_acc, float* lse_acc, const void* o_part, FmhaStrides o_part_strides,
+               const float* lse_part, void* o_out, int32_t batch, int32_t heads, int32_t rows,
+               int32_t head_dim, void* stream) {
+  return fmha_merge_rows(o_acc, lse_acc, o_part, o_part_strides, lse_part, o_out, batch, heads,
+                         rows, rows, 0, head_dim, stream);
 }
 
 int fmha_b200_forward(const void* query_ptr, const void* key_ptr, const void* value_ptr,

@@ -25,7 +25,7 @@ FMHA_BWD_SKIP_DQ_CONVERT = 2
 FMHA_BWD_PREPROCESS_ONLY = 4
 
 EXPORTED_SYMBOLS = (
-    "fmha_fwd", "fmha_bwd_workspace_bytes", "fmha_bwd", "fmha_bwd_static_scratch", "fmha_bwd_convert_dq", "fmha_merge", "fmha_b200_forward",
+    "fmha_fwd", "fmha_bwd_workspace_bytes", "fmha_bwd", "fmha_bwd_static_scratch", "fmha_bwd_convert_dq", "fmha_merge", "fmha_merge_rows", "fmha_b200_forward",
     "fmha_b200_backward", "fmha_status_string", "fmha_version",
 )
 
@@ -94,6 +94,10 @@ def load_library() -> ctypes.CDLL:
     lib.fmha_merge.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, FmhaStrides,
                                ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int32, ctypes.c_int32,
                                ctypes.c_int32, ctypes.c_int32, ctypes.c_void_p]
+    lib.fmha_merge_rows.restype = ctypes.c_int
+    lib.fmha_merge_rows.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, FmhaStrides,
+                                    ctypes.c_void_p, ctypes.c_void_p] + [ctypes.c_int32] * 6 + [
+                                        ctypes.c_void_p]
     lib.fmha_b200_forward.restype = ctypes.c_int
     lib.fmha_b200_forward.argtypes = [ctypes.c_void_p] * 5 + [ctypes.c_int] * 5 + [
         ctypes.c_float, ctypes.c_int, ctypes.c_void_p]
@@ -261,15 +265,18 @@ def bwd_convert_dq(workspace, dq, scale: float, stream=None):
     return dq
 
 
-def merge(o_acc, lse_acc, o_part, lse_part, o_out=None, stream=None):
-    """In-place LSE merge of (o_part fp16, lse_part) into (o_acc fp32 contiguous, lse_acc)."""
+def merge(o_acc, lse_acc, o_part, lse_part, o_out=None, stream=None, row_offset: int = 0):
+    """In-place LSE merge of (o_part fp16, lse_part) into (o_acc fp32 contiguous, lse_acc).  The
+    partial result covers rows [row_offset, row_offset + o_part.shape[1]) of the accumulators."""
     Z, N, H, D = o_part.shape
+    acc_rows = o_acc.shape[1]
     if not (o_acc.is_contiguous() and lse_acc.is_contiguous() and lse_part.is_contiguous()):
         raise RuntimeError("o_acc, lse_acc and lse_part must be contiguous")
     if o_out is not None and not o_out.is_contiguous():
         raise RuntimeError("o_out must be contiguous")
     with torch.cuda.device(o_part.device):
-        _check(load_library().fmha_merge(_ptr(o_acc), _ptr(lse_acc), _ptr(o_part), _strides(o_part),
-                                         _ptr(lse_part), _ptr(o_out), Z, H, N, D, _stream(stream)),
-               "fmha_merge")
+        _check(load_library().fmha_merge_rows(_ptr(o_acc), _ptr(lse_acc), _ptr(o_part),
+                                              _strides(o_part), _ptr(lse_part), _ptr(o_out), Z, H, N,
+                                              acc_rows, int(row_offset), D, _stream(stream)),
+               "fmha_merge_rows")
     return o_acc, lse_acc

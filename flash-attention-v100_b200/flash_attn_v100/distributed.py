@@ -86,15 +86,7 @@ class CudaBackend:
 
     def merge(self, o_acc, lse_acc, o_part, lse_part, rows: slice):
         """Merge a partial result for query rows ``rows`` into the accumulators, in place."""
-        if rows.start in (0, None) and rows.stop in (None, o_acc.shape[1]):
-            self.cabi.merge(o_acc, lse_acc, o_part, lse_part)
-            return
-        # a row sub-range is not contiguous in the (Z, H, N) statistics: merge a compact copy
-        o_sub = o_acc[:, rows].contiguous()
-        l_sub = lse_acc[:, :, rows].contiguous()
-        self.cabi.merge(o_sub, l_sub, o_part, lse_part.contiguous())
-        o_acc[:, rows] = o_sub
-        lse_acc[:, :, rows] = l_sub
+        self.cabi.merge(o_acc, lse_acc, o_part, lse_part, row_offset=rows.start or 0)
 
     def finish(self, o_acc, lse_acc, dtype):
         return o_acc.to(dtype), lse_acc

@@ -177,6 +177,15 @@ int fmha_merge(float* o_acc, float* lse_acc, const void* o_part, FmhaStrides o_p
                const float* lse_part, void* o_out, int32_t batch, int32_t heads, int32_t rows,
                int32_t head_dim, void* stream);
 
+/* The same merge for a partial result that covers only rows [row_offset, row_offset + rows) of
+ * accumulators with acc_rows rows (zig-zag ring attention: some steps compute the second half of
+ * the local query rows only).  o_part (Z, rows, H, D) with strides, lse_part (Z, H, rows);
+ * o_acc / o_out (Z, acc_rows, H, D), lse_acc (Z, H, acc_rows), all contiguous.
+ * No counterpart in the reference. */
+int fmha_merge_rows(float* o_acc, float* lse_acc, const void* o_part, FmhaStrides o_part_strides,
+                    const float* lse_part, void* o_out, int32_t batch, int32_t heads, int32_t rows,
+                    int32_t acc_rows, int32_t row_offset, int32_t head_dim, void* stream);
+
 /* Reference-shaped launchers: same argument meaning as include/fused_mha.h:1-6, dense
  * (batch, m|n, head, k) tensors, except that the `max`/`sum` pair becomes one `lse` buffer,
  * the backward's `d_ptr` (fp16 D) is dropped in favour of a caller workspace, and a status

@@ -34,6 +34,26 @@ def test_merge_kernel_matches_oracle_merge():
     assert oracle.max_abs(lse_acc.cpu(), ref_lse) <= helpers.TOL_LSE_MAX_ABS
 
 
+def test_merge_of_a_row_range_into_larger_accumulators():
+    """fmha_merge_rows: a partial result for the second half of the query rows merged in place
+    into full-height accumulators equals the merge of a compact copy of that row range."""
+    from flash_attn_v100 import cabi
+
+    Z, N, H, D = 2, 256, 3, 128
+    q, k, v, _ = oracle.make_inputs(Z, N, H, D, seed=13)
+    qd, kd, vd = q.cuda(), k.cuda(), v.cuda()
+    half = N // 2
+    o_acc = torch.randn((Z, N, H, D), device="cuda")
+    lse_acc = torch.randn((Z, H, N), device="cuda")
+    o_p, l_p = cabi.fwd(qd[:, half:], kd, vd, 0.1, False)
+    o_ref, l_ref = o_acc.clone(), lse_acc.clone()
+    o_sub, l_sub = o_ref[:, half:].contiguous(), l_ref[:, :, half:].contiguous()
+    cabi.merge(o_sub, l_sub, o_p, l_p)
+    o_ref[:, half:], l_ref[:, :, half:] = o_sub, l_sub
+    cabi.merge(o_acc, lse_acc, o_p, l_p, row_offset=half)
+    assert torch.equal(o_acc, o_ref) and torch.equal(lse_acc, l_ref)
+
+
 def test_backward_accumulates_over_key_blocks_into_fp32_buffers():
     """Ring-style backward on one GPU: two key blocks, dQ accumulated in one workspace over both
     calls, dK/dV added into row ranges of fp32 buffers (batch stride != dense), dQ converted at
