@@ -387,28 +387,46 @@ def run_ours(args):
         sum(e[i].elapsed_time(e[i + 1]) for e in ev) / iters for i in range(4))
     ms_bwd = ms_pre + ms_bwd_main + ms_cvt
 
-    # ---- end to end through the public API with host buffers
+    # ---- end to end through the public API with host buffers.  Every step copies its own inputs
+    # from pinned host memory and its own results back; the copies of neighbouring steps overlap
+    # with each other and with the kernels (PCIe is full duplex): inputs of step i+1 go up while
+    # step i computes and the results of step i-1 come down, through two sets of device buffers.
     h_out, h_dq, h_dk, h_dv = (torch.empty_like(hq).pin_memory() for _ in range(4))
+    s_up, s_down = torch.cuda.Stream(), torch.cuda.Stream()
+    sets = [{"in": [torch.empty_like(q) for _ in range(4)], "res": None,
+             "up": torch.cuda.Event(), "done": torch.cuda.Event(), "down": torch.cuda.Event()}
+            for _ in range(2)]
 
-    def e2e_step():
-        q2 = hq.to(dev, non_blocking=True).requires_grad_()
-        k2 = hk.to(dev, non_blocking=True).requires_grad_()
-        v2 = hv.to(dev, non_blocking=True).requires_grad_()
-        do2 = hdo.to(dev, non_blocking=True)
-        o2 = flash_attn_func(q2, k2, v2, scale, causal)
-        o2.backward(do2)
-        h_out.copy_(o2.detach(), non_blocking=True)
-        h_dq.copy_(q2.grad, non_blocking=True)
-        h_dk.copy_(k2.grad, non_blocking=True)
-        h_dv.copy_(v2.grad, non_blocking=True)
+    def e2e_run(n_steps):
+        main = torch.cuda.current_stream()
+        for i in range(n_steps):
+            b = sets[i % 2]
+            with torch.cuda.stream(s_up):
+                s_up.wait_event(b["done"])   # the buffers' previous user (step i-2) has computed
+                for dst, src in zip(b["in"], (hq, hk, hv, hdo)):
+                    dst.copy_(src, non_blocking=True)
+                b["up"].record(s_up)
+            main.wait_event(b["up"])
+            main.wait_event(b["down"])       # the previous results of this set have gone down
+            q2, k2, v2 = (t.detach().requires_grad_() for t in b["in"][:3])
+            o2 = flash_attn_func(q2, k2, v2, scale, causal)
+            o2.backward(b["in"][3])
+            b["res"] = (o2.detach(), q2.grad, k2.grad, v2.grad)
+            b["done"].record(main)
+            with torch.cuda.stream(s_down):
+                s_down.wait_event(b["done"])
+                for dst, src in zip((h_out, h_dq, h_dk, h_dv), b["res"]):
+                    dst.copy_(src, non_blocking=True)
+                b["down"].record(s_down)
+        main.wait_stream(s_down)
+        main.wait_stream(s_up)
 
-    for _ in range(2):
-        e2e_step()
+    e2e_run(2)
     torch.cuda.synchronize()
     if world > 1:
         dist.barrier()
-    e2e_iters = max(3, min(args.steps, 10))
-    ms_e2e = time_events(e2e_step, e2e_iters, torch)
+    e2e_iters = max(4, min(args.steps, 10))
+    ms_e2e = time_events(lambda: e2e_run(e2e_iters), 1, torch) / e2e_iters
     t = torch.tensor([ms_e2e], dtype=torch.float64, device=dev)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -450,7 +468,8 @@ def run_ours(args):
                          "traffic": NCU_TRAFFIC_BYTES.get(args.workload)},
             "e2e": {"value": world * (f_fwd + f_bwd) / (ms_e2e * 1e-3) / 1e12, "unit": "TFLOPS",
                     "ms_per_step": ms_e2e, "h2d_bytes_per_step": 4 * tensor_bytes,
-                    "d2h_bytes_per_step": 4 * tensor_bytes, "api": "flash_attn_v100.flash_attn_func + backward"},
+                    "d2h_bytes_per_step": 4 * tensor_bytes, "api": "flash_attn_v100.flash_attn_func + backward",
+                    "overlap": "copies of neighbouring steps overlap (two buffer sets, three streams)"},
             "gpu_launches": 4 * args.steps,  # fwd, bwd preprocess, bwd main, bwd convert per step
             "clocks": clocks,
         }
