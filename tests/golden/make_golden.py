@@ -55,7 +55,9 @@ def input_digest(q, k, v, dout) -> str:
 
 
 def main():
-    ref_root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) < 2:
+        sys.exit("usage: make_golden.py <path to a checkout of flash-attention-v100>")
+    ref_root = sys.argv[1]
     src = reference_math_path_source(ref_root)
     for name, (Z, N, H, D, causal, sm_scale, seed) in CASES.items():
         q, k, v, dout = make_inputs(Z, N, H, D, seed)
