@@ -45,6 +45,27 @@ def test_tile_edges(N, D, causal):
     _run(2, N, 2, D, causal, seed=N + D)
 
 
+def test_long_sequence_many_steps_per_item():
+    """N = 8192: 64 KV tiles per work item, i.e. 128 steps through the double-buffered S, the
+    K/V ring and the Q ring of one persistent CTA, against the oracle on the whole problem."""
+    _run(1, 8192, 1, 128, True, seed=21)
+
+
+def test_many_items_per_cta_sampled_heads():
+    """Z*H = 1184 heads of N = 512: every persistent forward CTA walks eight work items and the
+    barrier phases run on across them; 6 heads, spread over the grid, are compared with the
+    oracle (the oracle on all heads would take minutes)."""
+    Z, N, H, D = 37, 512, 32, 64
+    q, k, v, dout = oracle.make_inputs(Z, N, H, D, seed=22)
+    scale = oracle.default_scale(D)
+    out, lse, dq, dk, dv = helpers.gpu_fwd_bwd(q, k, v, dout, scale, True)
+    for z, h in ((0, 0), (5, 31), (11, 7), (23, 16), (30, 1), (36, 31)):
+        sl = (slice(z, z + 1), slice(None), slice(h, h + 1))
+        ref = oracle.attention_fwd_bwd(q[sl], k[sl], v[sl], dout[sl], scale, True)
+        got = (out[sl], lse[z:z + 1, h:h + 1], dq[sl], dk[sl], dv[sl])
+        helpers.check_against_oracle(got, ref, f"head ({z},{h}) of Z{Z} H{H} N{N} D{D}")
+
+
 @pytest.mark.parametrize("causal", [False, True])
 def test_cfg2(causal):
     """BASELINE config 2: Z=4, H=16, N=1024, D=64, scale 0.125."""
