@@ -68,6 +68,15 @@ struct FwdKernelParams {
 #define FMHA_ABLATE 0  // debug builds: bit 0 no exp2, bit 1 no row max, bit 2 no P store
 #endif
 
+// pairs out of every 4 whose exponential is a polynomial on the FMA pipe (the rest use MUFU),
+// for head_dim 128 and for head_dim 64
+#ifndef FMHA_FWD_POLY_PAIRS
+#define FMHA_FWD_POLY_PAIRS 0
+#endif
+#ifndef FMHA_FWD_POLY_PAIRS_D64
+#define FMHA_FWD_POLY_PAIRS_D64 0
+#endif
+
 template <int D>
 struct FwdTraits {
   static constexpr int kBlockM = 128;  // rows per query tile
@@ -89,15 +98,11 @@ struct FwdTraits {
   // Q tiles, K/V ring, one output staging tile per softmax group
   static constexpr int kSmemBytes = 1024 + (kTilesM + 2) * kTileBytes + kStages * kSlotBytes;
   static constexpr int kTmemCols = 512;
+  static constexpr int kPolyPairs = (D == 64) ? FMHA_FWD_POLY_PAIRS_D64 : FMHA_FWD_POLY_PAIRS;
   static constexpr uint32_t kIdescQK = umma_idesc_f16(128, kStepN, 0, 0);
   static constexpr uint32_t kIdescPV = umma_idesc_f16(128, D, 0, 1);
 };
 
-// pairs out of every 4 whose exponential is a polynomial on the FMA pipe (the rest use MUFU)
-#ifndef FMHA_FWD_POLY_PAIRS
-#define FMHA_FWD_POLY_PAIRS 0
-#endif
-constexpr int kFwdPolyPairs = FMHA_FWD_POLY_PAIRS;
 constexpr int kFwdRegsIssue = 88;                                 // warps 8-11
 constexpr int kFwdRegsSoftmax = 168 + (168 - kFwdRegsIssue) / 2;  // warps 0-7: 208
 static_assert(kFwdRegsIssue <= 168 && kFwdRegsSoftmax >= 168 && kFwdRegsSoftmax % 8 == 0,
@@ -583,8 +588,8 @@ __global__ void __launch_bounds__(384, 1)
           for (int i = 0; i < 32; i += 2) {
             const uint64_t x2 = fma2(pack2(s[cc][i], s[cc][i + 1]), c2, nm2);
             uint64_t p2;
-            // kFwdPolyPairs of every 4 pairs go through the FMA pipe instead of the MUFU unit
-            if (((i >> 1) & 3) < kFwdPolyPairs) {
+            // kPolyPairs of every 4 pairs go through the FMA pipe instead of the MUFU unit
+            if (((i >> 1) & 3) < T::kPolyPairs) {
               p2 = poly_exp2_pair(x2);
             } else {
               uint32_t x0, x1;
