@@ -45,6 +45,22 @@ def test_tile_edges(N, D, causal):
     _run(2, N, 2, D, causal, seed=N + D)
 
 
+@pytest.mark.parametrize("causal", [False, True])
+@pytest.mark.parametrize("D", [64, 128])
+def test_growing_scores_exercise_the_lazy_rescale(D, causal):
+    """Keys whose norm grows by 1.5x per block of 64: the running row maximum grows by more than
+    2^8 at the late steps, the last one included, so the forward kernel has to rescale its
+    output accumulator there (it does so only then), after waiting for the previous O += P V."""
+    Z, N, H = 1, 512, 2
+    q, k, v, dout = oracle.make_inputs(Z, N, H, D, seed=31)
+    ramp = (1.5 ** torch.arange(N // 64, dtype=torch.float32)).repeat_interleave(64)
+    k = (k.float() * ramp.view(1, N, 1, 1)).half()
+    scale = oracle.default_scale(D)
+    got = helpers.gpu_fwd_bwd(q, k, v, dout, scale, causal)
+    ref = oracle.attention_fwd_bwd(q, k, v, dout, scale, causal)
+    helpers.check_against_oracle(got, ref, f"growing scores D{D} causal={causal}")
+
+
 def test_long_sequence_many_steps_per_item():
     """N = 8192: 64 KV tiles per work item, i.e. 128 steps through the double-buffered S, the
     K/V ring and the Q ring of one persistent CTA, against the oracle on the whole problem."""
