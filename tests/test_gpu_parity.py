@@ -179,3 +179,25 @@ def test_status_word_stays_zero_and_negative_scale():
     got = helpers.gpu_fwd_bwd(q, k, v, dout, -0.2, True)
     ref = oracle.attention_fwd_bwd(q, k, v, dout, -0.2, True)
     helpers.check_against_oracle(got, ref, "negative scale")
+
+
+def test_a_set_status_word_drains_the_kernels_without_touching_the_outputs():
+    """A status word that is already non-zero (an earlier kernel gave up on a bounded wait) makes
+    every CTA of the attention kernels return at once: the word keeps its value and the outputs
+    keep their contents.  No wait is made to run out here: the word is set by the host."""
+    from flash_attn_v100 import cabi
+
+    q, k, v, dout = (t.cuda() for t in oracle.make_inputs(2, 256, 2, 128, seed=9))
+    out_ok, lse = cabi.fwd(q, k, v, 0.1, True)
+    status = torch.full((1,), 0x142, dtype=torch.int32, device="cuda")
+    out = torch.full_like(q, 7.0)
+    cabi.fwd(q, k, v, 0.1, True, out=out, lse=torch.empty_like(lse), status=status)
+    dk, dv = torch.full_like(k, 7.0), torch.full_like(v, 7.0)
+    cabi.bwd(q, k, v, out_ok, dout, lse, 0.1, True, dk=dk, dv=dv, status=status)
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0x142
+    assert bool((out == 7.0).all()) and bool((dk == 7.0).all()) and bool((dv == 7.0).all())
+    # and with a clean word the same calls work again (nothing was left behind)
+    status.zero_()
+    out2, _ = cabi.fwd(q, k, v, 0.1, True, status=status)
+    assert torch.equal(out2, out_ok) and int(status.item()) == 0
