@@ -159,7 +159,8 @@ int launch_fwd(const FmhaFwdParams* p, cudaStream_t stream) {
     return FMHA_ERR_LAUNCH;
   // persistent grid: one CTA per SM (or per super-item = pair of query blocks, if fewer)
   const long long n_super = (long long)((kp.num_q_blocks + 1) / 2) * kp.num_heads_total;
-  const unsigned grid = (unsigned)std::min<long long>(n_super, sm_count());
+  const int sms = std::max(1, sm_count() - std::max(0, (int)p->sm_margin));
+  const unsigned grid = (unsigned)std::min<long long>(n_super, sms);
   kernel<<<grid, T::kThreads, T::kSmemBytes, stream>>>(tq, tk, tv, to, kp);
   return cudaGetLastError() == cudaSuccess ? FMHA_OK : FMHA_ERR_LAUNCH;
 }

@@ -43,7 +43,7 @@ class FmhaFwdParams(ctypes.Structure):
         ("batch", ctypes.c_int32), ("heads", ctypes.c_int32), ("seqlen_q", ctypes.c_int32),
         ("seqlen_k", ctypes.c_int32), ("head_dim", ctypes.c_int32),
         ("scale", ctypes.c_float), ("causal", ctypes.c_int32), ("causal_shift", ctypes.c_int32),
-        ("status", ctypes.c_void_p),
+        ("status", ctypes.c_void_p), ("sm_margin", ctypes.c_int32),
     ]
 
 
@@ -144,7 +144,7 @@ def _require_cuda_half(*tensors):
                                "contiguous last dimension")
 
 
-def fwd_params(q, k, v, o, lse, scale, causal, causal_shift=0, status=None) -> FmhaFwdParams:
+def fwd_params(q, k, v, o, lse, scale, causal, causal_shift=0, status=None, sm_margin=0) -> FmhaFwdParams:
     p = FmhaFwdParams()
     p.q, p.k, p.v, p.o, p.lse = q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), lse.data_ptr()
     p.q_strides, p.k_strides, p.v_strides, p.o_strides = _strides(q), _strides(k), _strides(v), _strides(o)
@@ -154,21 +154,22 @@ def fwd_params(q, k, v, o, lse, scale, causal, causal_shift=0, status=None) -> F
     p.causal = int(bool(causal))
     p.causal_shift = int(causal_shift)
     p.status = None if status is None else status.data_ptr()
+    p.sm_margin = int(sm_margin)
     return p
 
 
 def fwd(q, k, v, scale: float, causal: bool = False, causal_shift: int = 0,
         out: Optional[torch.Tensor] = None, lse: Optional[torch.Tensor] = None,
-        status: Optional[torch.Tensor] = None, stream=None):
+        status: Optional[torch.Tensor] = None, stream=None, sm_margin: int = 0):
     """O, LSE through ``fmha_fwd`` on the current (or given) stream; outputs allocated with torch
-    unless passed in."""
+    unless passed in.  ``sm_margin``: SMs the persistent kernel leaves to other streams' kernels."""
     _require_cuda_half(q, k, v, out)
     Z, Nq, H, D = q.shape
     if out is None:
         out = torch.empty_like(q)
     if lse is None:
         lse = torch.empty((Z, H, Nq), dtype=torch.float32, device=q.device)
-    p = fwd_params(q, k, v, out, lse, scale, causal, causal_shift, status)
+    p = fwd_params(q, k, v, out, lse, scale, causal, causal_shift, status, sm_margin)
     with torch.cuda.device(q.device):
         _check(load_library().fmha_fwd(ctypes.byref(p), _stream(stream)), "fmha_fwd")
     return out, lse

@@ -70,6 +70,11 @@ typedef struct {
   int32_t causal;       /* 0 / 1 */
   int32_t causal_shift; /* see above; 0 for the reference's square causal mask */
   int32_t* status;      /* optional device status word */
+  /* SMs to leave free (0 = none).  The forward kernel is persistent, one CTA per SM for its whole
+   * run; a caller that has a copy or collective kernel in flight on another stream (ring
+   * attention posts the next K/V exchange before it launches the step) gives those kernels room
+   * to run beside it instead of after it. */
+  int32_t sm_margin;
 } FmhaFwdParams;
 
 typedef struct {

@@ -201,3 +201,14 @@ def test_a_set_status_word_drains_the_kernels_without_touching_the_outputs():
     status.zero_()
     out2, _ = cabi.fwd(q, k, v, 0.1, True, status=status)
     assert torch.equal(out2, out_ok) and int(status.item()) == 0
+
+
+def test_forward_with_fewer_ctas_gives_the_same_bits():
+    """sm_margin only changes how many persistent CTAs share the work list, never the result."""
+    from flash_attn_v100 import cabi
+
+    q, k, v, _ = (t.cuda() for t in oracle.make_inputs(4, 1024, 24, 128, seed=10))
+    out0, lse0 = cabi.fwd(q, k, v, 0.09, True)
+    for margin in (1, 47, 147, 1000):
+        out1, lse1 = cabi.fwd(q, k, v, 0.09, True, sm_margin=margin)
+        assert torch.equal(out0, out1) and torch.equal(lse0, lse1), f"sm_margin={margin}"

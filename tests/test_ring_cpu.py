@@ -19,7 +19,7 @@ sys.path.insert(0, PKG)
 class OracleBackend:
     """Per-block compute by the CPU oracle (fp32), same interface as distributed.CudaBackend."""
 
-    def fwd(self, q, k, v, scale, causal):
+    def fwd(self, q, k, v, scale, causal, overlap=False):
         return oracle.attention_forward(q, k, v, scale, causal)
 
     def new_accumulators(self, q):
