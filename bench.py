@@ -465,6 +465,7 @@ def run_ours(args):
             "roofline": {"kernel": f"fmha_bwd_kernel<{D}> (fused dK/dV/dQ)", "bound": "tensor",
                          "achieved": achieved, "peak": peaks["tflops"], "unit": "TFLOP/s",
                          "frac": achieved / peaks["tflops"], "peak_source": peaks["source"] + " (burst)",
+                         "frac_of_sustained_peak": achieved / peaks["tflops_sustained"],
                          "traffic": NCU_TRAFFIC_BYTES.get(args.workload)},
             "e2e": {"value": world * (f_fwd + f_bwd) / (ms_e2e * 1e-3) / 1e12, "unit": "TFLOPS",
                     "ms_per_step": ms_e2e, "h2d_bytes_per_step": 4 * tensor_bytes,
