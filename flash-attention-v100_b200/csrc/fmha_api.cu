@@ -333,6 +333,13 @@ int fmha_bwd(const FmhaBwdParams* p, void* workspace, size_t workspace_bytes, vo
     return rc;
   if (p->dv_accum == nullptr && (rc = check_strides(p->dv_strides, p->seqlen_k, p->heads, p->batch)))
     return rc;
+  if (p->dk_accum != nullptr || p->dv_accum != nullptr) {
+    // the epilogue adds with 16-byte accesses at accum + z * stride: the stride must keep them
+    // aligned, and batch entries must not overlap
+    const int64_t st = p->accum_batch_stride;
+    if (st < 0 || (st != 0 && (st % 4 != 0 || st < (int64_t)p->seqlen_k * p->heads * p->head_dim)))
+      return FMHA_ERR_BAD_STRIDE;
+  }
   const BwdWorkspace w = carve_workspace(workspace, p->batch, p->heads, p->seqlen_q, p->head_dim);
   if (workspace == nullptr || workspace_bytes < w.bytes) return FMHA_ERR_WORKSPACE;
   if (!aligned16(workspace)) return FMHA_ERR_BAD_ALIGNMENT;
@@ -342,8 +349,10 @@ int fmha_bwd(const FmhaBwdParams* p, void* workspace, size_t workspace_bytes, vo
 
 int fmha_bwd_static_scratch(const FmhaBwdParams* p, void* stream) {
   if (p == nullptr) return FMHA_ERR_NULL_POINTER;
-  // the shared area cannot carry an accumulator over from an earlier call
-  if (p->flags & (FMHA_BWD_KEEP_WORKSPACE | FMHA_BWD_PREPROCESS_ONLY)) return FMHA_ERR_WORKSPACE;
+  // the shared area cannot carry an accumulator over from an earlier call, nor hand an
+  // unconverted fp32 dQ to a later one (the caller has no address for it)
+  if (p->flags & (FMHA_BWD_KEEP_WORKSPACE | FMHA_BWD_PREPROCESS_ONLY | FMHA_BWD_SKIP_DQ_CONVERT))
+    return FMHA_ERR_WORKSPACE;
   if (p->batch <= 0 || p->heads <= 0 || p->seqlen_q <= 0 || p->head_dim <= 0)
     return FMHA_ERR_BAD_SHAPE;
   const size_t need = fmha_bwd_workspace_bytes(p);

@@ -84,6 +84,7 @@ constexpr uint32_t kWaitPollLimit = 1u << 22;
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_word,
                                           int who) {
   if (mbar_try_wait(bar, parity)) return true;
+  if (*abort_word != 0) return false;  // some wait already gave up: drain without polling
   for (uint32_t i = 0; i < kWaitPollLimit; ++i) {
     if (mbar_try_wait(bar, parity)) return true;
     if ((i & 255u) == 255u && *abort_word != 0) return false;

@@ -58,9 +58,9 @@ void check_shapes(const at::Tensor& q, const at::Tensor& k, const at::Tensor& v)
               "sequence lengths must be multiples of 32 (pad the inputs), got ", Nq, " and ", Nk);
 }
 
-std::vector<at::Tensor> mha_fwd(const at::Tensor& q, const at::Tensor& k, const at::Tensor& v,
-                                std::optional<at::Tensor> out_, double softmax_scale,
-                                bool is_causal) {
+std::vector<at::Tensor> fwd_impl(const at::Tensor& q, const at::Tensor& k, const at::Tensor& v,
+                                 std::optional<at::Tensor> out_, double softmax_scale,
+                                 bool is_causal, bool want_sum) {
   check_input(q, "q");
   check_input(k, "k");
   check_input(v, "v");
@@ -78,7 +78,6 @@ std::vector<at::Tensor> mha_fwd(const at::Tensor& q, const at::Tensor& k, const 
   c10::cuda::CUDAGuard guard(q.device());
   auto fopts = q.options().dtype(at::kFloat);
   at::Tensor lse = at::empty({B, H, Nq}, fopts);
-  at::Tensor ones = at::ones({B, H, Nq}, fopts);
 
   FmhaFwdParams p = {};
   p.q = q.data_ptr();
@@ -99,7 +98,22 @@ std::vector<at::Tensor> mha_fwd(const at::Tensor& q, const at::Tensor& k, const 
   p.causal = is_causal ? 1 : 0;
   p.causal_shift = 0;
   check_status(fmha_fwd(&p, at::cuda::getCurrentCUDAStream().stream()), "fmha_fwd");
-  return {out, lse, ones};
+  if (!want_sum) return {out, lse};
+  return {out, lse, at::ones({B, H, Nq}, fopts)};
+}
+
+// the reference's entry point: {out, softmax_max := lse, softmax_sum := 1}
+std::vector<at::Tensor> mha_fwd(const at::Tensor& q, const at::Tensor& k, const at::Tensor& v,
+                                std::optional<at::Tensor> out_, double softmax_scale,
+                                bool is_causal) {
+  return fwd_impl(q, k, v, out_, softmax_scale, is_causal, true);
+}
+
+// {out, lse} only: what this package's own autograd glue uses (no tensor of ones to fill)
+std::vector<at::Tensor> mha_fwd_lse(const at::Tensor& q, const at::Tensor& k, const at::Tensor& v,
+                                    std::optional<at::Tensor> out_, double softmax_scale,
+                                    bool is_causal) {
+  return fwd_impl(q, k, v, out_, softmax_scale, is_causal, false);
 }
 
 std::vector<at::Tensor> mha_bwd(const at::Tensor& dout, const at::Tensor& q, const at::Tensor& k,
@@ -181,6 +195,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.doc() = "B200 (sm_100a) fused multi-head attention";
   // positional calls only, like the reference's pybind exports (kernel/fused_mha_api.cpp:166-167)
   m.def("fwd", &mha_fwd, "Forward pass: fwd(q, k, v, out|None, softmax_scale, is_causal)");
+  m.def("fwd_lse", &mha_fwd_lse,
+        "Forward pass returning [out, lse]: fwd_lse(q, k, v, out|None, softmax_scale, is_causal)");
   m.def("bwd", &mha_bwd,
         "Backward pass: bwd(dout, q, k, v, out, D|None, softmax_sum|None, softmax_max, dq|None, "
         "dk|None, dv|None, softmax_scale, is_causal)");

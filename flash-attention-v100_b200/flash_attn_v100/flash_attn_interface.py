@@ -15,10 +15,17 @@ What changed underneath:
   * the contract "N_CTX is a multiple of 32, right-padded by the caller" (README.md:3) is
     checked, and tail tiles are masked inside the kernels.
 
+  * the two extension calls are registered as ``torch.library`` custom ops
+    (``flash_attn_v100::fwd`` / ``flash_attn_v100::bwd``, each with a fake implementation that
+    only describes output shapes), so that ``flash_attn_func`` can sit inside a
+    ``torch.compile(fullgraph=True)`` region: the compiler sees two opaque ops instead of a
+    pybind call it cannot trace.  The reference's glue (:62-99) calls the extension directly
+    and breaks the graph.
+
 There is no CPU path: importing this module needs the compiled extension, and calling it needs
 a CUDA device.
 """
-from typing import Optional
+from typing import Optional, Tuple
 
 import torch
 
@@ -30,20 +37,56 @@ def _maybe_contiguous(x):
     return x.contiguous() if x.stride(-1) != 1 else x
 
 
+@torch.library.custom_op("flash_attn_v100::fwd", mutates_args=(), device_types="cuda")
+def _fwd_op(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, softmax_scale: float,
+            causal: bool) -> Tuple[torch.Tensor, torch.Tensor]:
+    out, softmax_lse = flash_attn_cuda.fwd_lse(q, k, v, None, softmax_scale, causal)
+    return out, softmax_lse
+
+
+@_fwd_op.register_fake
+def _fwd_fake(q, k, v, softmax_scale, causal):
+    Z, N, H, _ = q.shape
+    return torch.empty_like(q), q.new_empty((Z, H, N), dtype=torch.float32)
+
+
+@torch.library.custom_op("flash_attn_v100::bwd", mutates_args=(), device_types="cuda")
+def _bwd_op(dout: torch.Tensor, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, out: torch.Tensor,
+            softmax_lse: torch.Tensor, softmax_scale: float, causal: bool
+            ) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    dq, dk, dv = flash_attn_cuda.bwd(
+        dout, q, k, v, out,
+        None,          # D: computed by the extension in fp32
+        None,          # softmax_sum: softmax_lse already is max + ln(sum)
+        softmax_lse,
+        None, None, None, softmax_scale, causal,
+    )
+    return dq, dk, dv
+
+
+@_bwd_op.register_fake
+def _bwd_fake(dout, q, k, v, out, softmax_lse, softmax_scale, causal):
+    return torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+
+
 def _flash_attn_forward(q, k, v, softmax_scale, causal):
     q, k, v = [_maybe_contiguous(x) for x in (q, k, v)]
-    out, softmax_lse, softmax_sum = flash_attn_cuda.fwd(q, k, v, None, softmax_scale, causal)
-    return out, q, k, v, softmax_lse, softmax_sum
+    out, softmax_lse = _fwd_op(q, k, v, float(softmax_scale), bool(causal))
+    return out, q, k, v, softmax_lse, None
 
 
 def _flash_attn_backward(dout, q, k, v, out, softmax_lse, softmax_sum, dq, dk, dv,
                          softmax_scale, causal):
-    # dq, dk, dv are allocated by us, so they are contiguous already
+    """Same arguments as the reference's (:26-60).  With preallocated ``dq, dk, dv`` or a
+    ``softmax_sum`` (the reference's calling convention) the extension is called directly;
+    otherwise through the registered op, which allocates the gradients itself."""
     dout, q, k, v, out = [_maybe_contiguous(x) for x in (dout, q, k, v, out)]
+    if dq is None and dk is None and dv is None and softmax_sum is None:
+        return _bwd_op(dout, q, k, v, out, softmax_lse, float(softmax_scale), bool(causal))
     dq, dk, dv = flash_attn_cuda.bwd(
         dout, q, k, v, out,
         None,          # D: computed by the extension in fp32
-        softmax_sum,   # None here: softmax_lse already is max + ln(sum)
+        softmax_sum,
         softmax_lse,
         dq, dk, dv, softmax_scale, causal,
     )
@@ -64,9 +107,9 @@ class FlashAttnFunc(torch.autograd.Function):
     @staticmethod
     def backward(ctx, dout, *args):
         q, k, v, out, softmax_lse = ctx.saved_tensors
-        dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
-        _flash_attn_backward(dout, q, k, v, out, softmax_lse, None, dq, dk, dv,
-                             ctx.softmax_scale, ctx.causal)
+        # no zero-filled gradients as in the reference (:84): the kernels overwrite them
+        dq, dk, dv = _flash_attn_backward(dout, q, k, v, out, softmax_lse, None, None, None, None,
+                                          ctx.softmax_scale, ctx.causal)
         return dq, dk, dv, None, None
 
 

@@ -23,8 +23,15 @@
  *  - `stream` is a cudaStream_t passed as void*.  All launches are asynchronous on it.
  *  - `status` (optional, may be NULL) points to one int32 in DEVICE memory that the caller
  *    zeroes once; a kernel that gives up on a bounded wait writes a non-zero code there.
- *  - Thread safety: entry points keep no mutable global state and may be called from any
- *    thread with the target device current.
+ *  - Sequence lengths: the C ABI accepts any positive seqlen_q / seqlen_k; tails of the
+ *    128-row tiles are masked inside the kernels.  The reference's "multiple of 32" contract
+ *    (README.md:3) is enforced one level up, by the torch extension's `fwd` / `bwd`.
+ *  - Thread safety: entry points may be called from any thread with the target device
+ *    current.  The only process-wide state is read-mostly: the resolved driver entry point
+ *    for tensor-map encoding, and, for fmha_bwd_static_scratch, the per-device address of the
+ *    built-in scratch area (looked up once per device ordinal in the primary context; it
+ *    goes stale if that context is destroyed with cudaDeviceReset) and the area itself,
+ *    which every call of that entry point on a device shares (see there).
  */
 #ifndef FMHA_B200_H_
 #define FMHA_B200_H_
@@ -91,7 +98,10 @@ typedef struct {
   float* dv_accum;  /* optional fp32 (Z, seqlen_k, H, D): dV is ADDED into it */
   /* element stride between batch entries of dk_accum / dv_accum; 0 = dense
    * (seqlen_k * H * D).  Rows and heads are dense.  Lets a row range of a larger buffer be
-   * the target (ring attention adds into the first half of a travelling block). */
+   * the target (ring attention adds into the first half of a travelling block).  Must be 0, or
+   * a multiple of 4 elements (the adds are 16-byte accesses) that is at least
+   * seqlen_k * H * D (batch entries must not overlap); anything else, negative values
+   * included, is rejected with FMHA_ERR_BAD_STRIDE. */
   int64_t accum_batch_stride;
   FmhaStrides q_strides, k_strides, v_strides, o_strides, dout_strides;
   FmhaStrides dq_strides, dk_strides, dv_strides;
@@ -151,16 +161,23 @@ int fmha_bwd(const FmhaBwdParams* p, void* workspace, size_t workspace_bytes, vo
  *
  *  - Limit: fmha_bwd_workspace_bytes(p) must not exceed FMHA_STATIC_SCRATCH_BYTES, otherwise
  *    FMHA_ERR_TOO_LARGE is returned and nothing is launched (e.g. Z*N*H*D <= ~8.3M elements).
- *  - Cost: every GPU on which the library is loaded holds the 32 MiB until the process exits,
- *    whether or not this entry point is ever called.
- *  - The first call on each device looks up the device address of the area (a host-side
- *    query, no allocation).  Make that first call outside any stream capture.
+ *  - Cost: every GPU on which the library's device code is loaded holds the 32 MiB until the
+ *    process exits, whether or not this entry point is ever called.  The CUDA runtime
+ *    reserves it when it loads the library's module on a device, which with lazy module
+ *    loading happens at the first fmha_* launch (or the first call of this entry point) on
+ *    that device, not at dlopen.  A host that hands all free HBM to its own pool must
+ *    therefore make one warm-up fmha_* call per device BEFORE it does so, outside stream
+ *    capture and outside any latency-critical section (module loading allocates and
+ *    synchronises inside the driver); after that warm-up this entry point never allocates.
+ *  - The first call on each device looks up the device address of the area and caches it
+ *    per device ordinal.  Make that first call outside any stream capture.
  *  - All calls on a device share the one area and it keeps whatever the last call left; each
  *    call re-initialises the parts it needs (dQ accumulator zeroed, statistics rewritten), so
  *    stale contents are harmless, but two calls that overlap on the GPU (different streams,
  *    or different host threads without ordering) race on it.  Serialise them on one stream.
- *  - FMHA_BWD_KEEP_WORKSPACE and FMHA_BWD_PREPROCESS_ONLY are rejected with FMHA_ERR_WORKSPACE: a
- *    shared area cannot carry state from one call to the next.
+ *  - FMHA_BWD_KEEP_WORKSPACE, FMHA_BWD_PREPROCESS_ONLY and FMHA_BWD_SKIP_DQ_CONVERT are rejected
+ *    with FMHA_ERR_WORKSPACE: a shared area cannot carry state from one call to the next, and
+ *    an unconverted dQ left in it would be out of the caller's reach.
  */
 int fmha_bwd_static_scratch(const FmhaBwdParams* p, void* stream);
 

@@ -102,6 +102,43 @@ def test_backward_workspace_size_and_validation(built_library):
     assert lib.fmha_bwd(ctypes.byref(p), 0x2000, 1 << 30, None) == 2
 
 
+def test_backward_rejects_bad_accumulator_batch_stride(built_library):
+    """dk_accum / dv_accum are added into with 16-byte accesses at accum + z * stride: a stride
+    that would misalign them, overlap batch entries or is negative is a status code, not a GPU
+    fault.  Validation returns before any CUDA call."""
+    from flash_attn_v100 import cabi
+
+    lib = cabi.load_library()
+    p = cabi.FmhaBwdParams()
+    for name in ("q", "k", "v", "o", "dout", "lse", "dq", "dk_accum", "dv_accum"):
+        setattr(p, name, 0x1000)
+    p.batch, p.heads, p.seqlen_q, p.seqlen_k, p.head_dim, p.scale = 2, 2, 64, 32, 64, 1.0
+    for s in (p.q_strides, p.o_strides, p.dout_strides, p.dq_strides):
+        s.batch, s.row, s.head = 64 * 2 * 64, 2 * 64, 64
+    for s in (p.k_strides, p.v_strides):
+        s.batch, s.row, s.head = 32 * 2 * 64, 2 * 64, 64
+    dense = 32 * 2 * 64
+    for stride in (-dense, dense + 2, dense - 4, 4):
+        p.accum_batch_stride = stride
+        assert lib.fmha_bwd(ctypes.byref(p), 0x2000, 1 << 30, None) == 4, stride
+    # 0 (dense) and a larger multiple of 4 pass validation (the next check to fail is the
+    # workspace, which is too small here)
+    for stride in (0, dense, 2 * dense + 4):
+        p.accum_batch_stride = stride
+        assert lib.fmha_bwd(ctypes.byref(p), 0x2000, 16, None) == 6, stride
+
+
+def test_static_scratch_refuses_flags_that_carry_state(built_library):
+    from flash_attn_v100 import cabi
+
+    lib = cabi.load_library()
+    p = cabi.FmhaBwdParams()
+    p.batch, p.heads, p.seqlen_q, p.seqlen_k, p.head_dim, p.scale = 1, 1, 32, 32, 64, 1.0
+    for flag in (cabi.FMHA_BWD_KEEP_WORKSPACE, cabi.FMHA_BWD_SKIP_DQ_CONVERT, cabi.FMHA_BWD_PREPROCESS_ONLY):
+        p.flags = flag
+        assert lib.fmha_bwd_static_scratch(ctypes.byref(p), None) == 6, flag
+
+
 def test_python_surface_matches_reference_names(built_library):
     """Same names as flash_attn_v100/flash_attn_interface.py and __init__.py of the reference."""
     import importlib.util

@@ -70,3 +70,38 @@ def test_reference_extension_calling_convention():
     ext.bwd(dout, q, k, v, out, D, softmax_sum, softmax_max, dq, dk, dv, 0.1, True)
     ref = oracle.attention_fwd_bwd(qc, kc, vc, doc, 0.1, True)
     helpers.check_against_oracle((out.cpu(), softmax_max.cpu(), dq.cpu(), dk.cpu(), dv.cpu()), ref, "ext")
+
+
+def test_registered_ops_and_torch_compile_fullgraph():
+    """The extension calls are ``torch.library`` ops with fake implementations, so
+    ``flash_attn_func`` compiles into one graph (the reference's glue,
+    flash_attn_interface.py:62-99, calls pybind functions the compiler cannot trace).  The
+    ``aot_eager`` backend traces forward and backward with fake tensors and runs the captured
+    graph eagerly: same kernels, same bits as the uncompiled call."""
+    from flash_attn_v100 import flash_attn_func
+
+    qc, kc, vc, doc = oracle.make_inputs(2, 256, 3, 128, seed=14)
+    dout = doc.cuda()
+
+    def loss(q, k, v):
+        return (flash_attn_func(q, k, v, 0.1, True).float() * dout.float()).sum()
+
+    def grads(fn):
+        q, k, v = (t.cuda().requires_grad_() for t in (qc, kc, vc))
+        fn(q, k, v).backward()
+        return q.grad, k.grad, v.grad
+
+    eager = grads(loss)
+    compiled = grads(torch.compile(loss, fullgraph=True, backend="aot_eager"))
+    assert torch.equal(eager[1], compiled[1]) and torch.equal(eager[2], compiled[2])
+    assert oracle.rel_l2(compiled[0].float().cpu(), eager[0].float().cpu()) < 1e-3  # dQ: fp32 add order
+    ref = oracle.attention_fwd_bwd(qc, kc, vc, doc, 0.1, True)
+    for a, b in zip(compiled, ref[2:]):
+        assert oracle.rel_l2(a.float().cpu(), b) <= helpers.TOL_GRAD_REL_L2
+    # schema, fake implementation and dispatch registration of both ops
+    q, k, v = qc.cuda(), kc.cuda(), vc.cuda()
+    torch.library.opcheck(torch.ops.flash_attn_v100.fwd.default, (q, k, v, 0.1, True),
+                          test_utils=("test_schema", "test_faketensor"))
+    out, lse = torch.ops.flash_attn_v100.fwd(q, k, v, 0.1, True)
+    torch.library.opcheck(torch.ops.flash_attn_v100.bwd.default, (dout, q, k, v, out, lse, 0.1, True),
+                          test_utils=("test_schema", "test_faketensor"))

@@ -77,3 +77,26 @@ def test_flop_model():
 
 def test_default_scale():
     assert oracle.default_scale(64) == 0.125
+
+
+@pytest.mark.parametrize("causal,shift,n_k", [(False, 0, None), (True, 0, None), (True, 64, 224), (True, -32, 96)])
+def test_blockwise_oracle_equals_the_plain_oracle(causal, shift, n_k):
+    """The chunked form (one group of heads and one chunk of query rows at a time, used where the
+    whole score matrix does not fit) is the same computation: identical up to fp32 summation
+    order, rows that see no key included."""
+    from oracle import attention_oracle_blockwise as blockwise
+
+    q, k, v, dout = oracle.make_inputs(2, 160, 3, 64, seed=17, n_k=n_k)
+    ref = oracle.attention_fwd_bwd(q, k, v, dout, 0.11, causal, shift)
+    got = blockwise.attention_fwd_bwd_blockwise(q, k, v, dout, 0.11, causal, shift, row_chunk=48,
+                                                head_chunk=2)
+    assert torch.equal(torch.isfinite(got[1]), torch.isfinite(ref[1]))
+    fin = torch.isfinite(ref[1])
+    assert oracle.max_abs(got[1][fin], ref[1][fin]) < 1e-5
+    for a, b in ((got[0], ref[0]), (got[2], ref[2]), (got[3], ref[3]), (got[4], ref[4])):
+        assert oracle.max_abs(a, b) < 2e-5
+    # a row subset keeps the rows' positions in the causal mask
+    rows = slice(64, 128)
+    o_r, l_r, dq_r = blockwise.attention_rows_blockwise(q, k, v, dout, rows, 0.11, causal, shift,
+                                                        row_chunk=40)
+    assert oracle.max_abs(o_r, ref[0][:, rows]) < 2e-5 and oracle.max_abs(dq_r, ref[2][:, rows]) < 2e-5
