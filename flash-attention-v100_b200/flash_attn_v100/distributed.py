@@ -80,6 +80,9 @@ class CudaBackend:
         # every SM given away is attention throughput lost.
         self.sm_margin = sm_margin
 
+    def comm_name(self, world: int) -> str:
+        return "NCCL send/recv" if world > 1 else "one rank, no exchange"
+
     def fwd(self, q, k, v, scale, causal, overlap: bool = False):
         return self.cabi.fwd(q, k, v, scale, causal, sm_margin=self.sm_margin if overlap else 0)
 
@@ -135,9 +138,13 @@ class CudaBackend:
 # ----------------------------------------------------------------------------------------------
 # ring plumbing
 # ----------------------------------------------------------------------------------------------
-def _exchange(tensors: List[torch.Tensor], group, rank: int, world: int):
+def _exchange(tensors: List[torch.Tensor], group, rank: int, world: int, comm: bool = True):
     """Post sends of ``tensors`` to rank+1 and receives of same-shaped buffers from rank-1;
-    returns (requests, received buffers).  The caller waits before touching the buffers."""
+    returns (requests, received buffers).  The caller waits before touching the buffers.
+    ``comm=False`` (measurements only) leaves the exchange out: the "received" buffers are the
+    tensors themselves, so that the same kernels run on the same shapes with nothing sent."""
+    if not comm:
+        return [], list(tensors)
     dst = dist.get_global_rank(group, (rank + 1) % world) if group is not None else (rank + 1) % world
     src = dist.get_global_rank(group, (rank - 1) % world) if group is not None else (rank - 1) % world
     bufs = [torch.empty_like(t) for t in tensors]
@@ -153,8 +160,8 @@ def _wait(reqs):
         r.wait()
 
 
-def ring_attention_forward(q, k, v, scale: float, causal: bool, group=None, backend=None
-                           ) -> Tuple[torch.Tensor, torch.Tensor]:
+def ring_attention_forward(q, k, v, scale: float, causal: bool, group=None, backend=None,
+                           comm: bool = True) -> Tuple[torch.Tensor, torch.Tensor]:
     """Forward over a zig-zag-sharded sequence: returns this rank's (out, lse) shard.
 
     q, k, v: (Z, 2c, H, D) local shards (``zigzag_split``).  K/V blocks rotate rank -> rank+1;
@@ -168,7 +175,7 @@ def ring_attention_forward(q, k, v, scale: float, causal: bool, group=None, back
     for step in range(world):
         reqs = None
         if step + 1 < world:
-            reqs, (k_nxt, v_nxt) = _exchange([k_cur, v_cur], group, rank, world)
+            reqs, (k_nxt, v_nxt) = _exchange([k_cur, v_cur], group, rank, world, comm)
         src = (rank - step) % world
         ov = reqs is not None  # an exchange is in flight beside this step's kernel
         if step == 0:
@@ -190,7 +197,7 @@ def ring_attention_forward(q, k, v, scale: float, causal: bool, group=None, back
 
 
 def ring_attention_backward(q, k, v, out, lse, dout, scale: float, causal: bool, group=None,
-                            backend=None):
+                            backend=None, comm: bool = True):
     """Backward over the same sharding: returns this rank's (dq, dk, dv) shards.
 
     The K/V block and its fp32 (dK, dV) accumulator travel together; after ``world`` hops the
@@ -208,7 +215,7 @@ def ring_attention_backward(q, k, v, out, lse, dout, scale: float, causal: bool,
         # the next block's K/V can travel while this step computes; dK/dV follow afterwards
         reqs_kv = None
         if step + 1 < world:
-            reqs_kv, (k_nxt, v_nxt) = _exchange([k_cur, v_cur], group, rank, world)
+            reqs_kv, (k_nxt, v_nxt) = _exchange([k_cur, v_cur], group, rank, world, comm)
         src = (rank - step) % world
         if step == 0:
             backend.bwd_step(state, "full", q, k_cur, v_cur, out, dout, lse, scale, causal, dk_cur, dv_cur)
@@ -221,7 +228,7 @@ def ring_attention_backward(q, k, v, out, lse, dout, scale: float, causal: bool,
             backend.bwd_step(state, "half", q[:, half:], k_cur, v_cur, out[:, half:], dout[:, half:],
                              lse_half, scale, False, dk_cur, dv_cur)
         # hand the accumulators on (also after the last step: that hop brings them home)
-        reqs_g, (dk_nxt, dv_nxt) = _exchange([dk_cur, dv_cur], group, rank, world)
+        reqs_g, (dk_nxt, dv_nxt) = _exchange([dk_cur, dv_cur], group, rank, world, comm)
         if reqs_kv is not None:
             _wait(reqs_kv)
             k_cur, v_cur = k_nxt, v_nxt

@@ -33,7 +33,7 @@ def test_reference_arm_line_on_host_cores():
 
 @pytest.mark.gpu
 def test_our_arm_line_has_roofline_baseline_e2e_and_clocks():
-    d = _run("--steps", "3", "--warmup", "3", "--workload", "cfg2_causal")
+    d = _run("--steps", "3", "--warmup", "3", "--regions", "3", "--workload", "cfg2_causal")
     assert BASE_KEYS <= set(d) and "impl" not in d
     assert d["n_gpus"] == 1 and d["steps"] == 3 and d["gpu_launches"] == 12
     r = d["roofline"]
@@ -43,3 +43,5 @@ def test_our_arm_line_has_roofline_baseline_e2e_and_clocks():
     assert d["e2e"]["value"] > 0 and d["e2e"]["h2d_bytes_per_step"] > 0
     assert {"sm_mhz", "sm_max_mhz", "reasons"} <= set(d["clocks"])
     assert d["config"]["launch"].startswith("CUDA graph") or d["config"]["launch"].startswith("four")
+    assert d["regions"]["count"] == 3 and d["regions"]["min_ms"] <= d["ms_per_step"] <= d["regions"]["max_ms"]
+    assert 0.8 < d["kernels"]["sum_of_parts_over_step"] < 1.6
