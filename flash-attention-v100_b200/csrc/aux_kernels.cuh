@@ -6,11 +6,14 @@
 //     accumulation (kernel/fused_mha_kernel.cu:543,693) together with the fp32 accumulator.
 //   - merge: LSE-weighted merge of a partial attention result into running fp32
 //     accumulators (ring attention; no counterpart in the reference).
-// Each thread owns 8 consecutive head_dim elements (one 16-byte fp16 load) of one row.
+// Each thread owns 8 consecutive head_dim elements (one 16-byte load of fp16 or bf16) of one row.
 #pragma once
+#include <cuda_bf16.h>
 #include <cuda_fp16.h>
 #include <math_constants.h>
 #include <stdint.h>
+
+#include <type_traits>
 
 namespace fmha {
 
@@ -18,28 +21,47 @@ struct Strides3 {
   long long batch, row, head;
 };
 
+// E = __half or __nv_bfloat16: the 16-bit element type of the tensors
+template <typename E>
 __device__ __forceinline__ void unpack8(const uint4& u, float (&f)[8]) {
-  const __half2* h = reinterpret_cast<const __half2*>(&u);
+  if constexpr (sizeof(E) == 2 && std::is_same<E, __nv_bfloat16>::value) {
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
 #pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    const float2 t = __half22float2(h[i]);
-    f[2 * i] = t.x;
-    f[2 * i + 1] = t.y;
+    for (int i = 0; i < 4; ++i) {
+      const float2 t = __bfloat1622float2(h[i]);
+      f[2 * i] = t.x;
+      f[2 * i + 1] = t.y;
+    }
+  } else {
+    const __half2* h = reinterpret_cast<const __half2*>(&u);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float2 t = __half22float2(h[i]);
+      f[2 * i] = t.x;
+      f[2 * i + 1] = t.y;
+    }
   }
 }
+template <typename E>
 __device__ __forceinline__ uint4 pack8(const float (&f)[8]) {
   uint4 u;
-  __half2* h = reinterpret_cast<__half2*>(&u);
+  if constexpr (std::is_same<E, __nv_bfloat16>::value) {
+    __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&u);
 #pragma unroll
-  for (int i = 0; i < 4; ++i) h[i] = __floats2half2_rn(f[2 * i], f[2 * i + 1]);
+    for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+  } else {
+    __half2* h = reinterpret_cast<__half2*>(&u);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) h[i] = __floats2half2_rn(f[2 * i], f[2 * i + 1]);
+  }
   return u;
 }
 
 // rows are indexed (zh, q) over the PADDED query length so that lse2 / delta are complete
-template <int D>
+template <int D, typename E>
 __global__ void __launch_bounds__(256)
-    fmha_bwd_preprocess_kernel(const __half* __restrict__ o, Strides3 so,
-                               const __half* __restrict__ dout, Strides3 sdo,
+    fmha_bwd_preprocess_kernel(const E* __restrict__ o, Strides3 so,
+                               const E* __restrict__ dout, Strides3 sdo,
                                const float* __restrict__ lse, float* __restrict__ dq_accum,
                                float* __restrict__ lse2, float* __restrict__ delta, int heads,
                                int seqlen_q, int seqlen_q_pad, long long total_rows) {
@@ -63,8 +85,8 @@ __global__ void __launch_bounds__(256)
   const uint4 ud =
       *reinterpret_cast<const uint4*>(dout + z * sdo.batch + q * sdo.row + h * sdo.head + part * 8);
   float fo[8], fd[8];
-  unpack8(uo, fo);
-  unpack8(ud, fd);
+  unpack8<E>(uo, fo);
+  unpack8<E>(ud, fd);
   float acc = 0.f;
 #pragma unroll
   for (int i = 0; i < 8; ++i) acc = fmaf(fo[i], fd[i], acc);
@@ -82,9 +104,9 @@ __global__ void __launch_bounds__(256)
   }
 }
 
-template <int D>
+template <int D, typename E>
 __global__ void __launch_bounds__(256)
-    fmha_bwd_convert_dq_kernel(const float* __restrict__ dq_accum, __half* __restrict__ dq,
+    fmha_bwd_convert_dq_kernel(const float* __restrict__ dq_accum, E* __restrict__ dq,
                                Strides3 sdq, int heads, int seqlen_q, float scale,
                                long long total_rows) {
   constexpr int kGroup = D / 8;
@@ -101,14 +123,14 @@ __global__ void __launch_bounds__(256)
   const float4 a = src[0], b = src[1];
   float f[8] = {a.x * scale, a.y * scale, a.z * scale, a.w * scale,
                 b.x * scale, b.y * scale, b.z * scale, b.w * scale};
-  *reinterpret_cast<uint4*>(dq + z * sdq.batch + q * sdq.row + h * sdq.head + part * 8) = pack8(f);
+  *reinterpret_cast<uint4*>(dq + z * sdq.batch + q * sdq.row + h * sdq.head + part * 8) = pack8<E>(f);
 }
 
-template <int D>
+template <int D, typename E>
 __global__ void __launch_bounds__(256)
     fmha_merge_kernel(float* __restrict__ o_acc, float* __restrict__ lse_acc,
-                      const __half* __restrict__ o_part, Strides3 sp,
-                      const float* __restrict__ lse_part, __half* __restrict__ o_out, int heads,
+                      const E* __restrict__ o_part, Strides3 sp,
+                      const float* __restrict__ lse_part, E* __restrict__ o_out, int heads,
                       int rows, int acc_rows, int row_offset, long long total_rows) {
   constexpr int kGroup = D / 8;
   constexpr int kRowsPerBlock = 256 / kGroup;
@@ -143,14 +165,14 @@ __global__ void __launch_bounds__(256)
     const uint4 up =
         *reinterpret_cast<const uint4*>(o_part + z * sp.batch + q * sp.row + h * sp.head + part * 8);
     float fp[8];
-    unpack8(up, fp);
+    unpack8<E>(up, fp);
     float f[8] = {wa * a0.x + wb * fp[0], wa * a0.y + wb * fp[1], wa * a0.z + wb * fp[2],
                   wa * a0.w + wb * fp[3], wa * a1.x + wb * fp[4], wa * a1.y + wb * fp[5],
                   wa * a1.z + wb * fp[6], wa * a1.w + wb * fp[7]};
     acc[0] = make_float4(f[0], f[1], f[2], f[3]);
     acc[1] = make_float4(f[4], f[5], f[6], f[7]);
     if (o_out != nullptr)
-      *reinterpret_cast<uint4*>(o_out + acc_row * D + part * 8) = pack8(f);
+      *reinterpret_cast<uint4*>(o_out + acc_row * D + part * 8) = pack8<E>(f);
   }
   // every thread of a row has read lse_acc before its first thread overwrites it
   __syncwarp();

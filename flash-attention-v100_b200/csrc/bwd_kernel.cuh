@@ -49,6 +49,12 @@ struct BwdKernelParams {
   float scale, scale_log2;
   int causal, causal_shift;
   int* status;
+  // Deterministic dQ (not NULL): one word per (batch*head, query tile), zero at launch.  The
+  // CTAs that add into a query tile's dQ do so in the order of their KV tiles: CTA kb waits
+  // for the word to reach kb, adds, waits for its adds to complete and sets kb + 1.  The fp32
+  // additions then happen in one fixed order and dQ is the same bits on every run; the price
+  // is that the CTAs of a head run staggered by one query tile each.
+  int* dq_order;
   long long* timeline;  // debug builds (-DFMHA_TIMELINE) only
   int timeline_block;
 };
@@ -59,7 +65,7 @@ constexpr int kBwdRegsDq = 128 + (128 - kBwdRegsIssue) + 2 * (128 - kBwdRegsComp
 static_assert(kBwdRegsIssue <= 128 && kBwdRegsCompute <= 128 && kBwdRegsDq >= 128,
               "setmaxnreg.dec must not raise and .inc must not lower the 128 registers of the launch");
 
-template <int D>
+template <int D, bool kBf16 = false>
 struct BwdTraits {
   static constexpr int kBlock = 128;
   static constexpr int kBoxes = D / 64;
@@ -75,18 +81,18 @@ struct BwdTraits {
       1024 + (3 + kQStages) * kTileBytes + kDsBytes + kStageBytes + kStatBytes;
   static constexpr int kTmemCols = 512;
   static constexpr int kColS = 0, kColDP = 128, kColDQ = 128, kColDK = 256, kColDV = 256 + D;
-  static constexpr uint32_t kIdescST = umma_idesc_f16(128, 128, 0, 0);  // S^T, dP^T
-  static constexpr uint32_t kIdescDV = umma_idesc_f16(128, D, 0, 1);    // dV, dK
-  static constexpr uint32_t kIdescDQ = umma_idesc_f16(128, D, 1, 1);    // dQ
+  static constexpr uint32_t kIdescST = umma_idesc_f16(128, 128, 0, 0, kBf16);  // S^T, dP^T
+  static constexpr uint32_t kIdescDV = umma_idesc_f16(128, D, 0, 1, kBf16);    // dV, dK
+  static constexpr uint32_t kIdescDQ = umma_idesc_f16(128, D, 1, 1, kBf16);    // dQ
 };
 
-template <int D>
+template <int D, bool kBf16 = false>
 __global__ void __launch_bounds__(512, 1)
     fmha_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                     const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_do,
                     const __grid_constant__ CUtensorMap tm_dk, const __grid_constant__ CUtensorMap tm_dv,
                     const __grid_constant__ CUtensorMap tm_dqacc, const BwdKernelParams p) {
-  using T = BwdTraits<D>;
+  using T = BwdTraits<D, kBf16>;
   extern __shared__ uint8_t smem_raw[];
   __shared__ uint64_t bar_kv_full;
   __shared__ uint64_t bar_q_full[T::kQStages], bar_q_empty[T::kQStages];
@@ -341,8 +347,10 @@ __global__ void __launch_bounds__(512, 1)
         }
         const int fvh = first_visible - cg * 64;
 
-        uint32_t pp[32];  // P^T of this row and half, fp16 pairs
-        uint32_t npd[32]; // -(P^T o delta), fp16 pairs: dS^T = P^T o dP^T - P^T o delta
+        uint32_t pp[32];  // P^T of this row and half, 16-bit pairs
+        // fp16 only: -(P^T o delta) as fp16 pairs, so that dS^T = P^T o dP^T - P^T o delta is one
+        // half2 FMA per pair; with bf16 (8 mantissa bits) dS^T is formed in fp32 instead
+        uint32_t npd[kBf16 ? 1 : 32];
         if (tl) FMHA_TL(0, n, 0);
         mbar_wait(smem_u32(&bar_s_full), n & 1, &abort_word, 11);  // on a time-out: keep going,
         // every later wait returns at once and all 256 threads still meet at the named barrier
@@ -362,8 +370,14 @@ __global__ void __launch_bounds__(512, 1)
               const float x1 = fmaf(__uint_as_float(s[cc][i + 1]), c, -L.y);
               const float x2 = fmaf(__uint_as_float(s[cc][i + 2]), c, -L.z);
               const float x3 = fmaf(__uint_as_float(s[cc][i + 3]), c, -L.w);
-              pp[cc * 16 + (i >> 1) + 0] = exp2_half2(pack_half2(x0, x1));
-              pp[cc * 16 + (i >> 1) + 1] = exp2_half2(pack_half2(x2, x3));
+              if constexpr (kBf16) {
+                // a bf16 argument would cost P two to three digits: exponentials in fp32
+                pp[cc * 16 + (i >> 1) + 0] = pack_bf16x2(fast_exp2(x0), fast_exp2(x1));
+                pp[cc * 16 + (i >> 1) + 1] = pack_bf16x2(fast_exp2(x2), fast_exp2(x3));
+              } else {
+                pp[cc * 16 + (i >> 1) + 0] = exp2_half2(pack_half2(x0, x1));
+                pp[cc * 16 + (i >> 1) + 1] = exp2_half2(pack_half2(x2, x3));
+              }
             }
           if (fvh > 0) {
 #pragma unroll
@@ -379,11 +393,13 @@ __global__ void __launch_bounds__(512, 1)
         mbar_arrive(smem_u32(&bar_p_ready));
         if (tl) FMHA_TL(0, n, 2);
         // off the critical path (dP^T is not there yet): -(P o delta)
+        if constexpr (!kBf16) {
 #pragma unroll
-        for (int j = 0; j < 32; j += 2) {
-          const float4 Dl = lds128(sb + 512 + (cg * 64 + 2 * j) * 4);
-          npd[j + 0] = mul_half2(pp[j + 0], pack_half2(-Dl.x, -Dl.y));
-          npd[j + 1] = mul_half2(pp[j + 1], pack_half2(-Dl.z, -Dl.w));
+          for (int j = 0; j < 32; j += 2) {
+            const float4 Dl = lds128(sb + 512 + (cg * 64 + 2 * j) * 4);
+            npd[j + 0] = mul_half2(pp[j + 0], pack_half2(-Dl.x, -Dl.y));
+            npd[j + 1] = mul_half2(pp[j + 1], pack_half2(-Dl.z, -Dl.w));
+          }
         }
 
         mbar_wait(smem_u32(&bar_dp_full), n & 1, &abort_word, 12);
@@ -403,13 +419,25 @@ __global__ void __launch_bounds__(512, 1)
 #pragma unroll
             for (int k8 = 0; k8 < 4; ++k8) {  // 8 columns = one 16-byte chunk
               uint32_t w[4];
+              float dl[8];  // bf16 only: delta of this chunk's 8 query columns
+              if constexpr (kBf16) {
+                const float4 Da = lds128(sb + 512 + (cg * 64 + cc * 32 + k8 * 8) * 4);
+                const float4 Db = lds128(sb + 512 + (cg * 64 + cc * 32 + k8 * 8 + 4) * 4);
+                dl[0] = Da.x, dl[1] = Da.y, dl[2] = Da.z, dl[3] = Da.w;
+                dl[4] = Db.x, dl[5] = Db.y, dl[6] = Db.z, dl[7] = Db.w;
+              }
 #pragma unroll
               for (int q2 = 0; q2 < 4; ++q2) {
                 const int i = k8 * 8 + q2 * 2;     // column within this 32-column block
                 const int j = cc * 16 + (i >> 1);  // its fp16 pair
-                w[q2] = fma_half2(pp[j],
-                                  pack_half2(__uint_as_float(dp[cc][i]), __uint_as_float(dp[cc][i + 1])),
-                                  npd[j]);
+                if constexpr (kBf16) {
+                  w[q2] = pack_bf16x2(bf16_lo(pp[j]) * (__uint_as_float(dp[cc][i]) - dl[q2 * 2]),
+                                      bf16_hi(pp[j]) * (__uint_as_float(dp[cc][i + 1]) - dl[q2 * 2 + 1]));
+                } else {
+                  w[q2] = fma_half2(pp[j],
+                                    pack_half2(__uint_as_float(dp[cc][i]), __uint_as_float(dp[cc][i + 1])),
+                                    npd[j]);
+                }
               }
               const int ch = cc * 4 + k8;  // chunk of this thread's 128-byte row
               sts128(row_addr + ((ch ^ (r & 7)) << 4), w[0], w[1], w[2], w[3]);
@@ -454,9 +482,23 @@ __global__ void __launch_bounds__(512, 1)
           fence_proxy_async_smem();
           named_bar_sync(2, 128);
           if (r == 0) {
+            int* order_word = p.dq_order == nullptr
+                                  ? nullptr
+                                  : p.dq_order + (size_t)zh * nq_tiles + (i_begin + n);
+            if (order_word != nullptr && cc == 0) {
+              // the KV tiles before this one have added their share of this query tile
+              global_flag_wait(order_word, kb, &abort_word, p.status, 17);
+              fence_proxy_async_all();
+            }
             tma_reduce_add_4d(&tm_dqacc, stg_smem + (cc & 1) * 16384, cc * 32,
                               (i_begin + n) * T::kBlock, h, z);
             tma_commit_group();
+            if (order_word != nullptr && cc == D / 32 - 1) {
+              tma_wait_group<0>();  // the adds have been performed, not just read from shared memory
+              fence_proxy_async_all();
+              __threadfence();
+              global_flag_release(order_word, kb + 1);
+            }
           }
         }
         if (tl) FMHA_TL(1, n, 3);
@@ -514,10 +556,10 @@ __global__ void __launch_bounds__(512, 1)
             const uint32_t addr =
                 out_smem + (ch >> 3) * T::kBoxBytes + r * 128 + (((ch & 7) ^ (r & 7)) << 4);
             sts128(addr,
-                   pack_half2(__uint_as_float(a[k4 * 8 + 0]) * mul, __uint_as_float(a[k4 * 8 + 1]) * mul),
-                   pack_half2(__uint_as_float(a[k4 * 8 + 2]) * mul, __uint_as_float(a[k4 * 8 + 3]) * mul),
-                   pack_half2(__uint_as_float(a[k4 * 8 + 4]) * mul, __uint_as_float(a[k4 * 8 + 5]) * mul),
-                   pack_half2(__uint_as_float(a[k4 * 8 + 6]) * mul, __uint_as_float(a[k4 * 8 + 7]) * mul));
+                   pack16x2<kBf16>(__uint_as_float(a[k4 * 8 + 0]) * mul, __uint_as_float(a[k4 * 8 + 1]) * mul),
+                   pack16x2<kBf16>(__uint_as_float(a[k4 * 8 + 2]) * mul, __uint_as_float(a[k4 * 8 + 3]) * mul),
+                   pack16x2<kBf16>(__uint_as_float(a[k4 * 8 + 4]) * mul, __uint_as_float(a[k4 * 8 + 5]) * mul),
+                   pack16x2<kBf16>(__uint_as_float(a[k4 * 8 + 6]) * mul, __uint_as_float(a[k4 * 8 + 7]) * mul));
           }
         }
         fence_proxy_async_smem();

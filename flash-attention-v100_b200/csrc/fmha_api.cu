@@ -11,6 +11,7 @@
 #include <cmath>
 #include <cstdint>
 #include <cstring>
+#include <type_traits>
 
 #include "../../include/fmha_b200.h"
 #include "aux_kernels.cuh"
@@ -38,10 +39,10 @@ EncodeTiledFn get_encode_fn() {
   return fn;
 }
 
-// fp16 (Z, N, H, D) tensor with element strides -> 4-D map (D, N, H, Z), box 64 x box_rows x 1
+// 16-bit (Z, N, H, D) tensor with element strides -> 4-D map (D, N, H, Z), box 64 x box_rows x 1
 // x 1, 128-byte swizzle, zero fill outside the tensor
 int make_tensor_map(CUtensorMap* map, const void* base, int Z, int N, int H, int D,
-                    const FmhaStrides& s, unsigned box_rows = 128) {
+                    const FmhaStrides& s, bool bf16, unsigned box_rows = 128) {
   EncodeTiledFn encode = get_encode_fn();
   if (encode == nullptr) return FMHA_ERR_NO_DEVICE;
   // a stride of a size-1 dimension is never used for addressing; make it well-formed
@@ -52,7 +53,8 @@ int make_tensor_map(CUtensorMap* map, const void* base, int Z, int N, int H, int
   const cuuint64_t strides[3] = {(cuuint64_t)row * 2, (cuuint64_t)head * 2, (cuuint64_t)batch * 2};
   const cuuint32_t box[4] = {64, box_rows, 1, 1};
   const cuuint32_t estr[4] = {1, 1, 1, 1};
-  const CUresult r = encode(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4, const_cast<void*>(base), dims,
+  const CUresult r = encode(map, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16,
+                            4, const_cast<void*>(base), dims,
                             strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                             CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
@@ -95,7 +97,9 @@ int check_strides(const FmhaStrides& s, int N, int H, int Z) {
   return FMHA_OK;
 }
 
-int check_common(int batch, int heads, int seqlen_q, int seqlen_k, int head_dim, float scale) {
+int check_common(int batch, int heads, int seqlen_q, int seqlen_k, int head_dim, float scale,
+                 int dtype = FMHA_DTYPE_FP16) {
+  if (dtype != FMHA_DTYPE_FP16 && dtype != FMHA_DTYPE_BF16) return FMHA_ERR_BAD_DTYPE;
   if (head_dim != 64 && head_dim != 128) return FMHA_ERR_BAD_HEAD_DIM;
   if (batch <= 0 || heads <= 0 || seqlen_q <= 0 || seqlen_k <= 0) return FMHA_ERR_BAD_SHAPE;
   if (!std::isfinite(scale) || scale == 0.f) return FMHA_ERR_BAD_SHAPE;
@@ -113,6 +117,8 @@ struct BwdWorkspace {
   float* dq_accum;
   float* lse2;
   float* delta;
+  int* dq_order;       // one word per (batch*head, query tile): FMHA_BWD_DETERMINISTIC
+  size_t order_bytes;
   size_t bytes;
 };
 
@@ -124,22 +130,28 @@ BwdWorkspace carve_workspace(void* ws, int Z, int H, int Nq, int D) {
   w.dq_accum = reinterpret_cast<float*>(base);
   w.lse2 = reinterpret_cast<float*>(base + dq_bytes);
   w.delta = reinterpret_cast<float*>(base + dq_bytes + stat_bytes);
-  w.bytes = dq_bytes + 2 * stat_bytes;
+  w.dq_order = reinterpret_cast<int*>(base + dq_bytes + 2 * stat_bytes);
+  w.order_bytes = (size_t)Z * H * (round_up_128(Nq) / 128) * sizeof(int);
+  w.bytes = dq_bytes + 2 * stat_bytes + (w.order_bytes + 255) / 256 * 256;
   return w;
 }
 
-template <int D>
+template <int D, bool kBf16>
 int launch_fwd(const FmhaFwdParams* p, cudaStream_t stream) {
-  using T = fmha::FwdTraits<D>;
+  using T = fmha::FwdTraits<D, kBf16>;
   CUtensorMap tq, tk, tv, to;
   int rc;
-  if ((rc = make_tensor_map(&tq, p->q, p->batch, p->seqlen_q, p->heads, D, p->q_strides))) return rc;
+  if ((rc = make_tensor_map(&tq, p->q, p->batch, p->seqlen_q, p->heads, D, p->q_strides, kBf16)))
+    return rc;
   // K and V are loaded in half tiles of kStepN rows
-  if ((rc = make_tensor_map(&tk, p->k, p->batch, p->seqlen_k, p->heads, D, p->k_strides, T::kStepN)))
+  if ((rc = make_tensor_map(&tk, p->k, p->batch, p->seqlen_k, p->heads, D, p->k_strides, kBf16,
+                            T::kStepN)))
     return rc;
-  if ((rc = make_tensor_map(&tv, p->v, p->batch, p->seqlen_k, p->heads, D, p->v_strides, T::kStepN)))
+  if ((rc = make_tensor_map(&tv, p->v, p->batch, p->seqlen_k, p->heads, D, p->v_strides, kBf16,
+                            T::kStepN)))
     return rc;
-  if ((rc = make_tensor_map(&to, p->o, p->batch, p->seqlen_q, p->heads, D, p->o_strides))) return rc;
+  if ((rc = make_tensor_map(&to, p->o, p->batch, p->seqlen_q, p->heads, D, p->o_strides, kBf16)))
+    return rc;
   fmha::FwdKernelParams kp;
   kp.lse = p->lse;
   kp.heads = p->heads;
@@ -153,7 +165,7 @@ int launch_fwd(const FmhaFwdParams* p, cudaStream_t stream) {
   kp.status = p->status;
   kp.timeline = g_timeline;
   kp.timeline_block = g_timeline_block;
-  auto kernel = fmha::fmha_fwd_kernel<D>;
+  auto kernel = fmha::fmha_fwd_kernel<D, kBf16>;
   if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, T::kSmemBytes) !=
       cudaSuccess)
     return FMHA_ERR_LAUNCH;
@@ -165,9 +177,10 @@ int launch_fwd(const FmhaFwdParams* p, cudaStream_t stream) {
   return cudaGetLastError() == cudaSuccess ? FMHA_OK : FMHA_ERR_LAUNCH;
 }
 
-template <int D>
+template <int D, bool kBf16>
 int launch_bwd(const FmhaBwdParams* p, const BwdWorkspace& w, cudaStream_t stream) {
-  using T = fmha::BwdTraits<D>;
+  using T = fmha::BwdTraits<D, kBf16>;
+  using E = typename std::conditional<kBf16, __nv_bfloat16, __half>::type;
   const int Z = p->batch, H = p->heads, Nq = p->seqlen_q, Nk = p->seqlen_k;
   const int Nq_pad = round_up_128(Nq);
 
@@ -175,8 +188,8 @@ int launch_bwd(const FmhaBwdParams* p, const BwdWorkspace& w, cudaStream_t strea
     const long long rows = (long long)Z * H * Nq_pad;
     constexpr int rows_per_block = 256 / (D / 8);
     const unsigned grid = (unsigned)((rows + rows_per_block - 1) / rows_per_block);
-    fmha::fmha_bwd_preprocess_kernel<D><<<grid, 256, 0, stream>>>(
-        static_cast<const __half*>(p->o), to3(p->o_strides), static_cast<const __half*>(p->dout),
+    fmha::fmha_bwd_preprocess_kernel<D, E><<<grid, 256, 0, stream>>>(
+        static_cast<const E*>(p->o), to3(p->o_strides), static_cast<const E*>(p->dout),
         to3(p->dout_strides), p->lse, w.dq_accum, w.lse2, w.delta, H, Nq, Nq_pad, rows);
     if (cudaGetLastError() != cudaSuccess) return FMHA_ERR_LAUNCH;
   }
@@ -186,17 +199,17 @@ int launch_bwd(const FmhaBwdParams* p, const BwdWorkspace& w, cudaStream_t strea
     CUtensorMap tq, tk, tv, tdo, tdk, tdv, tacc;
     int rc;
     if ((rc = make_accum_map(&tacc, w.dq_accum, Z, Nq, H, D))) return rc;
-    if ((rc = make_tensor_map(&tq, p->q, Z, Nq, H, D, p->q_strides))) return rc;
-    if ((rc = make_tensor_map(&tk, p->k, Z, Nk, H, D, p->k_strides))) return rc;
-    if ((rc = make_tensor_map(&tv, p->v, Z, Nk, H, D, p->v_strides))) return rc;
-    if ((rc = make_tensor_map(&tdo, p->dout, Z, Nq, H, D, p->dout_strides))) return rc;
+    if ((rc = make_tensor_map(&tq, p->q, Z, Nq, H, D, p->q_strides, kBf16))) return rc;
+    if ((rc = make_tensor_map(&tk, p->k, Z, Nk, H, D, p->k_strides, kBf16))) return rc;
+    if ((rc = make_tensor_map(&tv, p->v, Z, Nk, H, D, p->v_strides, kBf16))) return rc;
+    if ((rc = make_tensor_map(&tdo, p->dout, Z, Nq, H, D, p->dout_strides, kBf16))) return rc;
     // with fp32 accumulation the fp16 outputs are not touched: any valid map will do
     const bool acc_k = p->dk_accum != nullptr, acc_v = p->dv_accum != nullptr;
     if ((rc = make_tensor_map(&tdk, acc_k ? p->k : p->dk, Z, Nk, H, D,
-                              acc_k ? p->k_strides : p->dk_strides)))
+                              acc_k ? p->k_strides : p->dk_strides, kBf16)))
       return rc;
     if ((rc = make_tensor_map(&tdv, acc_v ? p->v : p->dv, Z, Nk, H, D,
-                              acc_v ? p->v_strides : p->dv_strides)))
+                              acc_v ? p->v_strides : p->dv_strides, kBf16)))
       return rc;
     fmha::BwdKernelParams kp;
     kp.lse2 = w.lse2;
@@ -215,9 +228,15 @@ int launch_bwd(const FmhaBwdParams* p, const BwdWorkspace& w, cudaStream_t strea
     kp.causal = p->causal ? 1 : 0;
     kp.causal_shift = p->causal_shift;
     kp.status = p->status;
+    kp.dq_order = nullptr;
+    if (p->flags & FMHA_BWD_DETERMINISTIC) {
+      // a memset node, not an allocation; every call starts its own count at zero
+      if (cudaMemsetAsync(w.dq_order, 0, w.order_bytes, stream) != cudaSuccess) return FMHA_ERR_LAUNCH;
+      kp.dq_order = w.dq_order;
+    }
     kp.timeline = g_timeline;
     kp.timeline_block = g_timeline_block;
-    auto kernel = fmha::fmha_bwd_kernel<D>;
+    auto kernel = fmha::fmha_bwd_kernel<D, kBf16>;
     if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, T::kSmemBytes) !=
         cudaSuccess)
       return FMHA_ERR_LAUNCH;
@@ -230,8 +249,8 @@ int launch_bwd(const FmhaBwdParams* p, const BwdWorkspace& w, cudaStream_t strea
     const long long rows = (long long)Z * Nq * H;
     constexpr int rows_per_block = 256 / (D / 8);
     const unsigned grid = (unsigned)((rows + rows_per_block - 1) / rows_per_block);
-    fmha::fmha_bwd_convert_dq_kernel<D><<<grid, 256, 0, stream>>>(
-        w.dq_accum, static_cast<__half*>(p->dq), to3(p->dq_strides), H, Nq, p->scale, rows);
+    fmha::fmha_bwd_convert_dq_kernel<D, E><<<grid, 256, 0, stream>>>(
+        w.dq_accum, static_cast<E*>(p->dq), to3(p->dq_strides), H, Nq, p->scale, rows);
     if (cudaGetLastError() != cudaSuccess) return FMHA_ERR_LAUNCH;
   }
   return FMHA_OK;
@@ -285,7 +304,7 @@ int fmha_fwd(const FmhaFwdParams* p, void* stream) {
   if (p == nullptr || p->q == nullptr || p->k == nullptr || p->v == nullptr || p->o == nullptr ||
       p->lse == nullptr)
     return FMHA_ERR_NULL_POINTER;
-  int rc = check_common(p->batch, p->heads, p->seqlen_q, p->seqlen_k, p->head_dim, p->scale);
+  int rc = check_common(p->batch, p->heads, p->seqlen_q, p->seqlen_k, p->head_dim, p->scale, p->dtype);
   if (rc) return rc;
   if (!aligned16(p->q) || !aligned16(p->k) || !aligned16(p->v) || !aligned16(p->o))
     return FMHA_ERR_BAD_ALIGNMENT;
@@ -294,7 +313,9 @@ int fmha_fwd(const FmhaFwdParams* p, void* stream) {
   if ((rc = check_strides(p->v_strides, p->seqlen_k, p->heads, p->batch))) return rc;
   if ((rc = check_strides(p->o_strides, p->seqlen_q, p->heads, p->batch))) return rc;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  return p->head_dim == 128 ? launch_fwd<128>(p, s) : launch_fwd<64>(p, s);
+  if (p->dtype == FMHA_DTYPE_BF16)
+    return p->head_dim == 128 ? launch_fwd<128, true>(p, s) : launch_fwd<64, true>(p, s);
+  return p->head_dim == 128 ? launch_fwd<128, false>(p, s) : launch_fwd<64, false>(p, s);
 }
 
 size_t fmha_bwd_workspace_bytes(const FmhaBwdParams* p) {
@@ -315,7 +336,7 @@ int fmha_bwd(const FmhaBwdParams* p, void* workspace, size_t workspace_bytes, vo
   if (!skip_convert && p->dq == nullptr) return FMHA_ERR_NULL_POINTER;
   if (p->dk_accum == nullptr && p->dk == nullptr) return FMHA_ERR_NULL_POINTER;
   if (p->dv_accum == nullptr && p->dv == nullptr) return FMHA_ERR_NULL_POINTER;
-  int rc = check_common(p->batch, p->heads, p->seqlen_q, p->seqlen_k, p->head_dim, p->scale);
+  int rc = check_common(p->batch, p->heads, p->seqlen_q, p->seqlen_k, p->head_dim, p->scale, p->dtype);
   if (rc) return rc;
   if (!aligned16(p->q) || !aligned16(p->k) || !aligned16(p->v) || !aligned16(p->dout) ||
       (!keep && !aligned16(p->o)) || (!skip_convert && !aligned16(p->dq)) ||
@@ -344,7 +365,9 @@ int fmha_bwd(const FmhaBwdParams* p, void* workspace, size_t workspace_bytes, vo
   if (workspace == nullptr || workspace_bytes < w.bytes) return FMHA_ERR_WORKSPACE;
   if (!aligned16(workspace)) return FMHA_ERR_BAD_ALIGNMENT;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  return p->head_dim == 128 ? launch_bwd<128>(p, w, s) : launch_bwd<64>(p, w, s);
+  if (p->dtype == FMHA_DTYPE_BF16)
+    return p->head_dim == 128 ? launch_bwd<128, true>(p, w, s) : launch_bwd<64, true>(p, w, s);
+  return p->head_dim == 128 ? launch_bwd<128, false>(p, w, s) : launch_bwd<64, false>(p, w, s);
 }
 
 int fmha_bwd_static_scratch(const FmhaBwdParams* p, void* stream) {
@@ -366,8 +389,9 @@ int fmha_bwd_static_scratch(const FmhaBwdParams* p, void* stream) {
 
 int fmha_bwd_convert_dq(const void* workspace, void* dq, FmhaStrides dq_strides, int32_t batch,
                         int32_t heads, int32_t seqlen_q, int32_t head_dim, float scale,
-                        void* stream) {
+                        int32_t dtype, void* stream) {
   if (workspace == nullptr || dq == nullptr) return FMHA_ERR_NULL_POINTER;
+  if (dtype != FMHA_DTYPE_FP16 && dtype != FMHA_DTYPE_BF16) return FMHA_ERR_BAD_DTYPE;
   if (head_dim != 64 && head_dim != 128) return FMHA_ERR_BAD_HEAD_DIM;
   if (batch <= 0 || heads <= 0 || seqlen_q <= 0) return FMHA_ERR_BAD_SHAPE;
   if (!aligned16(workspace) || !aligned16(dq)) return FMHA_ERR_BAD_ALIGNMENT;
@@ -378,20 +402,30 @@ int fmha_bwd_convert_dq(const void* workspace, void* dq, FmhaStrides dq_strides,
   const unsigned grid = (unsigned)((rows + rows_per_block - 1) / rows_per_block);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const float* acc = static_cast<const float*>(workspace);
-  if (head_dim == 128)
-    fmha::fmha_bwd_convert_dq_kernel<128><<<grid, 256, 0, s>>>(acc, static_cast<__half*>(dq),
-                                                               to3(dq_strides), heads, seqlen_q, scale, rows);
-  else
-    fmha::fmha_bwd_convert_dq_kernel<64><<<grid, 256, 0, s>>>(acc, static_cast<__half*>(dq),
-                                                              to3(dq_strides), heads, seqlen_q, scale, rows);
+  const fmha::Strides3 sd = to3(dq_strides);
+  if (dtype == FMHA_DTYPE_BF16) {
+    auto* out = static_cast<__nv_bfloat16*>(dq);
+    if (head_dim == 128)
+      fmha::fmha_bwd_convert_dq_kernel<128, __nv_bfloat16><<<grid, 256, 0, s>>>(acc, out, sd, heads, seqlen_q, scale, rows);
+    else
+      fmha::fmha_bwd_convert_dq_kernel<64, __nv_bfloat16><<<grid, 256, 0, s>>>(acc, out, sd, heads, seqlen_q, scale, rows);
+  } else {
+    auto* out = static_cast<__half*>(dq);
+    if (head_dim == 128)
+      fmha::fmha_bwd_convert_dq_kernel<128, __half><<<grid, 256, 0, s>>>(acc, out, sd, heads, seqlen_q, scale, rows);
+    else
+      fmha::fmha_bwd_convert_dq_kernel<64, __half><<<grid, 256, 0, s>>>(acc, out, sd, heads, seqlen_q, scale, rows);
+  }
   return cudaGetLastError() == cudaSuccess ? FMHA_OK : FMHA_ERR_LAUNCH;
 }
 
 int fmha_merge_rows(float* o_acc, float* lse_acc, const void* o_part, FmhaStrides o_part_strides,
                     const float* lse_part, void* o_out, int32_t batch, int32_t heads, int32_t rows,
-                    int32_t acc_rows, int32_t row_offset, int32_t head_dim, void* stream) {
+                    int32_t acc_rows, int32_t row_offset, int32_t head_dim, int32_t dtype,
+                    void* stream) {
   if (o_acc == nullptr || lse_acc == nullptr || o_part == nullptr || lse_part == nullptr)
     return FMHA_ERR_NULL_POINTER;
+  if (dtype != FMHA_DTYPE_FP16 && dtype != FMHA_DTYPE_BF16) return FMHA_ERR_BAD_DTYPE;
   if (head_dim != 64 && head_dim != 128) return FMHA_ERR_BAD_HEAD_DIM;
   if (batch <= 0 || heads <= 0 || rows <= 0 || row_offset < 0 ||
       (long long)row_offset + rows > (long long)acc_rows)
@@ -403,22 +437,34 @@ int fmha_merge_rows(float* o_acc, float* lse_acc, const void* o_part, FmhaStride
   const int rows_per_block = 256 / (head_dim / 8);
   const unsigned grid = (unsigned)((total + rows_per_block - 1) / rows_per_block);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  if (head_dim == 128)
-    fmha::fmha_merge_kernel<128><<<grid, 256, 0, s>>>(
-        o_acc, lse_acc, static_cast<const __half*>(o_part), to3(o_part_strides), lse_part,
-        static_cast<__half*>(o_out), heads, rows, acc_rows, row_offset, total);
-  else
-    fmha::fmha_merge_kernel<64><<<grid, 256, 0, s>>>(
-        o_acc, lse_acc, static_cast<const __half*>(o_part), to3(o_part_strides), lse_part,
-        static_cast<__half*>(o_out), heads, rows, acc_rows, row_offset, total);
+  const fmha::Strides3 sp = to3(o_part_strides);
+  if (dtype == FMHA_DTYPE_BF16) {
+    auto* part = static_cast<const __nv_bfloat16*>(o_part);
+    auto* out = static_cast<__nv_bfloat16*>(o_out);
+    if (head_dim == 128)
+      fmha::fmha_merge_kernel<128, __nv_bfloat16><<<grid, 256, 0, s>>>(
+          o_acc, lse_acc, part, sp, lse_part, out, heads, rows, acc_rows, row_offset, total);
+    else
+      fmha::fmha_merge_kernel<64, __nv_bfloat16><<<grid, 256, 0, s>>>(
+          o_acc, lse_acc, part, sp, lse_part, out, heads, rows, acc_rows, row_offset, total);
+  } else {
+    auto* part = static_cast<const __half*>(o_part);
+    auto* out = static_cast<__half*>(o_out);
+    if (head_dim == 128)
+      fmha::fmha_merge_kernel<128, __half><<<grid, 256, 0, s>>>(
+          o_acc, lse_acc, part, sp, lse_part, out, heads, rows, acc_rows, row_offset, total);
+    else
+      fmha::fmha_merge_kernel<64, __half><<<grid, 256, 0, s>>>(
+          o_acc, lse_acc, part, sp, lse_part, out, heads, rows, acc_rows, row_offset, total);
+  }
   return cudaGetLastError() == cudaSuccess ? FMHA_OK : FMHA_ERR_LAUNCH;
 }
 
 int fmha_merge(float* o_acc, float* lse_acc, const void* o_part, FmhaStrides o_part_strides,
                const float* lse_part, void* o_out, int32_t batch, int32_t heads, int32_t rows,
-               int32_t head_dim, void* stream) {
+               int32_t head_dim, int32_t dtype, void* stream) {
   return fmha_merge_rows(o_acc, lse_acc, o_part, o_part_strides, lse_part, o_out, batch, heads,
-                         rows, rows, 0, head_dim, stream);
+                         rows, rows, 0, head_dim, dtype, stream);
 }
 
 int fmha_b200_forward(const void* query_ptr, const void* key_ptr, const void* value_ptr,
@@ -484,11 +530,12 @@ const char* fmha_status_string(int status) {
     case FMHA_ERR_NO_DEVICE: return "CUDA driver entry point unavailable";
     case FMHA_ERR_LAUNCH: return "kernel launch failed";
     case FMHA_ERR_TOO_LARGE: return "a size exceeds the supported maximum";
+    case FMHA_ERR_BAD_DTYPE: return "dtype must be FMHA_DTYPE_FP16 or FMHA_DTYPE_BF16";
     default: return "unknown status";
   }
 }
 
-const char* fmha_version(void) { return "0.1.0"; }
+const char* fmha_version(void) { return "0.2.0"; }
 
 #ifdef FMHA_TIMELINE
 // debug builds only: device buffer (>= 3 * 512 int64) and the CTA whose events are recorded

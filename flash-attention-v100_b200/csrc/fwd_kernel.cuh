@@ -31,6 +31,10 @@
 // item (its Q / K loads and first S = Q K^T), so that the load latency at the head of an item
 // and the store at its tail are hidden.
 //
+// Element type: fp16 (the reference's only type, kernel/fused_mha_api.cpp:25-29) or bf16
+// (kBf16): the tensor cores take either by two bits of the instruction descriptor; P and O are
+// then rounded to bf16 instead of fp16, everything in between stays fp32.
+//
 // Tensor memory (512 columns): S_t buffer b at [t * 128 + b * 64, + 64); O_0 [256, 256 + D),
 // O_1 [256 + D, 256 + 2 D); P_t(h) aliases the first 32 columns of the S_t buffer it came from
 // (two fp16 per 32-bit column).
@@ -77,7 +81,7 @@ struct FwdKernelParams {
 #define FMHA_FWD_POLY_PAIRS_D64 0
 #endif
 
-template <int D>
+template <int D, bool kBf16 = false>
 struct FwdTraits {
   static constexpr int kBlockM = 128;  // rows per query tile
   static constexpr int kTilesM = 2;    // query tiles per work item
@@ -99,8 +103,8 @@ struct FwdTraits {
   static constexpr int kSmemBytes = 1024 + (kTilesM + 2) * kTileBytes + kStages * kSlotBytes;
   static constexpr int kTmemCols = 512;
   static constexpr int kPolyPairs = (D == 64) ? FMHA_FWD_POLY_PAIRS_D64 : FMHA_FWD_POLY_PAIRS;
-  static constexpr uint32_t kIdescQK = umma_idesc_f16(128, kStepN, 0, 0);
-  static constexpr uint32_t kIdescPV = umma_idesc_f16(128, D, 0, 1);
+  static constexpr uint32_t kIdescQK = umma_idesc_f16(128, kStepN, 0, 0, kBf16);
+  static constexpr uint32_t kIdescPV = umma_idesc_f16(128, D, 0, 1, kBf16);
 };
 
 constexpr int kFwdRegsIssue = 88;                                 // warps 8-11
@@ -161,12 +165,12 @@ __device__ __forceinline__ void fwd_item_extent(const FwdKernelParams& p, int q0
   }
 }
 
-template <int D>
+template <int D, bool kBf16 = false>
 __global__ void __launch_bounds__(384, 1)
     fmha_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                     const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_o,
                     const FwdKernelParams p) {
-  using T = FwdTraits<D>;
+  using T = FwdTraits<D, kBf16>;
   extern __shared__ uint8_t smem_raw[];
   __shared__ uint64_t bar_q_full[2];   // Q_t of the current item has landed
   __shared__ uint64_t bar_q_free[2];   // the last S_t = Q_t K^T of the item is done: Q_t reusable
@@ -599,7 +603,7 @@ __global__ void __launch_bounds__(384, 1)
             if (i & 2) lb = add2(lb, p2); else la = add2(la, p2);
             uint32_t p0, p1;
             unpack2(p2, p0, p1);
-            pk[cc * 16 + (i >> 1)] = pack_half2(__uint_as_float(p0), __uint_as_float(p1));
+            pk[cc * 16 + (i >> 1)] = pack16x2<kBf16>(__uint_as_float(p0), __uint_as_float(p1));
           }
         }
         if (!(FMHA_ABLATE & 4)) tmem_st32(tSb, pk);
@@ -639,8 +643,8 @@ __global__ void __launch_bounds__(384, 1)
           for (int cc = 0; cc < D / 32; ++cc)
 #pragma unroll
             for (int i = 0; i < 32; i += 2)
-              oh[cc * 16 + (i >> 1)] = pack_half2(__uint_as_float(o[cc][i]) * inv_l,
-                                                  __uint_as_float(o[cc][i + 1]) * inv_l);
+              oh[cc * 16 + (i >> 1)] = pack16x2<kBf16>(__uint_as_float(o[cc][i]) * inv_l,
+                                                       __uint_as_float(o[cc][i + 1]) * inv_l);
         } else {
 #pragma unroll
           for (int i = 0; i < D / 2; ++i) oh[i] = 0u;

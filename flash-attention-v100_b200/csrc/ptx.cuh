@@ -56,6 +56,11 @@ __device__ __forceinline__ void fence_barrier_init() {
 __device__ __forceinline__ void fence_proxy_async_smem() {
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
 }
+// orders accesses of the generic proxy (ordinary loads / stores, flags) with those of the async
+// proxy (TMA copies and reductions), all state spaces
+__device__ __forceinline__ void fence_proxy_async_all() {
+  asm volatile("fence.proxy.async;" ::: "memory");
+}
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
@@ -91,6 +96,28 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
   }
   atomicCAS(const_cast<int*>(abort_word), 0, kErrWaitTimeout | (who & 0xff));
   return false;
+}
+
+// Bounded wait for a word in global memory to reach `want`; another CTA of the same grid with a
+// LOWER block index sets it (blocks are dispatched in index order, so that CTA is running or
+// done).  Gives up at once when this CTA, or the grid (status word), is already aborting.
+constexpr uint32_t kFlagPollLimit = 1u << 21;
+__device__ __forceinline__ bool global_flag_wait(const int* flag, int want, volatile int* abort_word,
+                                                 const int* status, int who) {
+  for (uint32_t i = 0; i < kFlagPollLimit; ++i) {
+    int v;
+    asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
+    if (v >= want) return true;
+    if (*abort_word != 0) return false;
+    if (status != nullptr && (i & 31u) == 31u && *reinterpret_cast<const volatile int*>(status) != 0)
+      break;
+    __nanosleep(64);
+  }
+  atomicCAS(const_cast<int*>(abort_word), 0, kErrWaitTimeout | (who & 0xff));
+  return false;
+}
+__device__ __forceinline__ void global_flag_release(int* flag, int value) {
+  asm volatile("st.release.gpu.global.s32 [%0], %1;" ::"l"(flag), "r"(value) : "memory");
 }
 
 // ---------------------------------------------------------------------------------
@@ -220,13 +247,13 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32
 
 
 // ---------------------------------------------------------------------------------
-// UMMA descriptors (fp16 operands, fp32 accumulate, dense, cta_group::1, M = 128)
+// UMMA descriptors (16-bit operands, fp32 accumulate, dense, cta_group::1, M = 128)
 // ---------------------------------------------------------------------------------
-// Instruction descriptor bits: [4,6) D format (1 = f32); [7,10) A format (0 = f16);
+// Instruction descriptor bits: [4,6) D format (1 = f32); [7,10) A format (0 = f16, 1 = bf16);
 // [10,13) B format; 15 A major (0 = K, 1 = MN); 16 B major; [17,23) N >> 3; [24,29) M >> 4.
 __host__ __device__ constexpr uint32_t umma_idesc_f16(int m, int n, int a_mn_major,
-                                                      int b_mn_major) {
-  return (1u << 4) | (0u << 7) | (0u << 10) | (uint32_t(a_mn_major) << 15) |
+                                                      int b_mn_major, bool bf16 = false) {
+  return (1u << 4) | (uint32_t(bf16) << 7) | (uint32_t(bf16) << 10) | (uint32_t(a_mn_major) << 15) |
          (uint32_t(b_mn_major) << 16) | (uint32_t(n >> 3) << 17) | (uint32_t(m >> 4) << 24);
 }
 
@@ -463,5 +490,19 @@ __device__ __forceinline__ uint32_t pack_half2(float lo, float hi) {
   __half2 h = __floats2half2_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&h);
 }
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
+  uint32_t r;
+  asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+  return r;
+}
+// two fp32 values -> one 32-bit word of the kernel's 16-bit element type (low half = first)
+template <bool kBf16>
+__device__ __forceinline__ uint32_t pack16x2(float lo, float hi) {
+  if constexpr (kBf16) return pack_bf16x2(lo, hi);
+  else return pack_half2(lo, hi);
+}
+// the two bf16 values of a word as fp32 (a bf16 is the upper half of an fp32)
+__device__ __forceinline__ float bf16_lo(uint32_t w) { return __uint_as_float(w << 16); }
+__device__ __forceinline__ float bf16_hi(uint32_t w) { return __uint_as_float(w & 0xffff0000u); }
 
 }  // namespace fmha

@@ -7,7 +7,7 @@
 //
 // Differences from the reference extension, all widenings:
 //   - any sm_100 device instead of the sm_70 gate (kernel/fused_mha_api.cpp:21-23);
-//   - head_dim 64 or 128 (reference: 128 only, :44); sequence length a multiple of 32 is
+//   - bf16 beside fp16 (reference: fp16 only, :25-29); head_dim 64 or 128 (reference: 128 only, :44); sequence length a multiple of 32 is
 //     CHECKED (the reference only documents it, README.md:3);
 //   - q and k/v may differ in sequence length; row/head/batch strides are honoured;
 //   - `fwd` returns {out, softmax_max, softmax_sum} like the reference (:71), where
@@ -37,7 +37,8 @@ FmhaStrides strides_of(const at::Tensor& t) {
 
 void check_input(const at::Tensor& t, const char* name) {
   TORCH_CHECK(t.is_cuda(), name, " must be on CUDA");
-  TORCH_CHECK(t.scalar_type() == at::kHalf, "This repo only supports fp16 data type (", name, ")");
+  TORCH_CHECK(t.scalar_type() == at::kHalf || t.scalar_type() == at::kBFloat16,
+              "This repo only supports fp16 and bf16 data types (", name, ")");
   TORCH_CHECK(t.dim() == 4, name, " must have shape (batch, seqlen, heads, head_size)");
   TORCH_CHECK(t.stride(-1) == 1, name, " must have contiguous last dimension");
 }
@@ -54,6 +55,8 @@ void check_shapes(const at::Tensor& q, const at::Tensor& k, const at::Tensor& v)
   TORCH_CHECK(k.size(0) == B && k.size(2) == H && k.size(3) == D,
               "k must have shape (batch_size, seqlen_k, num_heads, head_size)");
   TORCH_CHECK(v.sizes() == k.sizes(), "v must have the shape of k");
+  TORCH_CHECK(k.scalar_type() == q.scalar_type() && v.scalar_type() == q.scalar_type(),
+              "q, k and v must have the same data type");
   TORCH_CHECK(Nq % 32 == 0 && Nk % 32 == 0,
               "sequence lengths must be multiples of 32 (pad the inputs), got ", Nq, " and ", Nk);
 }
@@ -71,7 +74,8 @@ std::vector<at::Tensor> fwd_impl(const at::Tensor& q, const at::Tensor& k, const
   if (out_.has_value()) {
     out = out_.value();
     check_input(out, "out");
-    TORCH_CHECK(out.sizes() == q.sizes(), "out must have the shape of q");
+    TORCH_CHECK(out.sizes() == q.sizes() && out.scalar_type() == q.scalar_type(),
+                "out must have the shape and type of q");
   } else {
     out = at::empty_like(q);
   }
@@ -97,6 +101,7 @@ std::vector<at::Tensor> fwd_impl(const at::Tensor& q, const at::Tensor& k, const
   p.scale = static_cast<float>(softmax_scale);
   p.causal = is_causal ? 1 : 0;
   p.causal_shift = 0;
+  p.dtype = q.scalar_type() == at::kBFloat16 ? FMHA_DTYPE_BF16 : FMHA_DTYPE_FP16;
   check_status(fmha_fwd(&p, at::cuda::getCurrentCUDAStream().stream()), "fmha_fwd");
   if (!want_sum) return {out, lse};
   return {out, lse, at::ones({B, H, Nq}, fopts)};
@@ -130,8 +135,10 @@ std::vector<at::Tensor> mha_bwd(const at::Tensor& dout, const at::Tensor& q, con
   check_input(out, "out");
   check_input(dout, "dout");
   check_shapes(q, k, v);
-  TORCH_CHECK(out.sizes() == q.sizes(), "out must have the shape of q");
-  TORCH_CHECK(dout.sizes() == q.sizes(), "dout must have the shape of q");
+  TORCH_CHECK(out.sizes() == q.sizes() && out.scalar_type() == q.scalar_type(),
+              "out must have the shape and type of q");
+  TORCH_CHECK(dout.sizes() == q.sizes() && dout.scalar_type() == q.scalar_type(),
+              "dout must have the shape and type of q");
   const int B = q.size(0), Nq = q.size(1), H = q.size(2), D = q.size(3), Nk = k.size(1);
   TORCH_CHECK(softmax_max.is_cuda() && softmax_max.scalar_type() == at::kFloat &&
                   softmax_max.sizes() == at::IntArrayRef({B, H, Nq}),
@@ -148,7 +155,8 @@ std::vector<at::Tensor> mha_bwd(const at::Tensor& dout, const at::Tensor& q, con
   auto take = [&](std::optional<at::Tensor>& t, const at::Tensor& like, const char* name) {
     if (t.has_value()) {
       check_input(t.value(), name);
-      TORCH_CHECK(t->sizes() == like.sizes(), name, " must have the shape of its input");
+      TORCH_CHECK(t->sizes() == like.sizes() && t->scalar_type() == like.scalar_type(), name,
+                  " must have the shape and type of its input");
       return t.value();
     }
     return at::empty_like(like);
@@ -182,6 +190,7 @@ std::vector<at::Tensor> mha_bwd(const at::Tensor& dout, const at::Tensor& q, con
   p.head_dim = D;
   p.scale = static_cast<float>(softmax_scale);
   p.causal = is_causal ? 1 : 0;
+  p.dtype = q.scalar_type() == at::kBFloat16 ? FMHA_DTYPE_BF16 : FMHA_DTYPE_FP16;
   const size_t ws_bytes = fmha_bwd_workspace_bytes(&p);
   at::Tensor ws = at::empty({static_cast<int64_t>(ws_bytes)}, q.options().dtype(at::kByte));
   check_status(fmha_bwd(&p, ws.data_ptr(), ws_bytes, at::cuda::getCurrentCUDAStream().stream()),

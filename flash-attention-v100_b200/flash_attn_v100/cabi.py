@@ -23,6 +23,9 @@ FMHA_OK = 0
 FMHA_BWD_KEEP_WORKSPACE = 1
 FMHA_BWD_SKIP_DQ_CONVERT = 2
 FMHA_BWD_PREPROCESS_ONLY = 4
+FMHA_BWD_DETERMINISTIC = 8
+FMHA_DTYPE_FP16 = 0
+FMHA_DTYPE_BF16 = 1
 
 EXPORTED_SYMBOLS = (
     "fmha_fwd", "fmha_bwd_workspace_bytes", "fmha_bwd", "fmha_bwd_static_scratch", "fmha_bwd_convert_dq", "fmha_merge", "fmha_merge_rows", "fmha_b200_forward",
@@ -43,7 +46,7 @@ class FmhaFwdParams(ctypes.Structure):
         ("batch", ctypes.c_int32), ("heads", ctypes.c_int32), ("seqlen_q", ctypes.c_int32),
         ("seqlen_k", ctypes.c_int32), ("head_dim", ctypes.c_int32),
         ("scale", ctypes.c_float), ("causal", ctypes.c_int32), ("causal_shift", ctypes.c_int32),
-        ("status", ctypes.c_void_p), ("sm_margin", ctypes.c_int32),
+        ("status", ctypes.c_void_p), ("sm_margin", ctypes.c_int32), ("dtype", ctypes.c_int32),
     ]
 
 
@@ -60,7 +63,7 @@ class FmhaBwdParams(ctypes.Structure):
         ("batch", ctypes.c_int32), ("heads", ctypes.c_int32), ("seqlen_q", ctypes.c_int32),
         ("seqlen_k", ctypes.c_int32), ("head_dim", ctypes.c_int32),
         ("scale", ctypes.c_float), ("causal", ctypes.c_int32), ("causal_shift", ctypes.c_int32),
-        ("flags", ctypes.c_int32), ("status", ctypes.c_void_p),
+        ("flags", ctypes.c_int32), ("status", ctypes.c_void_p), ("dtype", ctypes.c_int32),
     ]
 
 
@@ -89,14 +92,14 @@ def load_library() -> ctypes.CDLL:
     lib.fmha_bwd_convert_dq.restype = ctypes.c_int
     lib.fmha_bwd_convert_dq.argtypes = [ctypes.c_void_p, ctypes.c_void_p, FmhaStrides, ctypes.c_int32,
                                         ctypes.c_int32, ctypes.c_int32, ctypes.c_int32, ctypes.c_float,
-                                        ctypes.c_void_p]
+                                        ctypes.c_int32, ctypes.c_void_p]
     lib.fmha_merge.restype = ctypes.c_int
     lib.fmha_merge.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, FmhaStrides,
                                ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int32, ctypes.c_int32,
-                               ctypes.c_int32, ctypes.c_int32, ctypes.c_void_p]
+                               ctypes.c_int32, ctypes.c_int32, ctypes.c_int32, ctypes.c_void_p]
     lib.fmha_merge_rows.restype = ctypes.c_int
     lib.fmha_merge_rows.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, FmhaStrides,
-                                    ctypes.c_void_p, ctypes.c_void_p] + [ctypes.c_int32] * 6 + [
+                                    ctypes.c_void_p, ctypes.c_void_p] + [ctypes.c_int32] * 7 + [
                                         ctypes.c_void_p]
     lib.fmha_b200_forward.restype = ctypes.c_int
     lib.fmha_b200_forward.argtypes = [ctypes.c_void_p] * 5 + [ctypes.c_int] * 5 + [
@@ -135,13 +138,21 @@ def _stream(stream) -> ctypes.c_void_p:
     return ctypes.c_void_p(stream.cuda_stream)
 
 
+def _dtype_code(t: torch.Tensor) -> int:
+    return FMHA_DTYPE_BF16 if t.dtype == torch.bfloat16 else FMHA_DTYPE_FP16
+
+
 def _require_cuda_half(*tensors):
+    """fp16 or bf16 (all the same) CUDA tensors of rank 4 with a contiguous last dimension."""
+    first = None
     for t in tensors:
         if t is None:
             continue
-        if not t.is_cuda or t.dtype != torch.float16 or t.dim() != 4 or t.stride(-1) != 1:
-            raise RuntimeError("expected fp16 CUDA tensors (batch, seqlen, heads, head_dim) with a "
-                               "contiguous last dimension")
+        first = t if first is None else first
+        if not t.is_cuda or t.dtype not in (torch.float16, torch.bfloat16) or t.dtype != first.dtype \
+                or t.dim() != 4 or t.stride(-1) != 1:
+            raise RuntimeError("expected fp16 or bf16 CUDA tensors of one type (batch, seqlen, heads, "
+                               "head_dim) with a contiguous last dimension")
 
 
 def fwd_params(q, k, v, o, lse, scale, causal, causal_shift=0, status=None, sm_margin=0) -> FmhaFwdParams:
@@ -155,6 +166,7 @@ def fwd_params(q, k, v, o, lse, scale, causal, causal_shift=0, status=None, sm_m
     p.causal_shift = int(causal_shift)
     p.status = None if status is None else status.data_ptr()
     p.sm_margin = int(sm_margin)
+    p.dtype = _dtype_code(q)
     return p
 
 
@@ -209,6 +221,7 @@ def bwd_params(q, k, v, o, dout, lse, dq, dk, dv, scale, causal, causal_shift=0,
     p.causal_shift = int(causal_shift)
     p.flags = int(flags)
     p.status = None if status is None else status.data_ptr()
+    p.dtype = _dtype_code(q)
     return p
 
 
@@ -257,17 +270,17 @@ def bwd_static_scratch(q, k, v, o, dout, lse, dq, dk, dv, scale: float, causal: 
 
 
 def bwd_convert_dq(workspace, dq, scale: float, stream=None):
-    """dq (fp16, strided) = scale * the fp32 dQ accumulator at the start of ``workspace``."""
+    """dq (fp16 or bf16, strided) = scale * the fp32 dQ accumulator at the start of ``workspace``."""
     Z, N, H, D = dq.shape
     with torch.cuda.device(dq.device):
         _check(load_library().fmha_bwd_convert_dq(ctypes.c_void_p(workspace.data_ptr()), _ptr(dq),
                                                   _strides(dq), Z, H, N, D, float(scale),
-                                                  _stream(stream)), "fmha_bwd_convert_dq")
+                                                  _dtype_code(dq), _stream(stream)), "fmha_bwd_convert_dq")
     return dq
 
 
 def merge(o_acc, lse_acc, o_part, lse_part, o_out=None, stream=None, row_offset: int = 0):
-    """In-place LSE merge of (o_part fp16, lse_part) into (o_acc fp32 contiguous, lse_acc).  The
+    """In-place LSE merge of (o_part fp16 / bf16, lse_part) into (o_acc fp32 contiguous, lse_acc).  The
     partial result covers rows [row_offset, row_offset + o_part.shape[1]) of the accumulators."""
     Z, N, H, D = o_part.shape
     acc_rows = o_acc.shape[1]
@@ -278,6 +291,7 @@ def merge(o_acc, lse_acc, o_part, lse_part, o_out=None, stream=None, row_offset:
     with torch.cuda.device(o_part.device):
         _check(load_library().fmha_merge_rows(_ptr(o_acc), _ptr(lse_acc), _ptr(o_part),
                                               _strides(o_part), _ptr(lse_part), _ptr(o_out), Z, H, N,
-                                              acc_rows, int(row_offset), D, _stream(stream)),
+                                              acc_rows, int(row_offset), D, _dtype_code(o_part),
+                                              _stream(stream)),
                "fmha_merge_rows")
     return o_acc, lse_acc

@@ -9,7 +9,10 @@
  * `void`, and never abort the process.
  *
  * Conventions
- *  - All tensors are fp16 unless stated; logical layout (Z, N, H, D) = (batch, sequence,
+ *  - All tensors are 16-bit floating point unless stated: fp16, the reference's only type
+ *    (kernel/fused_mha_api.cpp:25-29), or bf16, chosen by the `dtype` field / argument
+ *    (FMHA_DTYPE_*; 0 = fp16, so zero-initialised parameters mean what they always meant).
+ *    Every tensor of a call has the same type.  Logical layout (Z, N, H, D) = (batch, sequence,
  *    heads, head_dim) as in the reference (kernel/fused_mha_api.cpp:37-47).  Strides are in
  *    ELEMENTS and the head_dim stride must be 1.  Row/head/batch strides must be multiples
  *    of 8 elements and base pointers 16-byte aligned (TMA requirement).
@@ -55,8 +58,13 @@ enum {
   FMHA_ERR_TENSOR_MAP = 7,     /* cuTensorMapEncodeTiled failed */
   FMHA_ERR_NO_DEVICE = 8,      /* no sm_100 device / driver entry point unavailable */
   FMHA_ERR_LAUNCH = 9,         /* cudaLaunchKernel failed (see cudaGetLastError) */
-  FMHA_ERR_TOO_LARGE = 10      /* a size exceeds a stated limit */
+  FMHA_ERR_TOO_LARGE = 10,     /* a size exceeds a stated limit */
+  FMHA_ERR_BAD_DTYPE = 11      /* dtype is not one of FMHA_DTYPE_* */
 };
+
+/* element type of q, k, v, o, dout, dq, dk, dv (accumulation is fp32 either way) */
+#define FMHA_DTYPE_FP16 0
+#define FMHA_DTYPE_BF16 1
 
 /* element strides of one (Z, N, H, D) tensor; the D stride is 1 */
 typedef struct {
@@ -82,6 +90,7 @@ typedef struct {
    * attention posts the next K/V exchange before it launches the step) gives those kernels room
    * to run beside it instead of after it. */
   int32_t sm_margin;
+  int32_t dtype; /* FMHA_DTYPE_FP16 (0) or FMHA_DTYPE_BF16 */
 } FmhaFwdParams;
 
 typedef struct {
@@ -112,9 +121,10 @@ typedef struct {
   /* ring attention: 0 = normal (compute D, zero the fp32 dQ accumulator, convert dQ to fp16);
    * bit 0 set = do not zero the dQ accumulator nor recompute D (workspace carries both over
    * from an earlier call); bit 1 set = do not convert dQ (a later call will); bit 2 set = run
-   * the preprocess step only. */
+   * the preprocess step only; bit 3 set = deterministic dQ (see FMHA_BWD_DETERMINISTIC). */
   int32_t flags;
   int32_t* status;
+  int32_t dtype; /* FMHA_DTYPE_FP16 (0) or FMHA_DTYPE_BF16 */
 } FmhaBwdParams;
 
 #define FMHA_BWD_KEEP_WORKSPACE 1
@@ -124,13 +134,22 @@ typedef struct {
  * before the first K/V block arrives, and for timing the three kernels of a backward pass one by
  * one.  Not combinable with FMHA_BWD_KEEP_WORKSPACE (FMHA_ERR_WORKSPACE). */
 #define FMHA_BWD_PREPROCESS_ONLY 4
+/* Deterministic dQ: the fp32 partial sums of dQ from different key/value tiles are added in the
+ * order of the tiles instead of the order in which they happen to finish, so dQ is bit-for-bit
+ * the same on every run (dK, dV, O and LSE always are).  The CTAs of a (batch, head) then run
+ * staggered, one query tile apart, which costs up to a factor of two in the fused kernel.  The
+ * reference's dQ is a 64-way fp16 atomicAdd (kernel/fused_mha_kernel.cu:543,693) and has no
+ * such mode.  The order words live in the workspace (fmha_bwd_workspace_bytes accounts for
+ * them) and are cleared by every call that carries the flag. */
+#define FMHA_BWD_DETERMINISTIC 8
 
 /* Forward: O = softmax(scale * Q K^T [+ causal mask]) V and LSE.
  * Replaces fused_mha_forward (include/fused_mha.h:1-2, kernel/fused_mha_kernel.cu:891-902). */
 int fmha_fwd(const FmhaFwdParams* p, void* stream);
 
 /* Bytes of device workspace the backward needs for these sizes: an fp32 dQ accumulator
- * (Z, seqlen_q, H, D) followed by fp32 D = rowsum(dO * O) (Z, H, seqlen_q).  The reference
+ * (Z, seqlen_q, H, D) followed by fp32 lse * log2(e) and D = rowsum(dO * O), each (Z, H, seqlen_q
+ * padded to 128), and one int32 per (batch, head, 128-row query tile) for FMHA_BWD_DETERMINISTIC.  The reference
  * has no counterpart: it accumulates dQ with fp16 atomics in place
  * (kernel/fused_mha_kernel.cu:543,693) and computes D in PyTorch
  * (flash_attn_v100/flash_attn_interface.py:43-44). */
@@ -187,17 +206,17 @@ int fmha_bwd_static_scratch(const FmhaBwdParams* p, void* stream);
  * (kernel/fused_mha_kernel.cu:543,693). */
 int fmha_bwd_convert_dq(const void* workspace, void* dq, FmhaStrides dq_strides, int32_t batch,
                         int32_t heads, int32_t seqlen_q, int32_t head_dim, float scale,
-                        void* stream);
+                        int32_t dtype, void* stream);
 
 /* Ring-attention merge of a partial result into running fp32 accumulators, in place:
  *   lse' = logaddexp(lse_acc, lse_part);  o_acc = e^(lse_acc-lse') o_acc + e^(lse_part-lse') o_part
- * o_acc fp32 (Z, N, H, D) contiguous, lse_acc fp32 (Z, H, N) contiguous; o_part fp16 with
- * strides, lse_part fp32 (Z, H, N).  rows = N.  When `o_out` is not NULL the merged result is
- * also written as fp16 (Z, N, H, D) contiguous (used on the last ring step).
+ * o_acc fp32 (Z, N, H, D) contiguous, lse_acc fp32 (Z, H, N) contiguous; o_part 16-bit (`dtype`)
+ * with strides, lse_part fp32 (Z, H, N).  rows = N.  When `o_out` is not NULL the merged result
+ * is also written in `dtype` as (Z, N, H, D) contiguous (used on the last ring step).
  * No counterpart in the reference (it has no multi-GPU path). */
 int fmha_merge(float* o_acc, float* lse_acc, const void* o_part, FmhaStrides o_part_strides,
                const float* lse_part, void* o_out, int32_t batch, int32_t heads, int32_t rows,
-               int32_t head_dim, void* stream);
+               int32_t head_dim, int32_t dtype, void* stream);
 
 /* The same merge for a partial result that covers only rows [row_offset, row_offset + rows) of
  * accumulators with acc_rows rows (zig-zag ring attention: some steps compute the second half of
@@ -206,9 +225,10 @@ int fmha_merge(float* o_acc, float* lse_acc, const void* o_part, FmhaStrides o_p
  * No counterpart in the reference. */
 int fmha_merge_rows(float* o_acc, float* lse_acc, const void* o_part, FmhaStrides o_part_strides,
                     const float* lse_part, void* o_out, int32_t batch, int32_t heads, int32_t rows,
-                    int32_t acc_rows, int32_t row_offset, int32_t head_dim, void* stream);
+                    int32_t acc_rows, int32_t row_offset, int32_t head_dim, int32_t dtype,
+                    void* stream);
 
-/* Reference-shaped launchers: same argument meaning as include/fused_mha.h:1-6, dense
+/* Reference-shaped launchers: same argument meaning as include/fused_mha.h:1-6, dense fp16
  * (batch, m|n, head, k) tensors, except that the `max`/`sum` pair becomes one `lse` buffer,
  * the backward's `d_ptr` (fp16 D) is dropped in favour of a caller workspace, and a status
  * is returned.  m = seqlen_q, n = seqlen_k, k = head_dim. */

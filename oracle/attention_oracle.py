@@ -52,16 +52,17 @@ def default_scale(head_dim: int) -> float:
     return head_dim ** (-0.5)
 
 
-def make_inputs(Z: int, N: int, H: int, D: int, seed: int = 0, n_k: Optional[int] = None):
+def make_inputs(Z: int, N: int, H: int, D: int, seed: int = 0, n_k: Optional[int] = None,
+                dtype=torch.float16):
     """Seeded N(0,1) fp16 q, k, v, dout of shape (Z, N, H, D), drawn on the CPU in fp32 from one
     generator in the order q, k, v, dout and then rounded to fp16 (the reference draws N(0,1)
-    fp16 tensors, test.py:5-10)."""
+    fp16 tensors, test.py:5-10).  ``dtype=torch.bfloat16`` rounds the same draws to bf16."""
     g = torch.Generator().manual_seed(seed)
     n_k = N if n_k is None else n_k
-    q = torch.randn((Z, N, H, D), generator=g, dtype=torch.float32).half()
-    k = torch.randn((Z, n_k, H, D), generator=g, dtype=torch.float32).half()
-    v = torch.randn((Z, n_k, H, D), generator=g, dtype=torch.float32).half()
-    dout = torch.randn((Z, N, H, D), generator=g, dtype=torch.float32).half()
+    q = torch.randn((Z, N, H, D), generator=g, dtype=torch.float32).to(dtype)
+    k = torch.randn((Z, n_k, H, D), generator=g, dtype=torch.float32).to(dtype)
+    v = torch.randn((Z, n_k, H, D), generator=g, dtype=torch.float32).to(dtype)
+    dout = torch.randn((Z, N, H, D), generator=g, dtype=torch.float32).to(dtype)
     return q, k, v, dout
 
 

@@ -36,8 +36,8 @@ def test_status_strings(built_library):
     from flash_attn_v100 import cabi
 
     assert cabi.status_string(0) == "ok"
-    texts = {cabi.status_string(i) for i in range(0, 11)}
-    assert len(texts) == 11 and "unknown status" not in texts
+    texts = {cabi.status_string(i) for i in range(0, 12)}
+    assert len(texts) == 12 and "unknown status" not in texts
     assert cabi.status_string(999) == "unknown status"
 
 
@@ -57,7 +57,7 @@ def _fwd_params(cabi, **kw):
 @pytest.mark.parametrize("change,status", [
     (dict(q=None), 1), (dict(lse=None), 1), (dict(head_dim=96), 2), (dict(head_dim=32), 2),
     (dict(batch=0), 3), (dict(seqlen_k=-5), 3), (dict(scale=0.0), 3), (dict(scale=float("nan")), 3),
-    (dict(q=0x1008), 5),
+    (dict(q=0x1008), 5), (dict(dtype=2), 11), (dict(dtype=-1), 11),
 ])
 def test_forward_rejects_bad_parameters(built_library, change, status):
     from flash_attn_v100 import cabi
@@ -81,9 +81,11 @@ def test_backward_workspace_size_and_validation(built_library):
     from flash_attn_v100 import cabi
 
     lib = cabi.load_library()
-    # fp32 dQ accumulator (Z, N, H, D) + 2 x fp32 (Z, H, N padded to 128)
-    assert cabi.bwd_workspace_bytes(2, 96, 3, 64) == 2 * 96 * 3 * 64 * 4 + 2 * 2 * 3 * 128 * 4
-    assert cabi.bwd_workspace_bytes(8, 2048, 32, 128) == 8 * 2048 * 32 * 128 * 4 + 2 * 8 * 32 * 2048 * 4
+    # fp32 dQ accumulator (Z, N, H, D) + 2 x fp32 (Z, H, N padded to 128) + one int32 per (Z, H,
+    # query tile), rounded up to 256 bytes
+    assert cabi.bwd_workspace_bytes(2, 96, 3, 64) == 2 * 96 * 3 * 64 * 4 + 2 * 2 * 3 * 128 * 4 + 256
+    assert cabi.bwd_workspace_bytes(8, 2048, 32, 128) == \
+        8 * 2048 * 32 * 128 * 4 + 2 * 8 * 32 * 2048 * 4 + 8 * 32 * 16 * 4
     p = cabi.FmhaBwdParams()
     assert lib.fmha_bwd(ctypes.byref(p), None, 0, None) == 1
     for name in ("q", "k", "v", "o", "dout", "lse", "dq", "dk", "dv"):

@@ -142,6 +142,54 @@ def test_forward_is_deterministic_and_backward_dkdv_bitwise():
     assert oracle.rel_l2(a[0].float(), b[0].float()) < 1e-3     # dQ: fp32 reductions, order varies
 
 
+@pytest.mark.parametrize("Z,N,H,D,causal,n_k,dtype", [
+    (2, 1024, 4, 128, True, None, torch.float16), (2, 640, 3, 64, False, None, torch.float16),
+    (1, 384, 2, 128, True, 896, torch.float16), (2, 512, 4, 128, True, None, torch.bfloat16),
+])
+def test_deterministic_dq_is_bitwise_reproducible(Z, N, H, D, causal, n_k, dtype):
+    """FMHA_BWD_DETERMINISTIC: the partial sums of dQ are added in the order of the KV tiles, so
+    three runs give the same bits (the default mode only promises the tolerance), and the result
+    is as close to the oracle as the default mode's."""
+    from flash_attn_v100 import cabi
+
+    qc, kc, vc, doc = oracle.make_inputs(Z, N, H, D, seed=41, n_k=n_k, dtype=dtype)
+    q, k, v, dout = qc.cuda(), kc.cuda(), vc.cuda(), doc.cuda()
+    shift = 0 if n_k is None else n_k - N
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    out, lse = cabi.fwd(q, k, v, 0.1, causal, shift)
+    runs = [cabi.bwd(q, k, v, out, dout, lse, 0.1, causal, shift, flags=cabi.FMHA_BWD_DETERMINISTIC,
+                     status=status) for _ in range(3)]
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0
+    for other in runs[1:]:
+        for a, b in zip(runs[0], other):
+            assert torch.equal(a, b)
+    ref = oracle.attention_fwd_bwd(qc, kc, vc, doc, 0.1, causal, shift)
+    bf16 = dtype == torch.bfloat16
+    helpers.check_against_oracle((out.cpu(), lse.cpu()) + tuple(t.cpu() for t in runs[0]), ref,
+                                 f"deterministic Z{Z} N{N} H{H} D{D} causal={causal}",
+                                 helpers.TOL_O_MAX_ABS_BF16 if bf16 else helpers.TOL_O_MAX_ABS)
+
+
+def test_deterministic_dq_full_size_run_twice():
+    """BASELINE config 3 at full size (4096 CTAs, 16 per head, far more than fit the GPU at once):
+    the ordered reduction neither stalls nor changes between two runs."""
+    from flash_attn_v100 import cabi
+
+    g = torch.Generator(device="cuda").manual_seed(5)
+    q, k, v, dout = (torch.randn((8, 2048, 32, 128), generator=g, device="cuda", dtype=torch.float32).half()
+                     for _ in range(4))
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    out, lse = cabi.fwd(q, k, v, 128 ** -0.5, True)
+    a = cabi.bwd(q, k, v, out, dout, lse, 128 ** -0.5, True, flags=cabi.FMHA_BWD_DETERMINISTIC, status=status)
+    b = cabi.bwd(q, k, v, out, dout, lse, 128 ** -0.5, True, flags=cabi.FMHA_BWD_DETERMINISTIC, status=status)
+    c = cabi.bwd(q, k, v, out, dout, lse, 128 ** -0.5, True)
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0
+    assert all(torch.equal(x, y) for x, y in zip(a, b))
+    assert oracle.rel_l2(a[0].float(), c[0].float()) < 1e-3
+
+
 def test_linearity_in_v_and_dout_full_size():
     """Size-independent property at BASELINE config 3's full size (Z=8, H=32, N=2048, D=128,
     causal), where the CPU oracle is too slow: O is linear in V and dV is linear in dO, so
