@@ -64,7 +64,8 @@ __global__ void __launch_bounds__(256)
                                const E* __restrict__ dout, Strides3 sdo,
                                const float* __restrict__ lse, float* __restrict__ dq_accum,
                                float* __restrict__ lse2, float* __restrict__ delta, int heads,
-                               int seqlen_q, int seqlen_q_pad, long long total_rows) {
+                               int seqlen_q, int seqlen_q_pad, long long total_rows,
+                               const int* __restrict__ seqused_q) {
   constexpr int kGroup = D / 8;  // threads per row
   constexpr int kRowsPerBlock = 256 / kGroup;
   const int part = threadIdx.x % kGroup;
@@ -81,6 +82,9 @@ __global__ void __launch_bounds__(256)
     }
     return;
   }
+  // a padding row of a right-padded batch: P = exp2(s - inf) = 0 for it, it adds nothing to any
+  // gradient, and its own dQ stays zero
+  const bool padding = seqused_q != nullptr && q >= __ldg(seqused_q + z);
   const uint4 uo = *reinterpret_cast<const uint4*>(o + z * so.batch + q * so.row + h * so.head + part * 8);
   const uint4 ud =
       *reinterpret_cast<const uint4*>(dout + z * sdo.batch + q * sdo.row + h * sdo.head + part * 8);
@@ -93,8 +97,8 @@ __global__ void __launch_bounds__(256)
 #pragma unroll
   for (int off = kGroup / 2; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
   if (part == 0) {
-    delta[row_id] = acc;
-    lse2[row_id] = lse[zh * seqlen_q + q] * 1.4426950408889634f;
+    delta[row_id] = padding ? 0.f : acc;
+    lse2[row_id] = padding ? CUDART_INF_F : lse[zh * seqlen_q + q] * 1.4426950408889634f;
   }
   if (dq_accum != nullptr) {
     float4* dst = reinterpret_cast<float4*>(

@@ -55,6 +55,9 @@ struct BwdKernelParams {
   // additions then happen in one fixed order and dQ is the same bits on every run; the price
   // is that the CTAs of a head run staggered by one query tile each.
   int* dq_order;
+  // optional per-batch lengths (right-padded batches), see FmhaBwdParams
+  const int* seqused_q;
+  const int* seqused_k;
   long long* timeline;  // debug builds (-DFMHA_TIMELINE) only
   int timeline_block;
 };
@@ -130,14 +133,18 @@ __global__ void __launch_bounds__(512, 1)
   const int h = zh % p.heads;
   const int kv0 = kb * T::kBlock;
 
-  const int nq_tiles = (p.seqlen_q + T::kBlock - 1) / T::kBlock;
+  // the lengths that count for this batch entry: query tiles and keys beyond them are padding
+  const int sq = p.seqused_q == nullptr ? p.seqlen_q : max(0, min(p.seqlen_q, __ldg(p.seqused_q + z)));
+  const int sk = p.seqused_k == nullptr ? p.seqlen_k : max(0, min(p.seqlen_k, __ldg(p.seqused_k + z)));
+  const int nq_tiles = (sq + T::kBlock - 1) / T::kBlock;
   int i_begin = 0;
   if (p.causal) {
     // query row r sees key kv0 iff r + shift >= kv0
     const long long first_row = (long long)kv0 - p.causal_shift;
     i_begin = first_row <= 0 ? 0 : (int)min((long long)nq_tiles, first_row / T::kBlock);
   }
-  const int cnt = nq_tiles - i_begin;  // query tiles this CTA walks (may be 0)
+  // query tiles this CTA walks (may be 0; a KV tile that is all padding walks none)
+  const int cnt = kv0 < sk ? nq_tiles - i_begin : 0;
 
   if (threadIdx.x == 0) {
     mbar_init(smem_u32(&bar_kv_full), 1);
@@ -339,7 +346,7 @@ __global__ void __launch_bounds__(512, 1)
 
         // first visible query column of this thread's half (>= 64: none)
         int first_visible = 0;
-        if (kvi >= p.seqlen_k) {
+        if (kvi >= sk) {
           first_visible = T::kBlock;
         } else if (p.causal) {
           const long long fv = (long long)kvi - p.causal_shift - qbase;
@@ -484,7 +491,7 @@ __global__ void __launch_bounds__(512, 1)
           if (r == 0) {
             int* order_word = p.dq_order == nullptr
                                   ? nullptr
-                                  : p.dq_order + (size_t)zh * nq_tiles + (i_begin + n);
+                                  : p.dq_order + (size_t)zh * (p.seqlen_q_pad / T::kBlock) + (i_begin + n);
             if (order_word != nullptr && cc == 0) {
               // the KV tiles before this one have added their share of this query tile
               global_flag_wait(order_word, kb, &abort_word, p.status, 17);
@@ -519,7 +526,7 @@ __global__ void __launch_bounds__(512, 1)
       const int kvi = kv0 + r;
       if (accum != nullptr) {
         // ring attention: add this block's contribution into the travelling fp32 buffer
-        if (cnt > 0 && kvi < p.seqlen_k) {
+        if (cnt > 0 && kvi < sk) {
           float* dst = accum + (size_t)z * p.accum_batch_stride + ((size_t)kvi * p.heads + h) * D;
 #pragma unroll
           for (int cc = 0; cc < D / 32; ++cc) {

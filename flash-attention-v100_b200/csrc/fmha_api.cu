@@ -163,6 +163,8 @@ int launch_fwd(const FmhaFwdParams* p, cudaStream_t stream) {
   kp.causal = p->causal ? 1 : 0;
   kp.causal_shift = p->causal_shift;
   kp.status = p->status;
+  kp.seqused_q = p->seqused_q;
+  kp.seqused_k = p->seqused_k;
   kp.timeline = g_timeline;
   kp.timeline_block = g_timeline_block;
   auto kernel = fmha::fmha_fwd_kernel<D, kBf16>;
@@ -190,7 +192,7 @@ int launch_bwd(const FmhaBwdParams* p, const BwdWorkspace& w, cudaStream_t strea
     const unsigned grid = (unsigned)((rows + rows_per_block - 1) / rows_per_block);
     fmha::fmha_bwd_preprocess_kernel<D, E><<<grid, 256, 0, stream>>>(
         static_cast<const E*>(p->o), to3(p->o_strides), static_cast<const E*>(p->dout),
-        to3(p->dout_strides), p->lse, w.dq_accum, w.lse2, w.delta, H, Nq, Nq_pad, rows);
+        to3(p->dout_strides), p->lse, w.dq_accum, w.lse2, w.delta, H, Nq, Nq_pad, rows, p->seqused_q);
     if (cudaGetLastError() != cudaSuccess) return FMHA_ERR_LAUNCH;
   }
   if (p->flags & FMHA_BWD_PREPROCESS_ONLY) return FMHA_OK;
@@ -228,6 +230,8 @@ int launch_bwd(const FmhaBwdParams* p, const BwdWorkspace& w, cudaStream_t strea
     kp.causal = p->causal ? 1 : 0;
     kp.causal_shift = p->causal_shift;
     kp.status = p->status;
+    kp.seqused_q = p->seqused_q;
+    kp.seqused_k = p->seqused_k;
     kp.dq_order = nullptr;
     if (p->flags & FMHA_BWD_DETERMINISTIC) {
       // a memset node, not an allocation; every call starts its own count at zero

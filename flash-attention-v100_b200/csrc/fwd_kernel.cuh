@@ -63,6 +63,10 @@ struct FwdKernelParams {
   float scale_log2;     // scale * log2(e)
   int causal, causal_shift;
   int* status;
+  // optional per-batch lengths (right-padded batches): rows >= seqused_q[z] and keys >=
+  // seqused_k[z] are padding, skipped tile-wise and masked inside partial tiles
+  const int* seqused_q;
+  const int* seqused_k;
   // debug builds (-DFMHA_TIMELINE) only: clock64 stamps of one CTA, see FMHA_TL
   long long* timeline;
   int timeline_block;
@@ -145,20 +149,29 @@ struct FwdWorkIter {
   }
 };
 
+// the lengths that count for batch entry z: the tensors' own, or the caller's per-batch ones
+__device__ __forceinline__ void fwd_lengths(const FwdKernelParams& p, int z, int& sq, int& sk) {
+  sq = p.seqused_q == nullptr ? p.seqlen_q : max(0, min(p.seqlen_q, __ldg(p.seqused_q + z)));
+  sk = p.seqused_k == nullptr ? p.seqlen_k : max(0, min(p.seqlen_k, __ldg(p.seqused_k + z)));
+}
+
 // KV tiles each of the two query tiles of an item has to visit (0 = none)
 template <int D>
-__device__ __forceinline__ void fwd_item_extent(const FwdKernelParams& p, int q0, int (&n_kv)[2]) {
+__device__ __forceinline__ void fwd_item_extent(const FwdKernelParams& p, int z, int q0,
+                                                int (&n_kv)[2]) {
   using T = FwdTraits<D>;
-  const int nk_total = (p.seqlen_k + T::kBlockN - 1) / T::kBlockN;
+  int sq, sk;
+  fwd_lengths(p, z, sq, sk);
+  const int nk_total = (sk + T::kBlockN - 1) / T::kBlockN;
 #pragma unroll
   for (int t = 0; t < 2; ++t) {
     const int r0 = q0 + t * T::kBlockM;
-    if (r0 >= p.seqlen_q) {
+    if (r0 >= sq) {
       n_kv[t] = 0;
     } else if (!p.causal) {
       n_kv[t] = nk_total;
     } else {
-      const int r_last = min(r0 + T::kBlockM - 1, p.seqlen_q - 1);
+      const int r_last = min(r0 + T::kBlockM - 1, sq - 1);
       const long long lim = (long long)r_last + p.causal_shift;
       n_kv[t] = lim < 0 ? 0 : (int)min((long long)nk_total, lim / T::kBlockN + 1);
     }
@@ -255,7 +268,7 @@ __global__ void __launch_bounds__(384, 1)
         const int z = zh / p.heads, h = zh % p.heads;
         const int q0 = qb * (T::kBlockM * T::kTilesM);
         int n_kv[2];
-        fwd_item_extent<D>(p, q0, n_kv);
+        fwd_item_extent<D>(p, z, q0, n_kv);
         // slot loads in the order the MMA warps consume them:
         //   [K(0) K(1)]  [V(0) K(2)]  [V(1) K(3)]  ...  [V(nh-3) K(nh-1)]  [V(nh-2)]  [V(nh-1)]
         const int nh = 2 * max(n_kv[0], n_kv[1]);
@@ -300,7 +313,7 @@ __global__ void __launch_bounds__(384, 1)
         const int z = zh / p.heads, h = zh % p.heads;
         const int q0 = qb * (T::kBlockM * T::kTilesM);
         int n_kv[2];
-        fwd_item_extent<D>(p, q0, n_kv);
+        fwd_item_extent<D>(p, z, q0, n_kv);
         if (max(n_kv[0], n_kv[1]) == 0) continue;
 #pragma unroll
         for (int t = 0; t < T::kTilesM; ++t) {
@@ -387,7 +400,7 @@ __global__ void __launch_bounds__(384, 1)
       while (ok && work.next(zh, qb)) {
         const int q0 = qb * (T::kBlockM * T::kTilesM);
         int n_kv[2];
-        fwd_item_extent<D>(p, q0, n_kv);
+        fwd_item_extent<D>(p, zh / p.heads, q0, n_kv);
         const int n_max = max(n_kv[0], n_kv[1]);
         if (n_max == 0) continue;
         const int nh = 2 * n_kv[t];  // steps of this tile
@@ -491,12 +504,15 @@ __global__ void __launch_bounds__(384, 1)
       const int z = zh / p.heads, h = zh % p.heads;
       const int q0 = qb * (T::kBlockM * T::kTilesM);
       int n_kv[2];
-      fwd_item_extent<D>(p, q0, n_kv);
+      fwd_item_extent<D>(p, z, q0, n_kv);
+      int sq, sk;
+      fwd_lengths(p, z, sq, sk);
       const int n = n_kv[t];
       const bool tile_valid = (q0 + t * T::kBlockM) < p.seqlen_q;
       const int row = q0 + t * T::kBlockM + row_in_tile;
-      long long lim_ll = p.causal ? (long long)row + p.causal_shift : (long long)p.seqlen_k - 1;
-      lim_ll = min(lim_ll, (long long)p.seqlen_k - 1);
+      long long lim_ll = p.causal ? (long long)row + p.causal_shift : (long long)sk - 1;
+      lim_ll = min(lim_ll, (long long)sk - 1);
+      if (row >= sq) lim_ll = -1;  // a padding row sees nothing: O = 0, LSE = -inf
       lim_ll = max(lim_ll, -1ll);
       const int row_limit = (int)lim_ll;  // last visible key of this row (-1 = none)
 

@@ -61,9 +61,20 @@ void check_shapes(const at::Tensor& q, const at::Tensor& k, const at::Tensor& v)
               "sequence lengths must be multiples of 32 (pad the inputs), got ", Nq, " and ", Nk);
 }
 
+// per-batch lengths of a right-padded batch -> device pointer (or NULL)
+const int32_t* seqused_ptr(const std::optional<at::Tensor>& t, const at::Tensor& q, const char* name) {
+  if (!t.has_value()) return nullptr;
+  TORCH_CHECK(t->is_cuda() && t->scalar_type() == at::kInt && t->dim() == 1 &&
+                  t->size(0) == q.size(0) && t->is_contiguous(),
+              name, " must be a contiguous int32 CUDA tensor with one entry per batch");
+  return t->data_ptr<int32_t>();
+}
+
 std::vector<at::Tensor> fwd_impl(const at::Tensor& q, const at::Tensor& k, const at::Tensor& v,
                                  std::optional<at::Tensor> out_, double softmax_scale,
-                                 bool is_causal, bool want_sum) {
+                                 bool is_causal, bool want_sum,
+                                 std::optional<at::Tensor> seqused_q = std::nullopt,
+                                 std::optional<at::Tensor> seqused_k = std::nullopt) {
   check_input(q, "q");
   check_input(k, "k");
   check_input(v, "v");
@@ -102,6 +113,8 @@ std::vector<at::Tensor> fwd_impl(const at::Tensor& q, const at::Tensor& k, const
   p.causal = is_causal ? 1 : 0;
   p.causal_shift = 0;
   p.dtype = q.scalar_type() == at::kBFloat16 ? FMHA_DTYPE_BF16 : FMHA_DTYPE_FP16;
+  p.seqused_q = seqused_ptr(seqused_q, q, "seqused_q");
+  p.seqused_k = seqused_ptr(seqused_k, q, "seqused_k");
   check_status(fmha_fwd(&p, at::cuda::getCurrentCUDAStream().stream()), "fmha_fwd");
   if (!want_sum) return {out, lse};
   return {out, lse, at::ones({B, H, Nq}, fopts)};
@@ -117,18 +130,18 @@ std::vector<at::Tensor> mha_fwd(const at::Tensor& q, const at::Tensor& k, const 
 // {out, lse} only: what this package's own autograd glue uses (no tensor of ones to fill)
 std::vector<at::Tensor> mha_fwd_lse(const at::Tensor& q, const at::Tensor& k, const at::Tensor& v,
                                     std::optional<at::Tensor> out_, double softmax_scale,
-                                    bool is_causal) {
-  return fwd_impl(q, k, v, out_, softmax_scale, is_causal, false);
+                                    bool is_causal, std::optional<at::Tensor> seqused_q,
+                                    std::optional<at::Tensor> seqused_k) {
+  return fwd_impl(q, k, v, out_, softmax_scale, is_causal, false, seqused_q, seqused_k);
 }
 
-std::vector<at::Tensor> mha_bwd(const at::Tensor& dout, const at::Tensor& q, const at::Tensor& k,
-                                const at::Tensor& v, const at::Tensor& out,
-                                std::optional<at::Tensor> D_unused,
-                                std::optional<at::Tensor> softmax_sum, const at::Tensor& softmax_max,
-                                std::optional<at::Tensor> dq_, std::optional<at::Tensor> dk_,
-                                std::optional<at::Tensor> dv_, double softmax_scale,
-                                bool is_causal) {
-  (void)D_unused;
+std::vector<at::Tensor> bwd_impl(const at::Tensor& dout, const at::Tensor& q, const at::Tensor& k,
+                                 const at::Tensor& v, const at::Tensor& out,
+                                 std::optional<at::Tensor> softmax_sum, const at::Tensor& softmax_max,
+                                 std::optional<at::Tensor> dq_, std::optional<at::Tensor> dk_,
+                                 std::optional<at::Tensor> dv_, double softmax_scale, bool is_causal,
+                                 std::optional<at::Tensor> seqused_q, std::optional<at::Tensor> seqused_k,
+                                 bool deterministic) {
   check_input(q, "q");
   check_input(k, "k");
   check_input(v, "v");
@@ -191,11 +204,37 @@ std::vector<at::Tensor> mha_bwd(const at::Tensor& dout, const at::Tensor& q, con
   p.scale = static_cast<float>(softmax_scale);
   p.causal = is_causal ? 1 : 0;
   p.dtype = q.scalar_type() == at::kBFloat16 ? FMHA_DTYPE_BF16 : FMHA_DTYPE_FP16;
+  p.seqused_q = seqused_ptr(seqused_q, q, "seqused_q");
+  p.seqused_k = seqused_ptr(seqused_k, q, "seqused_k");
+  p.flags = deterministic ? FMHA_BWD_DETERMINISTIC : 0;
   const size_t ws_bytes = fmha_bwd_workspace_bytes(&p);
   at::Tensor ws = at::empty({static_cast<int64_t>(ws_bytes)}, q.options().dtype(at::kByte));
   check_status(fmha_bwd(&p, ws.data_ptr(), ws_bytes, at::cuda::getCurrentCUDAStream().stream()),
                "fmha_bwd");
   return {dq, dk, dv};
+}
+
+// the reference's entry point (kernel/fused_mha_api.cpp:74-87); its fp16 D argument is ignored
+std::vector<at::Tensor> mha_bwd(const at::Tensor& dout, const at::Tensor& q, const at::Tensor& k,
+                                const at::Tensor& v, const at::Tensor& out,
+                                std::optional<at::Tensor> D_unused,
+                                std::optional<at::Tensor> softmax_sum, const at::Tensor& softmax_max,
+                                std::optional<at::Tensor> dq_, std::optional<at::Tensor> dk_,
+                                std::optional<at::Tensor> dv_, double softmax_scale,
+                                bool is_causal) {
+  (void)D_unused;
+  return bwd_impl(dout, q, k, v, out, softmax_sum, softmax_max, dq_, dk_, dv_, softmax_scale,
+                  is_causal, std::nullopt, std::nullopt, false);
+}
+
+// this package's own glue: lse instead of (max, sum), per-batch lengths, deterministic dQ
+std::vector<at::Tensor> mha_bwd_lse(const at::Tensor& dout, const at::Tensor& q, const at::Tensor& k,
+                                    const at::Tensor& v, const at::Tensor& out, const at::Tensor& lse,
+                                    double softmax_scale, bool is_causal,
+                                    std::optional<at::Tensor> seqused_q,
+                                    std::optional<at::Tensor> seqused_k, bool deterministic) {
+  return bwd_impl(dout, q, k, v, out, std::nullopt, lse, std::nullopt, std::nullopt, std::nullopt,
+                  softmax_scale, is_causal, seqused_q, seqused_k, deterministic);
 }
 
 }  // namespace
@@ -205,7 +244,11 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   // positional calls only, like the reference's pybind exports (kernel/fused_mha_api.cpp:166-167)
   m.def("fwd", &mha_fwd, "Forward pass: fwd(q, k, v, out|None, softmax_scale, is_causal)");
   m.def("fwd_lse", &mha_fwd_lse,
-        "Forward pass returning [out, lse]: fwd_lse(q, k, v, out|None, softmax_scale, is_causal)");
+        "Forward pass returning [out, lse]: fwd_lse(q, k, v, out|None, softmax_scale, is_causal, "
+        "seqused_q|None, seqused_k|None)");
+  m.def("bwd_lse", &mha_bwd_lse,
+        "Backward pass: bwd_lse(dout, q, k, v, out, lse, softmax_scale, is_causal, seqused_q|None, "
+        "seqused_k|None, deterministic)");
   m.def("bwd", &mha_bwd,
         "Backward pass: bwd(dout, q, k, v, out, D|None, softmax_sum|None, softmax_max, dq|None, "
         "dk|None, dv|None, softmax_scale, is_causal)");

@@ -47,6 +47,7 @@ class FmhaFwdParams(ctypes.Structure):
         ("seqlen_k", ctypes.c_int32), ("head_dim", ctypes.c_int32),
         ("scale", ctypes.c_float), ("causal", ctypes.c_int32), ("causal_shift", ctypes.c_int32),
         ("status", ctypes.c_void_p), ("sm_margin", ctypes.c_int32), ("dtype", ctypes.c_int32),
+        ("seqused_q", ctypes.c_void_p), ("seqused_k", ctypes.c_void_p),
     ]
 
 
@@ -64,6 +65,7 @@ class FmhaBwdParams(ctypes.Structure):
         ("seqlen_k", ctypes.c_int32), ("head_dim", ctypes.c_int32),
         ("scale", ctypes.c_float), ("causal", ctypes.c_int32), ("causal_shift", ctypes.c_int32),
         ("flags", ctypes.c_int32), ("status", ctypes.c_void_p), ("dtype", ctypes.c_int32),
+        ("seqused_q", ctypes.c_void_p), ("seqused_k", ctypes.c_void_p),
     ]
 
 
@@ -155,7 +157,16 @@ def _require_cuda_half(*tensors):
                                "head_dim) with a contiguous last dimension")
 
 
-def fwd_params(q, k, v, o, lse, scale, causal, causal_shift=0, status=None, sm_margin=0) -> FmhaFwdParams:
+def _seqused_ptr(t: Optional[torch.Tensor], batch: int):
+    if t is None:
+        return None
+    if not t.is_cuda or t.dtype != torch.int32 or t.dim() != 1 or t.numel() != batch or not t.is_contiguous():
+        raise RuntimeError("seqused_q / seqused_k must be contiguous int32 CUDA tensors with one entry per batch")
+    return t.data_ptr()
+
+
+def fwd_params(q, k, v, o, lse, scale, causal, causal_shift=0, status=None, sm_margin=0,
+               seqused_q=None, seqused_k=None) -> FmhaFwdParams:
     p = FmhaFwdParams()
     p.q, p.k, p.v, p.o, p.lse = q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), lse.data_ptr()
     p.q_strides, p.k_strides, p.v_strides, p.o_strides = _strides(q), _strides(k), _strides(v), _strides(o)
@@ -167,28 +178,32 @@ def fwd_params(q, k, v, o, lse, scale, causal, causal_shift=0, status=None, sm_m
     p.status = None if status is None else status.data_ptr()
     p.sm_margin = int(sm_margin)
     p.dtype = _dtype_code(q)
+    p.seqused_q = _seqused_ptr(seqused_q, q.shape[0])
+    p.seqused_k = _seqused_ptr(seqused_k, q.shape[0])
     return p
 
 
 def fwd(q, k, v, scale: float, causal: bool = False, causal_shift: int = 0,
         out: Optional[torch.Tensor] = None, lse: Optional[torch.Tensor] = None,
-        status: Optional[torch.Tensor] = None, stream=None, sm_margin: int = 0):
+        status: Optional[torch.Tensor] = None, stream=None, sm_margin: int = 0,
+        seqused_q: Optional[torch.Tensor] = None, seqused_k: Optional[torch.Tensor] = None):
     """O, LSE through ``fmha_fwd`` on the current (or given) stream; outputs allocated with torch
-    unless passed in.  ``sm_margin``: SMs the persistent kernel leaves to other streams' kernels."""
+    unless passed in.  ``sm_margin``: SMs the persistent kernel leaves to other streams' kernels.
+    ``seqused_q`` / ``seqused_k``: per-batch real lengths of right-padded batches (int32)."""
     _require_cuda_half(q, k, v, out)
     Z, Nq, H, D = q.shape
     if out is None:
         out = torch.empty_like(q)
     if lse is None:
         lse = torch.empty((Z, H, Nq), dtype=torch.float32, device=q.device)
-    p = fwd_params(q, k, v, out, lse, scale, causal, causal_shift, status, sm_margin)
+    p = fwd_params(q, k, v, out, lse, scale, causal, causal_shift, status, sm_margin, seqused_q, seqused_k)
     with torch.cuda.device(q.device):
         _check(load_library().fmha_fwd(ctypes.byref(p), _stream(stream)), "fmha_fwd")
     return out, lse
 
 
 def bwd_params(q, k, v, o, dout, lse, dq, dk, dv, scale, causal, causal_shift=0, dk_accum=None,
-               dv_accum=None, flags=0, status=None) -> FmhaBwdParams:
+               dv_accum=None, flags=0, status=None, seqused_q=None, seqused_k=None) -> FmhaBwdParams:
     p = FmhaBwdParams()
     p.q, p.k, p.v, p.dout, p.lse = q.data_ptr(), k.data_ptr(), v.data_ptr(), dout.data_ptr(), lse.data_ptr()
     p.o = None if o is None else o.data_ptr()
@@ -222,6 +237,8 @@ def bwd_params(q, k, v, o, dout, lse, dq, dk, dv, scale, causal, causal_shift=0,
     p.flags = int(flags)
     p.status = None if status is None else status.data_ptr()
     p.dtype = _dtype_code(q)
+    p.seqused_q = _seqused_ptr(seqused_q, q.shape[0])
+    p.seqused_k = _seqused_ptr(seqused_k, q.shape[0])
     return p
 
 
@@ -233,7 +250,7 @@ def bwd_workspace_bytes(Z: int, Nq: int, H: int, D: int) -> int:
 
 def bwd(q, k, v, o, dout, lse, scale: float, causal: bool = False, causal_shift: int = 0,
         dq=None, dk=None, dv=None, dk_accum=None, dv_accum=None, workspace=None, flags: int = 0,
-        status=None, stream=None):
+        status=None, stream=None, seqused_q=None, seqused_k=None):
     """dQ, dK, dV through ``fmha_bwd``.  Outputs and workspace are allocated with torch unless
     passed in; with ``dk_accum`` / ``dv_accum`` (fp32) the fp16 dK / dV are not produced."""
     _require_cuda_half(q, k, v, o, dout, dq, dk, dv)
@@ -247,7 +264,7 @@ def bwd(q, k, v, o, dout, lse, scale: float, causal: bool = False, causal_shift:
     if workspace is None:
         workspace = torch.empty(bwd_workspace_bytes(Z, Nq, H, D), dtype=torch.uint8, device=q.device)
     p = bwd_params(q, k, v, o, dout, lse, dq, dk, dv, scale, causal, causal_shift, dk_accum,
-                   dv_accum, flags, status)
+                   dv_accum, flags, status, seqused_q, seqused_k)
     with torch.cuda.device(q.device):
         _check(load_library().fmha_bwd(ctypes.byref(p), ctypes.c_void_p(workspace.data_ptr()),
                                        workspace.numel() * workspace.element_size(),

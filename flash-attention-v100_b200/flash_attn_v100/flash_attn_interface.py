@@ -38,34 +38,33 @@ def _maybe_contiguous(x):
 
 
 @torch.library.custom_op("flash_attn_v100::fwd", mutates_args=(), device_types="cuda")
-def _fwd_op(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, softmax_scale: float,
-            causal: bool) -> Tuple[torch.Tensor, torch.Tensor]:
-    out, softmax_lse = flash_attn_cuda.fwd_lse(q, k, v, None, softmax_scale, causal)
+def _fwd_op(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, softmax_scale: float, causal: bool,
+            seqused_q: Optional[torch.Tensor] = None, seqused_k: Optional[torch.Tensor] = None
+            ) -> Tuple[torch.Tensor, torch.Tensor]:
+    out, softmax_lse = flash_attn_cuda.fwd_lse(q, k, v, None, softmax_scale, causal, seqused_q, seqused_k)
     return out, softmax_lse
 
 
 @_fwd_op.register_fake
-def _fwd_fake(q, k, v, softmax_scale, causal):
+def _fwd_fake(q, k, v, softmax_scale, causal, seqused_q=None, seqused_k=None):
     Z, N, H, _ = q.shape
     return torch.empty_like(q), q.new_empty((Z, H, N), dtype=torch.float32)
 
 
 @torch.library.custom_op("flash_attn_v100::bwd", mutates_args=(), device_types="cuda")
 def _bwd_op(dout: torch.Tensor, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, out: torch.Tensor,
-            softmax_lse: torch.Tensor, softmax_scale: float, causal: bool
-            ) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
-    dq, dk, dv = flash_attn_cuda.bwd(
-        dout, q, k, v, out,
-        None,          # D: computed by the extension in fp32
-        None,          # softmax_sum: softmax_lse already is max + ln(sum)
-        softmax_lse,
-        None, None, None, softmax_scale, causal,
-    )
+            softmax_lse: torch.Tensor, softmax_scale: float, causal: bool,
+            seqused_q: Optional[torch.Tensor] = None, seqused_k: Optional[torch.Tensor] = None,
+            deterministic: bool = False) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    # D = rowsum(dO * O) is computed by the extension in fp32; softmax_lse already is max + ln(sum)
+    dq, dk, dv = flash_attn_cuda.bwd_lse(dout, q, k, v, out, softmax_lse, softmax_scale, causal,
+                                         seqused_q, seqused_k, deterministic)
     return dq, dk, dv
 
 
 @_bwd_op.register_fake
-def _bwd_fake(dout, q, k, v, out, softmax_lse, softmax_scale, causal):
+def _bwd_fake(dout, q, k, v, out, softmax_lse, softmax_scale, causal, seqused_q=None, seqused_k=None,
+              deterministic=False):
     return torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
 
 
@@ -111,6 +110,38 @@ class FlashAttnFunc(torch.autograd.Function):
         dq, dk, dv = _flash_attn_backward(dout, q, k, v, out, softmax_lse, None, None, None, None,
                                           ctx.softmax_scale, ctx.causal)
         return dq, dk, dv, None, None
+
+
+class FlashAttnPaddedFunc(torch.autograd.Function):
+    """``FlashAttnFunc`` with per-batch real lengths and the deterministic-dQ switch; no
+    counterpart in the reference, whose callers pad and pay for the padding (README.md:3)."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, seqused_q, seqused_k, softmax_scale, causal, deterministic):
+        if softmax_scale is None:
+            softmax_scale = q.shape[-1] ** (-0.5)
+        q, k, v = [_maybe_contiguous(x) for x in (q, k, v)]
+        out, softmax_lse = _fwd_op(q, k, v, float(softmax_scale), bool(causal), seqused_q, seqused_k)
+        ctx.save_for_backward(q, k, v, out, softmax_lse, seqused_q, seqused_k)
+        ctx.softmax_scale, ctx.causal, ctx.deterministic = float(softmax_scale), bool(causal), bool(deterministic)
+        return out
+
+    @staticmethod
+    def backward(ctx, dout, *args):
+        q, k, v, out, softmax_lse, seqused_q, seqused_k = ctx.saved_tensors
+        dq, dk, dv = _bwd_op(_maybe_contiguous(dout), q, k, v, out, softmax_lse, ctx.softmax_scale,
+                             ctx.causal, seqused_q, seqused_k, ctx.deterministic)
+        return dq, dk, dv, None, None, None, None, None
+
+
+def flash_attn_padded_func(q, k, v, seqused_q=None, seqused_k=None, softmax_scale: Optional[float] = None,
+                           causal: bool = False, deterministic: bool = False):
+    """``flash_attn_func`` for right-padded batches: ``seqused_q`` / ``seqused_k`` (int32 CUDA
+    tensors, one entry per batch, or None) give the real number of query rows / keys of every
+    batch entry.  Padding keys are masked, padding tiles are skipped instead of computed, the
+    padding rows of the output and of every gradient are zero.  ``deterministic=True`` adds the
+    partial sums of dQ in a fixed order (bit-for-bit reproducible, slower)."""
+    return FlashAttnPaddedFunc.apply(q, k, v, seqused_q, seqused_k, softmax_scale, causal, deterministic)
 
 
 def flash_attn_func(q, k, v, softmax_scale: Optional[float] = None, causal: bool = False):

@@ -91,6 +91,14 @@ typedef struct {
    * to run beside it instead of after it. */
   int32_t sm_margin;
   int32_t dtype; /* FMHA_DTYPE_FP16 (0) or FMHA_DTYPE_BF16 */
+  /* Right-padded batches (optional, NULL = every row counts): int32 device arrays of `batch`
+   * entries.  Batch entry z has seqused_q[z] real query rows and seqused_k[z] real keys; the
+   * rest of its seqlen_q / seqlen_k rows is padding.  Tiles that are all padding are skipped,
+   * not computed and thrown away; padding keys are masked; padding rows of o are written as
+   * zeros and their lse as -inf.  The padding must hold finite values.  The reference only has
+   * the contract "the caller pads" (README.md:3) and computes the padding like real rows. */
+  const int32_t* seqused_q;
+  const int32_t* seqused_k;
 } FmhaFwdParams;
 
 typedef struct {
@@ -125,6 +133,10 @@ typedef struct {
   int32_t flags;
   int32_t* status;
   int32_t dtype; /* FMHA_DTYPE_FP16 (0) or FMHA_DTYPE_BF16 */
+  /* Right-padded batches, as in FmhaFwdParams: padding rows contribute nothing to dk / dv, and
+   * the padding rows of dq, dk and dv are written as zeros. */
+  const int32_t* seqused_q;
+  const int32_t* seqused_k;
 } FmhaBwdParams;
 
 #define FMHA_BWD_KEEP_WORKSPACE 1
