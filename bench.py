@@ -383,27 +383,51 @@ def measure_ring(args, torch, dist, world, rank, dev, steps=None):
     g = torch.Generator(device=dev).manual_seed(rank)
     ql, kl, vl, dol = (torch.randn((Z, 2 * c, H, D), generator=g, device=dev, dtype=torch.float32).half()
                        for _ in range(4))
+    from flash_attn_v100 import peer_ring
+
     be = fd.CudaBackend()
+    ring = peer_ring.PeerRing((Z, 2 * c, H, D), torch.float16, dev)
     res_holder = {}
 
-    def make_step(comm):
+    def make_step(comm, transport):
         def step():
-            out, lse = fd.ring_attention_forward(ql, kl, vl, scale, causal, None, be, comm=comm)
-            grads = fd.ring_attention_backward(ql, kl, vl, out, lse, dol, scale, causal, None, be, comm=comm)
+            if transport == "peer":
+                out, lse = ring.forward(ql, kl, vl, scale, causal, exchange=comm)
+                grads = ring.backward(ql, kl, vl, out, lse, dol, scale, causal, exchange=comm)
+            else:
+                out, lse = fd.ring_attention_forward(ql, kl, vl, scale, causal, None, be, comm=comm)
+                grads = fd.ring_attention_backward(ql, kl, vl, out, lse, dol, scale, causal, None, be, comm=comm)
             res_holder["last"] = (out,) + tuple(grads)
         return step
 
-    step = make_step(True)
+    # the product path: blocks pulled / gradients pushed by the copy engines.  With many ranks a
+    # hop is short (0.15 ms of forward kernels at 8 GPUs) and the Python loop that issues it would
+    # be what is timed: the whole step (kernels, copies, flag kernels, events on three streams) is
+    # captured in a CUDA graph once and replayed; the flags carry an iteration number that lives
+    # on the device, so a replay is a new iteration.
+    step = make_step(True, "peer")
     for _ in range(3):
         step()
-    regs = timed_regions(step, steps, 3, torch, dist, world, dev)
+    graph = graph_of(step, torch) if args.graph != "off" else None
+    graphed = graph is not None
+    t = torch.tensor([1 if graphed else 0], device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MIN)  # replay only if every rank captured
+    graphed = bool(t.item())
+    timed = graph.replay if graphed else step
+    regs = timed_regions(timed, steps, 3, torch, dist, world, dev)
     ms = median(regs)
     got = res_holder["last"]
-    ms_nocomm = None
+    ring.check()
+    ms_nocomm = ms_nccl = None
     if world > 1:
-        quiet = make_step(False)
+        quiet = make_step(False, "peer")
         quiet()
         ms_nocomm = median(timed_regions(quiet, steps, 3, torch, dist, world, dev))
+        # for comparison: the same schedule with NCCL send/recv passing the blocks round
+        nccl = make_step(True, "nccl")
+        nccl()
+        ms_nccl = median(timed_regions(nccl, steps, 2, torch, dist, world, dev))
 
     # parity on two sampled heads: gather them from every rank, rebuild the whole sequence, run
     # the oracle on it, compare this rank's shard
@@ -430,7 +454,9 @@ def measure_ring(args, torch, dist, world, rank, dev, steps=None):
            "causal": causal, "value": fl / (ms * 1e-3) / 1e12, "unit": "TFLOPS", "ms_per_step": ms,
            "regions": region_stats(regs), "steps": steps,
            "per_gpu_tflops": fl / (ms * 1e-3) / 1e12 / world,
-           "parallelism": f"zig-zag ring attention x{world} ({be.comm_name(world)})",
+           "parallelism": f"zig-zag ring attention x{world} (K/V pulled from their owners and dK/dV pushed to "
+                          "theirs by the copy engines over NVLink; flags in peer memory)",
+           "launch": "CUDA graph replay of one ring step" if graphed else "launches issued from Python",
            "rows_per_gpu": 2 * c, "kv_bytes_per_hop": kv_hop, "dkdv_bytes_per_hop": 2 * kv_hop,
            "parity": parity}
     if ms_nocomm is not None:
@@ -438,6 +464,8 @@ def measure_ring(args, torch, dist, world, rank, dev, steps=None):
         res["ms_per_step_without_exchange"] = ms_nocomm
         res["exposed_comm_ms_per_hop"] = max(0.0, ms - ms_nocomm) / hops
         res["exposed_comm_frac_of_step"] = max(0.0, ms - ms_nocomm) / ms
+        res["ms_per_step_nccl_send_recv"] = ms_nccl
+    ring.close()
     return res
 
 
@@ -570,6 +598,9 @@ def run_ours(args):
     ms_fwd, ms_pre, ms_bwd_main, ms_cvt = (median([e[i].elapsed_time(e[i + 1]) for e in ev]) for i in range(4))
     ms_parts = median([e[0].elapsed_time(e[4]) for e in ev])
     ms_bwd = ms_pre + ms_bwd_main + ms_cvt
+    # the same plain steps once more, right behind the instrumented loop: what the events between
+    # the kernels cost, and how far the GPU has drifted since the timed regions
+    regs_after = timed_regions(timed_step, args.steps, 3, torch, dist, world, dev)
     clocks_kernels = sampler.stop() if sampler else None
 
     # ---- end to end through the public API with host buffers.  Every step copies its own inputs
@@ -665,6 +696,8 @@ def run_ours(args):
                 "bwd_preprocess_frac_of_measured_hbm": pre_bytes / ms_pre / 1e6 / peaks["hbm_gbs"],
                 "bwd_convert_ms": ms_cvt,
                 "sum_of_parts_ms": ms_parts, "sum_of_parts_over_step": ms_parts / ms_step,
+                "plain_step_ms_right_after": median(regs_after),
+                "sum_of_parts_over_step_right_after": ms_parts / median(regs_after),
                 "ms_x_sm_mhz": None if not mhz else {"fwd": ms_fwd * mhz, "bwd_preprocess": ms_pre * mhz,
                                                     "bwd_main": ms_bwd_main * mhz, "bwd_convert": ms_cvt * mhz,
                                                     "sm_mhz": mhz},

@@ -17,6 +17,7 @@
 #include "aux_kernels.cuh"
 #include "bwd_kernel.cuh"
 #include "fwd_kernel.cuh"
+#include "peer_kernels.cuh"
 
 namespace {
 
@@ -469,6 +470,152 @@ int fmha_merge(float* o_acc, float* lse_acc, const void* o_part, FmhaStrides o_p
                int32_t head_dim, int32_t dtype, void* stream) {
   return fmha_merge_rows(o_acc, lse_acc, o_part, o_part_strides, lse_part, o_out, batch, heads,
                          rows, rows, 0, head_dim, dtype, stream);
+}
+
+// ---------------------------------------------------------------------------------------
+// multi-GPU plumbing
+// ---------------------------------------------------------------------------------------
+int fmha_ipc_export(const void* ptr, void* handle64, int64_t* offset) {
+  if (ptr == nullptr || handle64 == nullptr || offset == nullptr) return FMHA_ERR_NULL_POINTER;
+  static_assert(sizeof(cudaIpcMemHandle_t) == 64, "the header promises 64 bytes");
+  using RangeFn = CUresult (*)(CUdeviceptr*, size_t*, CUdeviceptr);
+  void* fn = nullptr;
+  cudaDriverEntryPointQueryResult qres;
+  if (cudaGetDriverEntryPoint("cuMemGetAddressRange", &fn, cudaEnableDefault, &qres) != cudaSuccess ||
+      qres != cudaDriverEntryPointSuccess)
+    return FMHA_ERR_NO_DEVICE;
+  CUdeviceptr base = 0;
+  size_t size = 0;
+  if (reinterpret_cast<RangeFn>(fn)(&base, &size, reinterpret_cast<CUdeviceptr>(ptr)) != CUDA_SUCCESS)
+    return FMHA_ERR_BAD_ALIGNMENT;
+  cudaIpcMemHandle_t h;
+  if (cudaIpcGetMemHandle(&h, reinterpret_cast<void*>(base)) != cudaSuccess) {
+    (void)cudaGetLastError();
+    return FMHA_ERR_LAUNCH;
+  }
+  std::memcpy(handle64, &h, sizeof(h));
+  *offset = (int64_t)(reinterpret_cast<CUdeviceptr>(ptr) - base);
+  return FMHA_OK;
+}
+
+int fmha_ipc_open(const void* handle64, int64_t offset, void** ptr) {
+  if (handle64 == nullptr || ptr == nullptr) return FMHA_ERR_NULL_POINTER;
+  cudaIpcMemHandle_t h;
+  std::memcpy(&h, handle64, sizeof(h));
+  void* base = nullptr;
+  if (cudaIpcOpenMemHandle(&base, h, cudaIpcMemLazyEnablePeerAccess) != cudaSuccess) {
+    (void)cudaGetLastError();
+    return FMHA_ERR_LAUNCH;
+  }
+  *ptr = static_cast<char*>(base) + offset;
+  return FMHA_OK;
+}
+
+int fmha_ipc_close(void* ptr, int64_t offset) {
+  if (ptr == nullptr) return FMHA_ERR_NULL_POINTER;
+  if (cudaIpcCloseMemHandle(static_cast<char*>(ptr) - offset) != cudaSuccess) {
+    (void)cudaGetLastError();
+    return FMHA_ERR_LAUNCH;
+  }
+  return FMHA_OK;
+}
+
+int fmha_peer_copy(void* dst, const void* src, size_t bytes, void* stream) {
+  if (dst == nullptr || src == nullptr) return FMHA_ERR_NULL_POINTER;
+  if (bytes == 0) return FMHA_OK;
+  return cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDefault, static_cast<cudaStream_t>(stream)) ==
+                 cudaSuccess
+             ? FMHA_OK
+             : FMHA_ERR_LAUNCH;
+}
+
+int fmha_peer_copy_2d(void* dst, size_t dst_pitch, const void* src, size_t src_pitch,
+                      size_t row_bytes, size_t rows, void* stream) {
+  if (dst == nullptr || src == nullptr) return FMHA_ERR_NULL_POINTER;
+  if (row_bytes == 0 || rows == 0) return FMHA_OK;
+  if (row_bytes > dst_pitch || row_bytes > src_pitch) return FMHA_ERR_BAD_STRIDE;
+  return cudaMemcpy2DAsync(dst, dst_pitch, src, src_pitch, row_bytes, rows, cudaMemcpyDefault,
+                           static_cast<cudaStream_t>(stream)) == cudaSuccess
+             ? FMHA_OK
+             : FMHA_ERR_LAUNCH;
+}
+
+int fmha_counter_bump(int32_t* word, void* stream) {
+  if (word == nullptr) return FMHA_ERR_NULL_POINTER;
+  fmha::counter_bump_kernel<<<1, 1, 0, static_cast<cudaStream_t>(stream)>>>(word);
+  return cudaGetLastError() == cudaSuccess ? FMHA_OK : FMHA_ERR_LAUNCH;
+}
+
+int fmha_peer_signal(int32_t* const* flags, int32_t n, const int32_t* value, void* stream) {
+  if (flags == nullptr || value == nullptr) return FMHA_ERR_NULL_POINTER;
+  if (n <= 0) return FMHA_OK;
+  if (n > fmha::kMaxPeers) return FMHA_ERR_TOO_LARGE;
+  fmha::PeerFlagList list;
+  list.n = n;
+  for (int i = 0; i < n; ++i) {
+    if (flags[i] == nullptr) return FMHA_ERR_NULL_POINTER;
+    list.ptr[i] = flags[i];
+  }
+  fmha::peer_signal_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(list, value);
+  return cudaGetLastError() == cudaSuccess ? FMHA_OK : FMHA_ERR_LAUNCH;
+}
+
+int fmha_peer_wait(const int32_t* const* flags, int32_t n, const int32_t* value, int32_t* status,
+                   int32_t timeout_ms, void* stream) {
+  if (flags == nullptr || value == nullptr) return FMHA_ERR_NULL_POINTER;
+  if (n <= 0) return FMHA_OK;
+  if (n > fmha::kMaxPeers) return FMHA_ERR_TOO_LARGE;
+  if (timeout_ms <= 0 || timeout_ms > 60000) return FMHA_ERR_BAD_SHAPE;
+  fmha::PeerFlagList list;
+  list.n = n;
+  for (int i = 0; i < n; ++i) {
+    if (flags[i] == nullptr) return FMHA_ERR_NULL_POINTER;
+    list.ptr[i] = const_cast<int*>(flags[i]);
+  }
+  fmha::peer_wait_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(
+      list, value, status, (unsigned long long)timeout_ms * 1000000ull);
+  return cudaGetLastError() == cudaSuccess ? FMHA_OK : FMHA_ERR_LAUNCH;
+}
+
+int fmha_sum_partials(const float* const* parts, const int32_t* rows_per_part, int32_t n_parts,
+                      void* out, FmhaStrides out_strides, int32_t batch, int32_t heads, int32_t rows,
+                      int32_t head_dim, int32_t dtype, void* stream) {
+  if (parts == nullptr || rows_per_part == nullptr || out == nullptr) return FMHA_ERR_NULL_POINTER;
+  if (dtype != FMHA_DTYPE_FP16 && dtype != FMHA_DTYPE_BF16) return FMHA_ERR_BAD_DTYPE;
+  if (head_dim != 64 && head_dim != 128) return FMHA_ERR_BAD_HEAD_DIM;
+  if (batch <= 0 || heads <= 0 || rows <= 0 || n_parts <= 0) return FMHA_ERR_BAD_SHAPE;
+  if (n_parts > fmha::kMaxPeers) return FMHA_ERR_TOO_LARGE;
+  if (!aligned16(out)) return FMHA_ERR_BAD_ALIGNMENT;
+  int rc = check_strides(out_strides, rows, heads, batch);
+  if (rc) return rc;
+  fmha::PartList list;
+  list.n = n_parts;
+  for (int i = 0; i < n_parts; ++i) {
+    if (parts[i] == nullptr) return FMHA_ERR_NULL_POINTER;
+    if (!aligned16(parts[i])) return FMHA_ERR_BAD_ALIGNMENT;
+    if (rows_per_part[i] < 0 || rows_per_part[i] > rows) return FMHA_ERR_BAD_SHAPE;
+    list.ptr[i] = parts[i];
+    list.rows[i] = rows_per_part[i];
+  }
+  const long long total = (long long)batch * rows * heads;
+  const int rows_per_block = 256 / (head_dim / 8);
+  const unsigned grid = (unsigned)((total + rows_per_block - 1) / rows_per_block);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const fmha::Strides3 so = to3(out_strides);
+  if (dtype == FMHA_DTYPE_BF16) {
+    auto* o = static_cast<__nv_bfloat16*>(out);
+    if (head_dim == 128)
+      fmha::sum_partials_kernel<128, __nv_bfloat16><<<grid, 256, 0, s>>>(list, o, so, heads, rows, total);
+    else
+      fmha::sum_partials_kernel<64, __nv_bfloat16><<<grid, 256, 0, s>>>(list, o, so, heads, rows, total);
+  } else {
+    auto* o = static_cast<__half*>(out);
+    if (head_dim == 128)
+      fmha::sum_partials_kernel<128, __half><<<grid, 256, 0, s>>>(list, o, so, heads, rows, total);
+    else
+      fmha::sum_partials_kernel<64, __half><<<grid, 256, 0, s>>>(list, o, so, heads, rows, total);
+  }
+  return cudaGetLastError() == cudaSuccess ? FMHA_OK : FMHA_ERR_LAUNCH;
 }
 
 int fmha_b200_forward(const void* query_ptr, const void* key_ptr, const void* value_ptr,

@@ -30,6 +30,8 @@ FMHA_DTYPE_BF16 = 1
 EXPORTED_SYMBOLS = (
     "fmha_fwd", "fmha_bwd_workspace_bytes", "fmha_bwd", "fmha_bwd_static_scratch", "fmha_bwd_convert_dq", "fmha_merge", "fmha_merge_rows", "fmha_b200_forward",
     "fmha_b200_backward", "fmha_status_string", "fmha_version",
+    "fmha_ipc_export", "fmha_ipc_open", "fmha_ipc_close", "fmha_peer_copy", "fmha_peer_copy_2d",
+    "fmha_counter_bump", "fmha_peer_signal", "fmha_peer_wait", "fmha_sum_partials",
 )
 
 
@@ -109,6 +111,20 @@ def load_library() -> ctypes.CDLL:
     lib.fmha_b200_backward.restype = ctypes.c_int
     lib.fmha_b200_backward.argtypes = [ctypes.c_void_p] * 10 + [ctypes.c_size_t] + [
         ctypes.c_int] * 5 + [ctypes.c_float, ctypes.c_int, ctypes.c_void_p]
+    vp, i32, i64, sz = ctypes.c_void_p, ctypes.c_int32, ctypes.c_int64, ctypes.c_size_t
+    for name, args in (
+            ("fmha_ipc_export", [vp, vp, ctypes.POINTER(i64)]),
+            ("fmha_ipc_open", [vp, i64, ctypes.POINTER(vp)]),
+            ("fmha_ipc_close", [vp, i64]),
+            ("fmha_peer_copy", [vp, vp, sz, vp]),
+            ("fmha_peer_copy_2d", [vp, sz, vp, sz, sz, sz, vp]),
+            ("fmha_counter_bump", [vp, vp]),
+            ("fmha_peer_signal", [ctypes.POINTER(vp), i32, vp, vp]),
+            ("fmha_peer_wait", [ctypes.POINTER(vp), i32, vp, vp, i32, vp]),
+            ("fmha_sum_partials", [ctypes.POINTER(vp), ctypes.POINTER(i32), i32, vp, FmhaStrides, i32, i32,
+                                   i32, i32, i32, vp])):
+        getattr(lib, name).restype = ctypes.c_int
+        getattr(lib, name).argtypes = args
     lib.fmha_status_string.restype = ctypes.c_char_p
     lib.fmha_status_string.argtypes = [ctypes.c_int]
     lib.fmha_version.restype = ctypes.c_char_p
@@ -312,3 +328,72 @@ def merge(o_acc, lse_acc, o_part, lse_part, o_out=None, stream=None, row_offset:
                                               _stream(stream)),
                "fmha_merge_rows")
     return o_acc, lse_acc
+
+
+# ----------------------------------------------------------------------------------------------
+# multi-GPU plumbing (CUDA IPC addresses, copy-engine copies, flags between GPUs)
+# ----------------------------------------------------------------------------------------------
+def ipc_export(t: torch.Tensor):
+    """(64-byte handle, offset) that another process of this node can turn into an address of
+    ``t``'s memory with ``ipc_open``."""
+    handle = ctypes.create_string_buffer(64)
+    offset = ctypes.c_int64(0)
+    with torch.cuda.device(t.device):
+        _check(load_library().fmha_ipc_export(ctypes.c_void_p(t.data_ptr()), handle, ctypes.byref(offset)),
+               "fmha_ipc_export")
+    return bytes(handle.raw), int(offset.value)
+
+
+def ipc_open(handle: bytes, offset: int) -> int:
+    """Address (int) in this process of memory another process exported."""
+    out = ctypes.c_void_p(0)
+    _check(load_library().fmha_ipc_open(ctypes.c_char_p(handle), offset, ctypes.byref(out)), "fmha_ipc_open")
+    return int(out.value)
+
+
+def ipc_close(addr: int, offset: int):
+    _check(load_library().fmha_ipc_close(ctypes.c_void_p(addr), offset), "fmha_ipc_close")
+
+
+def peer_copy(dst: int, src: int, nbytes: int, stream=None):
+    _check(load_library().fmha_peer_copy(ctypes.c_void_p(dst), ctypes.c_void_p(src), nbytes, _stream(stream)),
+           "fmha_peer_copy")
+
+
+def peer_copy_2d(dst: int, dst_pitch: int, src: int, src_pitch: int, row_bytes: int, rows: int, stream=None):
+    _check(load_library().fmha_peer_copy_2d(ctypes.c_void_p(dst), dst_pitch, ctypes.c_void_p(src), src_pitch,
+                                            row_bytes, rows, _stream(stream)), "fmha_peer_copy_2d")
+
+
+def counter_bump(word: torch.Tensor, stream=None):
+    _check(load_library().fmha_counter_bump(ctypes.c_void_p(word.data_ptr()), _stream(stream)),
+           "fmha_counter_bump")
+
+
+def _addr_array(addrs):
+    return (ctypes.c_void_p * len(addrs))(*[ctypes.c_void_p(a) for a in addrs])
+
+
+def peer_signal(flag_addrs, value_addr: int, stream=None):
+    if flag_addrs:
+        _check(load_library().fmha_peer_signal(_addr_array(flag_addrs), len(flag_addrs),
+                                               ctypes.c_void_p(value_addr), _stream(stream)), "fmha_peer_signal")
+
+
+def peer_wait(flag_addrs, value_addr: int, status: Optional[torch.Tensor], timeout_ms: int, stream=None):
+    if flag_addrs:
+        _check(load_library().fmha_peer_wait(_addr_array(flag_addrs), len(flag_addrs), ctypes.c_void_p(value_addr),
+                                             None if status is None else ctypes.c_void_p(status.data_ptr()),
+                                             int(timeout_ms), _stream(stream)), "fmha_peer_wait")
+
+
+def sum_partials(part_addrs, rows_per_part, out: torch.Tensor, stream=None):
+    """out (Z, rows, H, D) 16-bit = sum of fp32 buffers (Z, rows, H, D), part s counting only its
+    first rows_per_part[s] rows of every batch entry."""
+    Z, rows, H, D = out.shape
+    rp = (ctypes.c_int32 * len(rows_per_part))(*rows_per_part)
+    with torch.cuda.device(out.device):
+        _check(load_library().fmha_sum_partials(_addr_array(part_addrs), rp, len(part_addrs), _ptr(out),
+                                                _strides(out), Z, H, rows, D, _dtype_code(out),
+                                                _stream(stream)), "fmha_sum_partials")
+    return out

@@ -79,12 +79,16 @@ class CudaBackend:
         # 32 free SMs shorten the ring forward by 10 % and 8 or 16 by nothing, while on long hops
         # every SM given away is attention throughput lost.
         self.sm_margin = sm_margin
+        # optional device status word handed to every attention kernel (a bounded wait that ran
+        # out anywhere makes the kernels behind it return at once)
+        self.status = None
 
     def comm_name(self, world: int) -> str:
         return "NCCL send/recv" if world > 1 else "one rank, no exchange"
 
     def fwd(self, q, k, v, scale, causal, overlap: bool = False):
-        return self.cabi.fwd(q, k, v, scale, causal, sm_margin=self.sm_margin if overlap else 0)
+        return self.cabi.fwd(q, k, v, scale, causal, sm_margin=self.sm_margin if overlap else 0,
+                             status=self.status)
 
     def new_accumulators(self, q):
         Z, N, H, D = q.shape
@@ -92,19 +96,21 @@ class CudaBackend:
         lse_acc = torch.full((Z, H, N), float("-inf"), dtype=torch.float32, device=q.device)
         return o_acc, lse_acc
 
-    def merge(self, o_acc, lse_acc, o_part, lse_part, rows: slice):
-        """Merge a partial result for query rows ``rows`` into the accumulators, in place."""
-        self.cabi.merge(o_acc, lse_acc, o_part, lse_part, row_offset=rows.start or 0)
+    def merge(self, o_acc, lse_acc, o_part, lse_part, rows: slice, o_out=None):
+        """Merge a partial result for query rows ``rows`` into the accumulators, in place; with
+        ``o_out`` the merged rows are also written in the tensors' 16-bit type."""
+        self.cabi.merge(o_acc, lse_acc, o_part, lse_part, o_out=o_out, row_offset=rows.start or 0)
 
     def finish(self, o_acc, lse_acc, dtype):
         return o_acc.to(dtype), lse_acc
 
-    def new_bwd_state(self, q):
+    def new_bwd_state(self, q, device=None):
         Z, N, H, D = q.shape
+        device = q.device if device is None else device
         nbytes = self.cabi.bwd_workspace_bytes
         return {
-            "full": torch.empty(nbytes(Z, N, H, D), dtype=torch.uint8, device=q.device),
-            "half": torch.empty(nbytes(Z, N // 2, H, D), dtype=torch.uint8, device=q.device),
+            "full": torch.empty(nbytes(Z, N, H, D), dtype=torch.uint8, device=device),
+            "half": torch.empty(nbytes(Z, N // 2, H, D), dtype=torch.uint8, device=device),
             "full_used": False, "half_used": False,
         }
 
@@ -114,7 +120,7 @@ class CudaBackend:
         c = self.cabi
         flags = c.FMHA_BWD_SKIP_DQ_CONVERT | (c.FMHA_BWD_KEEP_WORKSPACE if state[which + "_used"] else 0)
         c.bwd(q, k, v, o, dout, lse, scale, causal, dq=None, dk_accum=dk_acc, dv_accum=dv_acc,
-              workspace=state[which], flags=flags)
+              workspace=state[which], flags=flags, status=self.status)
         state[which + "_used"] = True
 
     def bwd_finish(self, state, q, k, v, o, dout, lse, scale):

@@ -1,0 +1,330 @@
+"""Ring attention over NVLink without a collective library in the data path.
+
+The reference is single-GPU (kernel/fused_mha_api.cpp:61); ``distributed.py`` adds sequence
+sharding with K/V blocks passed from rank to rank by NCCL send/recv.  On an NVSwitch node every
+GPU reaches every other at full bandwidth, so nothing has to be *passed round*: this module
+shards the same way (zig-zag, see ``distributed.py``) but
+
+* every rank PULLS the K/V block it needs next straight from the rank that owns it, with the
+  copy engines (``cudaMemcpyAsync`` from an address mapped through CUDA IPC), one step ahead,
+  on a stream of its own, while the attention kernel of the current step runs on all SMs;
+* in the backward pass every rank PUSHES its fp32 dK/dV contribution for a visiting block to
+  a slot at the block's owner, again with the copy engines while the next step computes; the
+  owner adds up the slots once at the end (``fmha_sum_partials``).  No accumulator travels and
+  nothing waits for a gradient hop;
+* readiness of a buffer is a flag in the consumer's memory set by the producer
+  (``fmha_peer_signal``) and awaited on the consumer's stream (``fmha_peer_wait``, bounded: a
+  wait that runs out sets the status word and the attention kernels behind it return at once).
+  Flags carry an iteration number kept on the device; there is no host synchronisation and no
+  allocation in a step.
+
+The attention kernels only ever read this GPU's own memory: a pulled block lands in a local
+buffer first.  torch.distributed is used once, to exchange the IPC handles.
+"""
+from __future__ import annotations
+
+from typing import List, Optional, Tuple
+
+import torch
+import torch.distributed as dist
+
+# rows of the flag matrix (one column per peer)
+_READY_F, _ACK_F, _READY_B, _ACK_B, _GRAD_READY, _GRAD_FREE, _N_FLAGS = 0, 1, 2, 3, 4, 5, 6
+
+
+class _KVSide:
+    """Export buffer, two receive buffers and the iteration words of one direction (fwd or bwd)."""
+
+    def __init__(self, shape, dtype, device, ready_row, ack_row):
+        self.export = torch.empty((2,) + shape, dtype=dtype, device=device)
+        self.recv = [torch.empty((2,) + shape, dtype=dtype, device=device) for _ in range(2)]
+        self.it = torch.zeros(2, dtype=torch.int32, device=device)  # [this iteration, the previous]
+        self.ready_row, self.ack_row = ready_row, ack_row
+
+
+class PeerRing:
+    """Buffers, peer mappings and streams for ring attention on local shards of one shape.
+
+    Create it once per (shard shape, dtype) on every rank of ``group`` (collective: the IPC
+    handles are exchanged here), then call ``forward`` / ``backward`` any number of times, all
+    ranks in the same order."""
+
+    def __init__(self, shard_shape, dtype, device, group=None, timeout_ms: int = 10000, sm_margin: int = 2):
+        from flash_attn_v100 import cabi, distributed as fd
+
+        self.cabi = cabi
+        self.group = group
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        if self.world > 16:
+            raise ValueError("PeerRing supports up to 16 ranks on one node")
+        self.shape = tuple(shard_shape)
+        self.dtype, self.device = dtype, torch.device(device)
+        Z, rows, H, D = self.shape
+        if rows % 2:
+            raise ValueError("a zig-zag shard has an even number of rows")
+        self.timeout_ms = int(timeout_ms)
+        self.backend = fd.CudaBackend(sm_margin=sm_margin if self.world > 1 else 0)
+        with torch.cuda.device(self.device):
+            self.fwd_side = _KVSide(self.shape, dtype, self.device, _READY_F, _ACK_F)
+            self.bwd_side = _KVSide(self.shape, dtype, self.device, _READY_B, _ACK_B)
+            self.flags = torch.zeros((_N_FLAGS, self.world), dtype=torch.int32, device=self.device)
+            self.grad_it = torch.zeros(2, dtype=torch.int32, device=self.device)
+            self.slots = torch.empty((self.world, 2) + self.shape, dtype=torch.float32, device=self.device)
+            self.part = [torch.empty((2,) + self.shape, dtype=torch.float32, device=self.device) for _ in range(2)]
+            self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
+            self.backend.status = self.status
+            self.bwd_state = self.backend.new_bwd_state(torch.empty(self.shape, dtype=dtype, device="meta"),
+                                                        device=self.device)
+            self.pull_stream = torch.cuda.Stream(device=self.device, priority=-1)
+            self.push_stream = torch.cuda.Stream(device=self.device, priority=-1)
+            torch.cuda.synchronize(self.device)
+        # ---- exchange the addresses (CUDA IPC): my export buffers, slots and flags for every peer
+        mine = {name: cabi.ipc_export(t) for name, t in (
+            ("kv_f", self.fwd_side.export), ("kv_b", self.bwd_side.export), ("slots", self.slots),
+            ("flags", self.flags))}
+        everyone = [None] * self.world
+        dist.all_gather_object(everyone, mine, group=group)
+        self._opened = {}
+        own = {"kv_f": self.fwd_side.export.data_ptr(), "kv_b": self.bwd_side.export.data_ptr(),
+               "slots": self.slots.data_ptr(), "flags": self.flags.data_ptr()}
+        self.peer = []
+        with torch.cuda.device(self.device):
+            for p in range(self.world):
+                if p == self.rank:
+                    self.peer.append(own)
+                    continue
+                entry = {}
+                for name, (handle, offset) in everyone[p].items():
+                    key = (p, handle)
+                    if key not in self._opened:
+                        self._opened[key] = cabi.ipc_open(handle, 0)
+                    entry[name] = self._opened[key] + offset
+                self.peer.append(entry)
+        dist.barrier(group=group)
+
+    # ---- addresses
+    def _flag(self, owner: int, row: int, col: int) -> int:
+        return self.peer[owner]["flags"] + 4 * (row * self.world + col)
+
+    def _others(self) -> List[int]:
+        return [p for p in range(self.world) if p != self.rank]
+
+    def close(self):
+        """Unmap the peers' memory (collective: nobody may still be copying)."""
+        torch.cuda.synchronize(self.device)
+        dist.barrier(group=self.group)
+        with torch.cuda.device(self.device):
+            for addr in self._opened.values():
+                self.cabi.ipc_close(addr, 0)
+        self._opened = {}
+
+    def check(self):
+        """Host check of the status word (synchronises): raises if a peer wait ran out."""
+        code = int(self.status.item())
+        if code != 0:
+            raise RuntimeError(f"ring attention: a bounded wait gave up (status {code:#x})")
+
+    # ---- K/V side shared by forward and backward
+    def _publish(self, side: _KVSide, k, v, cs, exchange: bool):
+        """This rank's K/V into the export buffer, once the peers have finished reading the
+        previous iteration's; then tell them.  Returns the address of the iteration word."""
+        c = self.cabi
+        cur, prev = side.it.data_ptr(), side.it.data_ptr() + 4
+        if self.world == 1:
+            return cur
+        if exchange:
+            others = self._others()
+            c.counter_bump(side.it, cs)
+            c.peer_wait([self._flag(self.rank, side.ack_row, p) for p in others], prev, self.status,
+                        self.timeout_ms, cs)
+        side.export[0].copy_(k)
+        side.export[1].copy_(v)
+        if exchange:
+            c.peer_signal([self._flag(p, side.ready_row, self.rank) for p in others], cur, cs)
+        return cur
+
+    def _pull(self, side: _KVSide, kv_name: str, t: int, cur: int, causal: bool, ev_free, ev_ready,
+              exchange: bool):
+        """Fetch the block of step t (t >= 1) into receive buffer t % 2 on the pull stream."""
+        c = self.cabi
+        Z, rows, H, D = self.shape
+        src = (self.rank - t) % self.world
+        buf = side.recv[t % 2]
+        esize = buf.element_size()
+        with torch.cuda.stream(self.pull_stream):
+            if t >= 3:
+                self.pull_stream.wait_event(ev_free[t % 2])  # the kernels of step t - 2 are done with it
+            if exchange:
+                c.peer_wait([self._flag(self.rank, side.ready_row, src)], cur, self.status,
+                            self.timeout_ms, self.pull_stream)
+                src_addr = self.peer[src][kv_name]
+            else:
+                src_addr = side.export.data_ptr()  # measurements: same bytes, local source
+            entry = rows * H * D * esize
+            if causal and src < self.rank:
+                # only the first half of the block is needed
+                c.peer_copy_2d(buf.data_ptr(), entry, src_addr, entry, entry // 2, 2 * Z, self.pull_stream)
+            else:
+                c.peer_copy(buf.data_ptr(), src_addr, 2 * Z * entry, self.pull_stream)
+            if exchange:
+                c.peer_signal([self._flag(src, side.ack_row, self.rank)], cur, self.pull_stream)
+            ev_ready[t % 2].record(self.pull_stream)
+
+    # ---- forward
+    def forward(self, q, k, v, scale: float, causal: bool, exchange: bool = True
+                ) -> Tuple[torch.Tensor, torch.Tensor]:
+        """This rank's (out, lse) shard; q, k, v are the local zig-zag shards."""
+        be, world, rank = self.backend, self.world, self.rank
+        cs = torch.cuda.current_stream(self.device)
+        side = self.fwd_side
+        half = self.shape[1] // 2
+        self.pull_stream.wait_stream(cs)  # earlier work on the receive buffers is behind us
+        cur = self._publish(side, k, v, cs, exchange)
+        ev_ready = [torch.cuda.Event(), torch.cuda.Event()]
+        ev_free = [torch.cuda.Event(), torch.cuda.Event()]
+        o_acc, lse_acc = be.new_accumulators(q)
+        out = torch.empty_like(q)
+        if world > 1:
+            self.pull_stream.wait_stream(cs)
+            self._pull(side, "kv_f", 1, cur, causal, ev_free, ev_ready, exchange)
+        for t in range(world):
+            src = (rank - t) % world
+            if t == 0:
+                kb, vb = k, v
+            else:
+                cs.wait_event(ev_ready[t % 2])
+                kb, vb = side.recv[t % 2][0], side.recv[t % 2][1]
+            if t + 1 < world:
+                self._pull(side, "kv_f", t + 1, cur, causal, ev_free, ev_ready, exchange)
+            last = t + 1 == world
+            ov = not last
+            if t == 0:
+                o_p, l_p = be.fwd(q, kb, vb, scale, causal, ov)
+                be.merge(o_acc, lse_acc, o_p, l_p, slice(0, None), out if last else None)
+            elif not causal:
+                o_p, l_p = be.fwd(q, kb, vb, scale, False, ov)
+                be.merge(o_acc, lse_acc, o_p, l_p, slice(0, None), out if last else None)
+            elif src < rank:
+                o_p, l_p = be.fwd(q, kb[:, :half], vb[:, :half], scale, False, ov)
+                be.merge(o_acc, lse_acc, o_p, l_p, slice(0, None), out if last else None)
+            else:
+                o_p, l_p = be.fwd(q[:, half:], kb, vb, scale, False, ov)
+                be.merge(o_acc, lse_acc, o_p, l_p, slice(half, None), None)
+                if last:
+                    out.copy_(o_acc)
+            if t >= 1:
+                ev_free[t % 2].record(cs)
+        cs.wait_stream(self.pull_stream)  # nothing of this call is left on the side stream
+        return out, lse_acc
+
+    # ---- backward
+    def backward(self, q, k, v, out, lse, dout, scale: float, causal: bool, exchange: bool = True):
+        """This rank's (dq, dk, dv) shards."""
+        c, be, world, rank = self.cabi, self.backend, self.world, self.rank
+        cs = torch.cuda.current_stream(self.device)
+        side = self.bwd_side
+        Z, rows, H, D = self.shape
+        half = rows // 2
+        others = self._others() if exchange else []
+        self.pull_stream.wait_stream(cs)
+        self.push_stream.wait_stream(cs)
+        cur = self._publish(side, k, v, cs, exchange)
+        # my slots may be written for this iteration: everything of my previous backward is
+        # behind this point of the stream
+        gcur = self.grad_it.data_ptr()
+        if others:
+            c.counter_bump(self.grad_it, cs)
+            c.peer_signal([self._flag(p, _GRAD_FREE, rank) for p in others], gcur, cs)
+        state = self.bwd_state
+        state["full_used"] = state["half_used"] = False
+        ev_ready = [torch.cuda.Event(), torch.cuda.Event()]
+        ev_free = [torch.cuda.Event(), torch.cuda.Event()]
+        ev_part = [torch.cuda.Event(), torch.cuda.Event()]
+        ev_pushed = [torch.cuda.Event(), torch.cuda.Event()]
+        lse_half = lse[:, :, half:].contiguous()
+        if world > 1:
+            self.pull_stream.wait_stream(cs)
+            self._pull(side, "kv_b", 1, cur, causal, ev_free, ev_ready, exchange)
+        slot_bytes = 2 * Z * rows * H * D * 4
+        entry = rows * H * D * 4
+        for t in range(world):
+            src = (rank - t) % world
+            if t == 0:
+                kb, vb = k, v
+                target = self.slots[rank]  # my own contribution goes straight into my slot
+            else:
+                cs.wait_event(ev_ready[t % 2])
+                kb, vb = side.recv[t % 2][0], side.recv[t % 2][1]
+                target = self.part[t % 2]
+                if t >= 3:
+                    cs.wait_event(ev_pushed[t % 2])  # the push of step t - 2 has read the buffer
+            first_half_only = causal and t > 0 and src < rank
+            if first_half_only:
+                target[:, :, :half].zero_()
+            else:
+                target.zero_()
+            if t + 1 < world:
+                self._pull(side, "kv_b", t + 1, cur, causal, ev_free, ev_ready, exchange)
+            dk_t, dv_t = target[0], target[1]
+            if t == 0:
+                be.bwd_step(state, "full", q, kb, vb, out, dout, lse, scale, causal, dk_t, dv_t)
+            elif not causal:
+                be.bwd_step(state, "full", q, kb, vb, out, dout, lse, scale, False, dk_t, dv_t)
+            elif src < rank:
+                be.bwd_step(state, "full", q, kb[:, :half], vb[:, :half], out, dout, lse, scale, False,
+                            dk_t[:, :half], dv_t[:, :half])
+            else:
+                be.bwd_step(state, "half", q[:, half:], kb, vb, out[:, half:], dout[:, half:], lse_half,
+                            scale, False, dk_t, dv_t)
+            if t >= 1:
+                ev_free[t % 2].record(cs)
+                ev_part[t % 2].record(cs)
+                if exchange:
+                    with torch.cuda.stream(self.push_stream):
+                        ps = self.push_stream
+                        ps.wait_event(ev_part[t % 2])
+                        c.peer_wait([self._flag(rank, _GRAD_FREE, src)], gcur, self.status, self.timeout_ms, ps)
+                        dst = self.peer[src]["slots"] + rank * slot_bytes
+                        if first_half_only:
+                            c.peer_copy_2d(dst, entry, target.data_ptr(), entry, entry // 2, 2 * Z, ps)
+                        else:
+                            c.peer_copy(dst, target.data_ptr(), slot_bytes, ps)
+                        c.peer_signal([self._flag(src, _GRAD_READY, rank)], gcur, ps)
+                        ev_pushed[t % 2].record(ps)
+        # every other rank's contribution to my block has arrived; add them up
+        c.peer_wait([self._flag(rank, _GRAD_READY, p) for p in others], gcur, self.status, self.timeout_ms, cs)
+        sources = list(range(world)) if exchange else [rank]
+        rows_per = [rows if (p == rank or not causal or p < rank) else half for p in sources]
+        dk, dv = torch.empty_like(k), torch.empty_like(v)
+        base = self.slots.data_ptr()
+        c.sum_partials([base + p * slot_bytes for p in sources], rows_per, dk, cs)
+        c.sum_partials([base + p * slot_bytes + slot_bytes // 2 for p in sources], rows_per, dv, cs)
+        cs.wait_stream(self.push_stream)
+        cs.wait_stream(self.pull_stream)
+        dq = be.bwd_finish(state, q, k, v, out, dout, lse, scale)
+        return dq, dk, dv
+
+
+class PeerRingAttnFunc(torch.autograd.Function):
+    """``PeerRingAttnFunc.apply(ring, q, k, v, softmax_scale, causal)`` on zig-zag shards."""
+
+    @staticmethod
+    def forward(ctx, ring: PeerRing, q, k, v, softmax_scale, causal):
+        if softmax_scale is None:
+            softmax_scale = q.shape[-1] ** (-0.5)
+        out, lse = ring.forward(q, k, v, softmax_scale, causal)
+        ctx.save_for_backward(q, k, v, out, lse)
+        ctx.ring, ctx.softmax_scale, ctx.causal = ring, softmax_scale, causal
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        q, k, v, out, lse = ctx.saved_tensors
+        dq, dk, dv = ctx.ring.backward(q, k, v, out, lse, dout.contiguous(), ctx.softmax_scale, ctx.causal)
+        return None, dq, dk, dv, None, None
+
+
+def peer_ring_flash_attn_func(ring: PeerRing, q, k, v, softmax_scale=None, causal=False):
+    """Sequence-parallel counterpart of ``flash_attn_func`` over ``ring`` (see ``PeerRing``)."""
+    return PeerRingAttnFunc.apply(ring, q, k, v, softmax_scale, causal)

@@ -240,6 +240,49 @@ int fmha_merge_rows(float* o_acc, float* lse_acc, const void* o_part, FmhaStride
                     int32_t acc_rows, int32_t row_offset, int32_t head_dim, int32_t dtype,
                     void* stream);
 
+/* ------------------------------------------------------------------------------------------
+ * Multi-GPU plumbing for ring attention between the processes of one node, one process per GPU.
+ * None of it has a counterpart in the reference (single GPU).  The attention kernels never
+ * read another GPU's memory: a K/V block is first copied into this GPU's own memory by a copy
+ * engine (fmha_peer_copy from an address obtained with fmha_ipc_open), flags tell the two sides
+ * when a buffer may be read or overwritten.  Everything is asynchronous on the stream given.
+ * ------------------------------------------------------------------------------------------ */
+
+/* CUDA IPC handle (64 bytes) of the allocation that holds `ptr`, and the offset of `ptr` in it;
+ * another process of the node turns the pair back into an address it can use as the source or
+ * the destination of fmha_peer_copy, or as a flag for fmha_peer_signal. */
+int fmha_ipc_export(const void* ptr, void* handle64, int64_t* offset);
+int fmha_ipc_open(const void* handle64, int64_t offset, void** ptr);
+/* Unmap an address obtained from fmha_ipc_open (pass the same offset). */
+int fmha_ipc_close(void* ptr, int64_t offset);
+
+/* bytes from src to dst, either of which may be another GPU's memory (copy engine, no SM). */
+int fmha_peer_copy(void* dst, const void* src, size_t bytes, void* stream);
+/* `rows` rows of `row_bytes` each, the rows `dst_pitch` / `src_pitch` bytes apart. */
+int fmha_peer_copy_2d(void* dst, size_t dst_pitch, const void* src, size_t src_pitch,
+                      size_t row_bytes, size_t rows, void* stream);
+
+/* word[0] += 1 and word[1] = the old word[0], on the stream: the iteration number the flags of
+ * one call carry, and the previous one.  Kept on the device so that a recorded sequence of
+ * these calls can be replayed. */
+int fmha_counter_bump(int32_t* word, void* stream);
+/* flags[i] <- *value for i < n (n <= 16), ordered after everything the stream did before; the
+ * flags may live in other GPUs' memory (fmha_ipc_open). */
+int fmha_peer_signal(int32_t* const* flags, int32_t n, const int32_t* value, void* stream);
+/* The stream waits until *flags[i] >= *value for every i < n (n <= 16; peers' fmha_peer_signal),
+ * at most timeout_ms (1..60000); a wait that runs out writes a non-zero code to *status (device
+ * memory, optional), which makes the attention kernels launched afterwards with that status
+ * word return at once. */
+int fmha_peer_wait(const int32_t* const* flags, int32_t n, const int32_t* value, int32_t* status,
+                   int32_t timeout_ms, void* stream);
+
+/* out (fp16 / bf16 with strides, (Z, rows, H, D)) = sum of n_parts (<= 16) fp32 buffers, each
+ * (Z, rows, H, D) contiguous, of which only the first rows_per_part[s] rows of every batch entry
+ * count (zig-zag ring attention: some ranks contribute to the first half of a block only). */
+int fmha_sum_partials(const float* const* parts, const int32_t* rows_per_part, int32_t n_parts,
+                      void* out, FmhaStrides out_strides, int32_t batch, int32_t heads, int32_t rows,
+                      int32_t head_dim, int32_t dtype, void* stream);
+
 /* Reference-shaped launchers: same argument meaning as include/fused_mha.h:1-6, dense fp16
  * (batch, m|n, head, k) tensors, except that the `max`/`sum` pair becomes one `lse` buffer,
  * the backward's `d_ptr` (fp16 D) is dropped in favour of a caller workspace, and a status

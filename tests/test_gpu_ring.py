@@ -111,41 +111,76 @@ def _free_port():
         return s.getsockname()[1]
 
 
-def _ring_worker(rank, world, port, causal, out_dir):
+def _ring_worker(rank, world, port, causal, out_dir, transport, Z, rows_per_rank, H, D, repeats):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
     torch.cuda.set_device(rank)
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
     try:
         from flash_attn_v100 import distributed as fd
+        from flash_attn_v100 import peer_ring
 
-        Z, N, H, D = 1, 512 * world, 4, 128
-        q, k, v, dout = oracle.make_inputs(Z, N, H, D, seed=9)
-        ql, kl, vl, dol = (fd.zigzag_split(t, rank, world).cuda().requires_grad_(i < 3)
-                           for i, t in enumerate((q, k, v, dout)))
-        out = fd.ring_flash_attn_func(ql, kl, vl, 0.1, causal)
-        out.backward(dol)
+        N = rows_per_rank * world
+        g = torch.Generator(device="cuda").manual_seed(9)  # every rank draws the same whole sequence
+        q, k, v, dout = (torch.randn((Z, N, H, D), generator=g, device="cuda", dtype=torch.float32).half()
+                         for _ in range(4))
+        ring = None
+        if transport == "peer":
+            ring = peer_ring.PeerRing((Z, rows_per_rank, H, D), torch.float16, torch.device("cuda", rank))
+        for _ in range(repeats):  # more than once: buffers, flags and iteration numbers are reused
+            ql, kl, vl, dol = (fd.zigzag_split(t, rank, world).requires_grad_(i < 3)
+                               for i, t in enumerate((q, k, v, dout)))
+            if ring is None:
+                out = fd.ring_flash_attn_func(ql, kl, vl, 0.1, causal)
+            else:
+                out = peer_ring.peer_ring_flash_attn_func(ring, ql, kl, vl, 0.1, causal)
+            out.backward(dol)
         torch.cuda.synchronize()
+        if ring is not None:
+            ring.check()
+            ring.close()
         torch.save(dict(out=out.detach().cpu(), dq=ql.grad.cpu(), dk=kl.grad.cpu(), dv=vl.grad.cpu()),
                    os.path.join(out_dir, f"rank{rank}.pt"))
     finally:
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("causal", [True, False])
-def test_ring_attention_on_gpus(causal, tmp_path):
-    """Zig-zag ring attention over NCCL send/recv against the oracle on the full sequence.
-    World size = visible GPUs (2, 4 or 8), world size 1 exercises the same code path without a
-    peer."""
-    from flash_attn_v100 import distributed as fd
+def _visible_world():
+    n = torch.cuda.device_count()
+    return 8 if n >= 8 else 4 if n >= 4 else 2 if n >= 2 else 1
 
-    world = torch.cuda.device_count()
-    world = 8 if world >= 8 else 4 if world >= 4 else 2 if world >= 2 else 1
-    mp.spawn(_ring_worker, args=(world, _free_port(), causal, str(tmp_path)), nprocs=world, join=True)
+
+def _run_ring(tmp_path, causal, transport, Z, rows_per_rank, H, D, repeats=1):
+    from flash_attn_v100 import distributed as fd
+    from oracle import attention_oracle_blockwise as blockwise
+
+    world = _visible_world()
+    mp.spawn(_ring_worker, args=(world, _free_port(), causal, str(tmp_path), transport, Z, rows_per_rank, H, D,
+                                 repeats), nprocs=world, join=True)
     parts = [torch.load(os.path.join(tmp_path, f"rank{r}.pt")) for r in range(world)]
-    Z, N, H, D = 1, 512 * world, 4, 128
-    q, k, v, dout = oracle.make_inputs(Z, N, H, D, seed=9)
-    ref_out, _, ref_dq, ref_dk, ref_dv = oracle.attention_fwd_bwd(q, k, v, dout, 0.1, causal)
+    N = rows_per_rank * world
+    g = torch.Generator(device="cuda").manual_seed(9)
+    q, k, v, dout = (torch.randn((Z, N, H, D), generator=g, device="cuda", dtype=torch.float32).half()
+                     for _ in range(4))
+    ref_out, _, ref_dq, ref_dk, ref_dv = (t.cpu() for t in blockwise.attention_fwd_bwd_blockwise(
+        q, k, v, dout, 0.1, causal))
     got = {key: fd.zigzag_merge([p[key] for p in parts]) for key in ("out", "dq", "dk", "dv")}
     assert oracle.max_abs(got["out"].float(), ref_out) <= helpers.TOL_O_MAX_ABS
     for key, ref in (("dq", ref_dq), ("dk", ref_dk), ("dv", ref_dv)):
         assert oracle.rel_l2(got[key].float(), ref) <= helpers.TOL_GRAD_REL_L2, key
+
+
+@pytest.mark.parametrize("causal", [True, False])
+@pytest.mark.parametrize("transport", ["nccl", "peer"])
+def test_ring_attention_on_gpus(transport, causal, tmp_path):
+    """Zig-zag ring attention against the oracle on the full sequence, with the K/V blocks passed
+    on by NCCL send/recv ("nccl") or pulled from their owners by the copy engines, gradients
+    pushed to theirs ("peer").  World size = visible GPUs (2, 4 or 8); world size 1 exercises the
+    same code path without a peer.  Two passes in a row: the second reuses every buffer and flag."""
+    _run_ring(tmp_path, causal, transport, Z=2, rows_per_rank=512, H=4, D=128, repeats=2)
+
+
+@pytest.mark.parametrize("transport", ["nccl", "peer"])
+def test_ring_attention_cfg5_shaped_shards(transport, tmp_path):
+    """Shards shaped like BASELINE config 5's at 8 GPUs (Z=1, H=32, D=128, 4096 rows per rank),
+    causal, checked against the blockwise oracle."""
+    _run_ring(tmp_path, True, transport, Z=1, rows_per_rank=4096, H=32, D=128)
