@@ -423,7 +423,11 @@ def measure_ring(args, torch, dist, world, rank, dev, steps=None):
     if world > 1:
         quiet = make_step(False, "peer")
         quiet()
-        ms_nocomm = median(timed_regions(quiet, steps, 3, torch, dist, world, dev))
+        qgraph = graph_of(quiet, torch) if graphed else None
+        t = torch.tensor([1 if qgraph is not None else 0], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MIN)
+        quiet_timed = qgraph.replay if bool(t.item()) else quiet
+        ms_nocomm = median(timed_regions(quiet_timed, steps, 3, torch, dist, world, dev))
         # for comparison: the same schedule with NCCL send/recv passing the blocks round
         nccl = make_step(True, "nccl")
         nccl()
@@ -464,7 +468,7 @@ def measure_ring(args, torch, dist, world, rank, dev, steps=None):
         res["ms_per_step_without_exchange"] = ms_nocomm
         res["exposed_comm_ms_per_hop"] = max(0.0, ms - ms_nocomm) / hops
         res["exposed_comm_frac_of_step"] = max(0.0, ms - ms_nocomm) / ms
-        res["ms_per_step_nccl_send_recv"] = ms_nccl
+        res["ms_per_step_nccl_send_recv"] = ms_nccl  # launches issued from Python, not replayed
     ring.close()
     return res
 
@@ -580,28 +584,36 @@ def run_ours(args):
     # ---- per-kernel timing, in place: the four kernels of a step in their normal order, an
     # event between each two (timed alone in a loop of its own a kernel runs at another SM clock
     # under the power cap, and the parts would not add up to the step); medians over the loop
-    iters = max(50, args.steps)
+    iters = args.kernel_iters
     both = cabi.FMHA_BWD_KEEP_WORKSPACE | cabi.FMHA_BWD_SKIP_DQ_CONVERT
-    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(5)] for _ in range(iters)]
-    torch.cuda.synchronize()
-    for e in ev:
-        e[0].record()
-        fwd()
-        e[1].record()
-        bwd(cabi.FMHA_BWD_PREPROCESS_ONLY)
-        e[2].record()
-        bwd(both)
-        e[3].record()
-        cabi.bwd_convert_dq(ws, dq, scale)
-        e[4].record()
-    torch.cuda.synchronize()
-    ms_fwd, ms_pre, ms_bwd_main, ms_cvt = (median([e[i].elapsed_time(e[i + 1]) for e in ev]) for i in range(4))
-    ms_parts = median([e[0].elapsed_time(e[4]) for e in ev])
+
+    def instrumented(n_iters):
+        ev = [[torch.cuda.Event(enable_timing=True) for _ in range(5)] for _ in range(n_iters)]
+        torch.cuda.synchronize()
+        for e in ev:
+            e[0].record()
+            fwd()
+            e[1].record()
+            bwd(cabi.FMHA_BWD_PREPROCESS_ONLY)
+            e[2].record()
+            bwd(both)
+            e[3].record()
+            cabi.bwd_convert_dq(ws, dq, scale)
+            e[4].record()
+        torch.cuda.synchronize()
+        return [median([e[i].elapsed_time(e[i + 1]) for e in ev]) for i in range(4)] + [
+            median([e[0].elapsed_time(e[4]) for e in ev])]
+
+    ms_fwd, ms_pre, ms_bwd_main, ms_cvt, ms_parts = instrumented(iters)
     ms_bwd = ms_pre + ms_bwd_main + ms_cvt
     # the same plain steps once more, right behind the instrumented loop: what the events between
     # the kernels cost, and how far the GPU has drifted since the timed regions
     regs_after = timed_regions(timed_step, args.steps, 3, torch, dist, world, dev)
     clocks_kernels = sampler.stop() if sampler else None
+    # and the same instrumented loop, short, after the GPU has been left idle for a second: the
+    # kernels at boost clocks, before the power cap bites (what a burst peak is measured like)
+    time.sleep(1.0)
+    idle = instrumented(8)
 
     # ---- end to end through the public API with host buffers.  Every step copies its own inputs
     # from pinned host memory and its own results back; the copies of neighbouring steps overlap
@@ -702,6 +714,13 @@ def run_ours(args):
                                                     "bwd_main": ms_bwd_main * mhz, "bwd_convert": ms_cvt * mhz,
                                                     "sm_mhz": mhz},
                 "frac_of_nominal_2250": {"fwd": f_fwd / ms_fwd / 1e9 / 2250.0, "bwd": f_bwd / ms_bwd / 1e9 / 2250.0},
+                "from_idle": {
+                    "what": "the same loop, 8 iterations, after one second of idle (boost clocks, no power cap yet)",
+                    "fwd_ms": idle[0], "bwd_preprocess_ms": idle[1], "bwd_main_ms": idle[2],
+                    "bwd_convert_ms": idle[3], "bwd_ms": idle[1] + idle[2] + idle[3],
+                    "fwd_frac_of_measured_peak": f_fwd / idle[0] / 1e9 / peaks["tflops"],
+                    "bwd_frac_of_measured_peak": f_bwd / (idle[1] + idle[2] + idle[3]) / 1e9 / peaks["tflops"],
+                    "bwd_main_frac_of_measured_peak": f_bwd / idle[2] / 1e9 / peaks["tflops"]},
             },
             "roofline": {"kernel": f"fmha_bwd_kernel<{D}> (fused dK/dV/dQ)",
                          "bound": "tensor",
@@ -737,6 +756,8 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-sharded", action="store_true",
                     help="skip the batch-split and ring-attention measurements that follow the headline")
+    ap.add_argument("--kernel-iters", type=int, default=50,
+                    help="iterations of the instrumented loop that times the kernels of a step one by one")
     ap.add_argument("--regions", type=int, default=15,
                     help="timed regions of --steps steps each, back to back; the median is reported")
     ap.add_argument("--graph", default="auto", choices=["auto", "on", "off"],

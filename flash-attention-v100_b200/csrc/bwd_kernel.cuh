@@ -462,7 +462,9 @@ __global__ void __launch_bounds__(512, 1)
       const bool tl = (r == 0);
       for (int n = 0; n < cnt; ++n) {
         if (tl) FMHA_TL(1, n, 0);
-        if (!mbar_wait(smem_u32(&bar_dq_full), n & 1, &abort_word, 14)) break;
+        // on a time-out keep going (like the compute groups): every later wait returns at once,
+        // and all 128 threads still meet at the named barriers
+        mbar_wait(smem_u32(&bar_dq_full), n & 1, &abort_word, 14);
         tc_fence_after();
         if (tl) FMHA_TL(1, n, 1);
         // The whole dQ row goes to registers first so that the dQ columns are released to the

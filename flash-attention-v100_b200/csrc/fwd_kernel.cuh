@@ -571,7 +571,15 @@ __global__ void __launch_bounds__(384, 1)
           const float m_new = (c >= 0.f) ? fmaxf(m_ref, mx) : fminf(m_ref, mx);
           // growth of the scaled maximum; NaN (inf - inf) compares false
           const bool need = (m_new - m_ref) * c > kRescaleThreshold;
-          if (__any_sync(0xffffffffu, need)) {
+          const bool any_need = __any_sync(0xffffffffu, need);
+#ifdef FMHA_COUNT_RESCALE
+          // debug builds: how often a warp takes the rescale path (word 0), per warp-step (word 1)
+          if (lane == 0 && p.timeline != nullptr) {
+            atomicAdd(reinterpret_cast<unsigned long long*>(p.timeline) + 1, 1ull);
+            if (any_need) atomicAdd(reinterpret_cast<unsigned long long*>(p.timeline), 1ull);
+          }
+#endif
+          if (any_need) {
             // O_t may still be accumulating the previous step: wait for that MMA.  The next
             // one is not issued before this thread has arrived on p_full.
             // That is known from the commit of S_t(hs+1), issued right behind it, or, for

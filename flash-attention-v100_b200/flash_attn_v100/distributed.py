@@ -64,6 +64,35 @@ def zigzag_merge(parts: List[torch.Tensor], dim: int = 1) -> torch.Tensor:
     return torch.cat(chunks, dim=dim)
 
 
+def ring_step_shapes(rank: int, world: int, causal: bool, rows: int):
+    """The dense block rank ``rank`` computes at every step of zig-zag ring attention over local
+    shards of ``rows`` rows: a list of ``(src, q_rows, kv_rows, causal_block)`` where ``src`` is
+    the rank that owns the K/V block, ``q_rows`` the slice of the local query rows that takes
+    part, ``kv_rows`` the slice of the block's rows that is needed, and ``causal_block`` whether
+    the block carries the ordinary causal mask (only the local one does)."""
+    half = rows // 2
+    full = slice(0, rows)
+    steps = []
+    for t in range(world):
+        src = (rank - t) % world
+        if t == 0:
+            steps.append((src, full, full, causal))
+        elif not causal:
+            steps.append((src, full, full, False))
+        elif src < rank:
+            steps.append((src, full, slice(0, half), False))  # all local Q x first half of the block
+        else:
+            steps.append((src, slice(half, rows), full, False))  # second half of local Q x whole block
+    return steps
+
+
+def ring_grad_rows(owner: int, world: int, causal: bool, rows: int):
+    """For the K/V block owned by ``owner``: how many of its rows (always a prefix) every source
+    rank contributes dK/dV for.  Ranks behind the owner in the sequence only ever see the first
+    half of the block."""
+    return [rows if (p == owner or not causal or p < owner) else rows // 2 for p in range(world)]
+
+
 # ----------------------------------------------------------------------------------------------
 # compute backend
 # ----------------------------------------------------------------------------------------------

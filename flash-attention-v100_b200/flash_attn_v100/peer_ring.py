@@ -53,6 +53,7 @@ class PeerRing:
         from flash_attn_v100 import cabi, distributed as fd
 
         self.cabi = cabi
+        self.fd = fd
         self.group = group
         self.world = dist.get_world_size(group)
         self.rank = dist.get_rank(group)
@@ -162,7 +163,8 @@ class PeerRing:
             else:
                 src_addr = side.export.data_ptr()  # measurements: same bytes, local source
             entry = rows * H * D * esize
-            if causal and src < self.rank:
+            kv_rows = self.fd.ring_step_shapes(self.rank, self.world, causal, rows)[t][2]
+            if kv_rows.stop < rows:
                 # only the first half of the block is needed
                 c.peer_copy_2d(buf.data_ptr(), entry, src_addr, entry, entry // 2, 2 * Z, self.pull_stream)
             else:
@@ -188,8 +190,8 @@ class PeerRing:
         if world > 1:
             self.pull_stream.wait_stream(cs)
             self._pull(side, "kv_f", 1, cur, causal, ev_free, ev_ready, exchange)
-        for t in range(world):
-            src = (rank - t) % world
+        rows = self.shape[1]
+        for t, (src, q_rows, kv_rows, causal_block) in enumerate(self.fd.ring_step_shapes(rank, world, causal, rows)):
             if t == 0:
                 kb, vb = k, v
             else:
@@ -198,21 +200,11 @@ class PeerRing:
             if t + 1 < world:
                 self._pull(side, "kv_f", t + 1, cur, causal, ev_free, ev_ready, exchange)
             last = t + 1 == world
-            ov = not last
-            if t == 0:
-                o_p, l_p = be.fwd(q, kb, vb, scale, causal, ov)
-                be.merge(o_acc, lse_acc, o_p, l_p, slice(0, None), out if last else None)
-            elif not causal:
-                o_p, l_p = be.fwd(q, kb, vb, scale, False, ov)
-                be.merge(o_acc, lse_acc, o_p, l_p, slice(0, None), out if last else None)
-            elif src < rank:
-                o_p, l_p = be.fwd(q, kb[:, :half], vb[:, :half], scale, False, ov)
-                be.merge(o_acc, lse_acc, o_p, l_p, slice(0, None), out if last else None)
-            else:
-                o_p, l_p = be.fwd(q[:, half:], kb, vb, scale, False, ov)
-                be.merge(o_acc, lse_acc, o_p, l_p, slice(half, None), None)
-                if last:
-                    out.copy_(o_acc)
+            whole_q = q_rows.start == 0
+            o_p, l_p = be.fwd(q[:, q_rows], kb[:, kv_rows], vb[:, kv_rows], scale, causal_block, not last)
+            be.merge(o_acc, lse_acc, o_p, l_p, q_rows, out if (last and whole_q) else None)
+            if last and not whole_q:
+                out.copy_(o_acc)
             if t >= 1:
                 ev_free[t % 2].record(cs)
         cs.wait_stream(self.pull_stream)  # nothing of this call is left on the side stream
@@ -248,8 +240,7 @@ class PeerRing:
             self._pull(side, "kv_b", 1, cur, causal, ev_free, ev_ready, exchange)
         slot_bytes = 2 * Z * rows * H * D * 4
         entry = rows * H * D * 4
-        for t in range(world):
-            src = (rank - t) % world
+        for t, (src, q_rows, kv_rows, causal_block) in enumerate(self.fd.ring_step_shapes(rank, world, causal, rows)):
             if t == 0:
                 kb, vb = k, v
                 target = self.slots[rank]  # my own contribution goes straight into my slot
@@ -259,24 +250,14 @@ class PeerRing:
                 target = self.part[t % 2]
                 if t >= 3:
                     cs.wait_event(ev_pushed[t % 2])  # the push of step t - 2 has read the buffer
-            first_half_only = causal and t > 0 and src < rank
-            if first_half_only:
-                target[:, :, :half].zero_()
-            else:
-                target.zero_()
+            first_half_only = kv_rows.stop < rows
+            target[:, :, kv_rows].zero_()
             if t + 1 < world:
                 self._pull(side, "kv_b", t + 1, cur, causal, ev_free, ev_ready, exchange)
-            dk_t, dv_t = target[0], target[1]
-            if t == 0:
-                be.bwd_step(state, "full", q, kb, vb, out, dout, lse, scale, causal, dk_t, dv_t)
-            elif not causal:
-                be.bwd_step(state, "full", q, kb, vb, out, dout, lse, scale, False, dk_t, dv_t)
-            elif src < rank:
-                be.bwd_step(state, "full", q, kb[:, :half], vb[:, :half], out, dout, lse, scale, False,
-                            dk_t[:, :half], dv_t[:, :half])
-            else:
-                be.bwd_step(state, "half", q[:, half:], kb, vb, out[:, half:], dout[:, half:], lse_half,
-                            scale, False, dk_t, dv_t)
+            whole_q = q_rows.start == 0
+            be.bwd_step(state, "full" if whole_q else "half", q[:, q_rows], kb[:, kv_rows], vb[:, kv_rows],
+                        out[:, q_rows], dout[:, q_rows], lse if whole_q else lse_half, scale, causal_block,
+                        target[0][:, kv_rows], target[1][:, kv_rows])
             if t >= 1:
                 ev_free[t % 2].record(cs)
                 ev_part[t % 2].record(cs)
@@ -295,7 +276,8 @@ class PeerRing:
         # every other rank's contribution to my block has arrived; add them up
         c.peer_wait([self._flag(rank, _GRAD_READY, p) for p in others], gcur, self.status, self.timeout_ms, cs)
         sources = list(range(world)) if exchange else [rank]
-        rows_per = [rows if (p == rank or not causal or p < rank) else half for p in sources]
+        all_rows = self.fd.ring_grad_rows(rank, world, causal, rows)
+        rows_per = [all_rows[p] for p in sources]
         dk, dv = torch.empty_like(k), torch.empty_like(v)
         base = self.slots.data_ptr()
         c.sum_partials([base + p * slot_bytes for p in sources], rows_per, dk, cs)

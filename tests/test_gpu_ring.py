@@ -105,6 +105,66 @@ def test_backward_in_three_separate_calls_matches_one_call():
     assert cabi.load_library().fmha_bwd_static_scratch(ctypes.byref(p), None) == 6
 
 
+def test_a_flag_wait_that_runs_out_sets_the_status_word_and_drains_the_kernels():
+    """The bounded wait for another GPU's flag, made to run out on one GPU: nothing ever sets the
+    flag, the wait gives up after its limit (200 ms here), writes its code to the status word, and
+    an attention kernel queued behind it with that status word returns without touching its
+    outputs.  With the word cleared and the flag set the same calls go through."""
+    import time
+
+    from flash_attn_v100 import cabi
+
+    flag = torch.zeros(1, dtype=torch.int32, device="cuda")
+    counter = torch.zeros(2, dtype=torch.int32, device="cuda")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    q, k, v, _ = (t.cuda() for t in oracle.make_inputs(1, 256, 2, 128, seed=2))
+    out_ok, _ = cabi.fwd(q, k, v, 0.1, True)
+    out = torch.full_like(q, 7.0)
+    cabi.counter_bump(counter)  # iteration 1: the flag would have to reach 1
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    cabi.peer_wait([flag.data_ptr()], counter.data_ptr(), status, 200)
+    cabi.fwd(q, k, v, 0.1, True, out=out, status=status)
+    torch.cuda.synchronize()
+    waited = time.perf_counter() - t0
+    assert 0.15 < waited < 5.0, waited
+    assert int(status.item()) == 0x200 and bool((out == 7.0).all())
+    # the producer's side of the hand-shake: a signal with the iteration number lets the wait pass
+    status.zero_()
+    cabi.peer_signal([flag.data_ptr()], counter.data_ptr())
+    t0 = time.perf_counter()
+    cabi.peer_wait([flag.data_ptr()], counter.data_ptr(), status, 200)
+    cabi.fwd(q, k, v, 0.1, True, out=out, status=status)
+    torch.cuda.synchronize()
+    assert time.perf_counter() - t0 < 0.15
+    assert int(status.item()) == 0 and torch.equal(out, out_ok)
+    assert counter.tolist() == [1, 0]
+    # invalid limits are refused on the host
+    lib = cabi.load_library()
+    import ctypes
+    arr = (ctypes.c_void_p * 1)(flag.data_ptr())
+    assert lib.fmha_peer_wait(arr, 1, ctypes.c_void_p(counter.data_ptr()), None, 0, None) == 3
+    assert lib.fmha_peer_wait(arr, 17, ctypes.c_void_p(counter.data_ptr()), None, 100, None) == 10
+
+
+def test_sum_partials_kernel():
+    """fmha_sum_partials: the owner's final dK / dV = the sum of the per-source fp32 partial
+    results, each counting only its first rows."""
+    from flash_attn_v100 import cabi
+
+    Z, rows, H, D = 2, 96, 3, 64
+    g = torch.Generator(device="cuda").manual_seed(3)
+    parts = [torch.randn((Z, rows, H, D), generator=g, device="cuda") for _ in range(5)]
+    counts = [96, 48, 96, 0, 48]
+    ref = torch.zeros((Z, rows, H, D), device="cuda")
+    for p, n in zip(parts, counts):
+        ref[:, :n] += p[:, :n]
+    for dtype in (torch.float16, torch.bfloat16):
+        out = torch.empty((Z, rows, H, D), dtype=dtype, device="cuda")
+        cabi.sum_partials([p.data_ptr() for p in parts], counts, out)
+        assert torch.equal(out, ref.to(dtype))
+
+
 def _free_port():
     with socket.socket() as s:
         s.bind(("127.0.0.1", 0))

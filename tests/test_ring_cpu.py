@@ -106,3 +106,59 @@ def test_zigzag_split_roundtrip_and_batch_shard():
         fd.zigzag_split(x, 0, 3)
     with pytest.raises(ValueError):
         fd.shard_batch(x, 0, 3)
+
+
+@pytest.mark.parametrize("causal", [True, False])
+@pytest.mark.parametrize("world", [1, 2, 3, 8])
+def test_pull_push_schedule_adds_up_to_full_attention(world, causal):
+    """The schedule of the copy-engine transport (``peer_ring.PeerRing``), which has no gloo
+    form because it moves data with CUDA IPC copies: every rank's per-step blocks
+    (``ring_step_shapes``) and the rows each source contributes to an owner's dK/dV
+    (``ring_grad_rows``) are played through for all ranks in one process, the oracle standing in
+    for the kernels and plain tensor copies for the transport.  Outputs merged through LSE and
+    gradients summed at the owners must equal attention over the whole sequence."""
+    from flash_attn_v100 import distributed as fd
+
+    Z, H, D = 1, 2, 64
+    rows = 32  # per rank
+    N = rows * world
+    q, k, v, dout = oracle.make_inputs(Z, N, H, D, seed=7)
+    ref_out, ref_lse, ref_dq, ref_dk, ref_dv = oracle.attention_fwd_bwd(q, k, v, dout, 0.2, causal)
+    shard = lambda t, r: fd.zigzag_split(t, r, world)
+    outs, lses, dqs = [], [], []
+    # slots[owner][source] = (dk, dv) partial, and how many rows of it the source wrote
+    slots = [[None] * world for _ in range(world)]
+    for r in range(world):
+        ql, dol = shard(q, r).float(), shard(dout, r).float()
+        o_acc = torch.zeros((Z, rows, H, D))
+        lse_acc = torch.full((Z, H, rows), float("-inf"))
+        plan = fd.ring_step_shapes(r, world, causal, rows)
+        assert [s[0] for s in plan] == [(r - t) % world for t in range(world)]
+        for src, q_rows, kv_rows, causal_block in plan:
+            kb, vb = shard(k, src)[:, kv_rows].float(), shard(v, src)[:, kv_rows].float()
+            o_p, l_p = oracle.attention_forward(ql[:, q_rows], kb, vb, 0.2, causal_block)
+            o, l = oracle.merge_partials(o_acc[:, q_rows], lse_acc[:, :, q_rows], o_p, l_p)
+            o_acc[:, q_rows], lse_acc[:, :, q_rows] = o, l
+        outs.append(o_acc), lses.append(lse_acc)
+        dq = torch.zeros((Z, rows, H, D))
+        for src, q_rows, kv_rows, causal_block in plan:
+            kb, vb = shard(k, src)[:, kv_rows].float(), shard(v, src)[:, kv_rows].float()
+            g = oracle.attention_backward(ql[:, q_rows], kb, vb, o_acc[:, q_rows], lse_acc[:, :, q_rows],
+                                          dol[:, q_rows], 0.2, causal_block)
+            dq[:, q_rows] += g[0]
+            slots[src][r] = (g[1], g[2], kv_rows.stop)
+        dqs.append(dq)
+    dks, dvs = [], []
+    for owner in range(world):
+        expect = fd.ring_grad_rows(owner, world, causal, rows)
+        dk, dv = torch.zeros((Z, rows, H, D)), torch.zeros((Z, rows, H, D))
+        for source in range(world):
+            part_dk, part_dv, n = slots[owner][source]
+            assert n == expect[source], (owner, source)  # what the owner adds is what the source sent
+            dk[:, :n] += part_dk
+            dv[:, :n] += part_dv
+        dks.append(dk), dvs.append(dv)
+    assert oracle.max_abs(fd.zigzag_merge(outs), ref_out) < 1e-5
+    assert oracle.max_abs(fd.zigzag_merge(lses, dim=2), ref_lse) < 1e-5
+    for got, ref in ((dqs, ref_dq), (dks, ref_dk), (dvs, ref_dv)):
+        assert oracle.max_abs(fd.zigzag_merge(got), ref) < 1e-4
