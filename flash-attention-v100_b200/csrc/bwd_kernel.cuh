@@ -44,6 +44,7 @@ struct BwdKernelParams {
   float* dk_accum;      // optional fp32 (Z, seqlen_k, H, D) contiguous
   float* dv_accum;      // optional
   long long accum_batch_stride;  // elements between batch entries of dk_accum / dv_accum
+  int accum_overwrite;  // 1: dK / dV REPLACE what dk_accum / dv_accum hold (FMHA_BWD_ACCUM_OVERWRITE)
   int heads, seqlen_q, seqlen_k, seqlen_q_pad;
   int num_kv_blocks;    // ceil(seqlen_k / 128)
   float scale, scale_log2;
@@ -527,21 +528,30 @@ __global__ void __launch_bounds__(512, 1)
       float* accum = is_dk ? p.dk_accum : p.dv_accum;
       const int kvi = kv0 + r;
       if (accum != nullptr) {
-        // ring attention: add this block's contribution into the travelling fp32 buffer
-        if (cnt > 0 && kvi < sk) {
-          float* dst = accum + (size_t)z * p.accum_batch_stride + ((size_t)kvi * p.heads + h) * D;
+        // ring attention: this block's contribution goes into an fp32 buffer, added to what is
+        // there or (accum_overwrite) in its place; then also rows nobody contributes to are
+        // written, as zeros, so that the buffer needs no clearing beforehand
+        const bool have = cnt > 0 && kvi < sk;                  // this thread's row has a result
+        const bool touch = kvi < p.seqlen_k && (have || p.accum_overwrite != 0);
+        float* dst = accum + (size_t)z * p.accum_batch_stride + ((size_t)kvi * p.heads + h) * D;
 #pragma unroll
-          for (int cc = 0; cc < D / 32; ++cc) {
-            uint32_t a[32];
+        for (int cc = 0; cc < D / 32; ++cc) {
+          uint32_t a[32];
+          if (cnt > 0) {  // uniform over the CTA: the tensor-memory load is a warp-wide instruction
             tmem_ld32(tAcc + cc * 32, a);
             tmem_wait_ld();
+          }
+          if (touch) {
 #pragma unroll
             for (int i = 0; i < 32; i += 4) {
-              float4 cur = *reinterpret_cast<float4*>(dst + cc * 32 + i);
-              cur.x += __uint_as_float(a[i + 0]) * mul;
-              cur.y += __uint_as_float(a[i + 1]) * mul;
-              cur.z += __uint_as_float(a[i + 2]) * mul;
-              cur.w += __uint_as_float(a[i + 3]) * mul;
+              float4 cur = make_float4(0.f, 0.f, 0.f, 0.f);
+              if (p.accum_overwrite == 0) cur = *reinterpret_cast<float4*>(dst + cc * 32 + i);
+              if (have) {
+                cur.x += __uint_as_float(a[i + 0]) * mul;
+                cur.y += __uint_as_float(a[i + 1]) * mul;
+                cur.z += __uint_as_float(a[i + 2]) * mul;
+                cur.w += __uint_as_float(a[i + 3]) * mul;
+              }
               *reinterpret_cast<float4*>(dst + cc * 32 + i) = cur;
             }
           }

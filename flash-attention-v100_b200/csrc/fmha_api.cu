@@ -221,6 +221,7 @@ int launch_bwd(const FmhaBwdParams* p, const BwdWorkspace& w, cudaStream_t strea
     kp.dv_accum = p->dv_accum;
     kp.accum_batch_stride =
         p->accum_batch_stride > 0 ? p->accum_batch_stride : (long long)Nk * H * D;
+    kp.accum_overwrite = (p->flags & FMHA_BWD_ACCUM_OVERWRITE) ? 1 : 0;
     kp.heads = H;
     kp.seqlen_q = Nq;
     kp.seqlen_k = Nk;

@@ -24,6 +24,7 @@ FMHA_BWD_KEEP_WORKSPACE = 1
 FMHA_BWD_SKIP_DQ_CONVERT = 2
 FMHA_BWD_PREPROCESS_ONLY = 4
 FMHA_BWD_DETERMINISTIC = 8
+FMHA_BWD_ACCUM_OVERWRITE = 16
 FMHA_DTYPE_FP16 = 0
 FMHA_DTYPE_BF16 = 1
 

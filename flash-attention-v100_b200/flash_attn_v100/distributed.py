@@ -143,11 +143,14 @@ class CudaBackend:
             "full_used": False, "half_used": False,
         }
 
-    def bwd_step(self, state, which, q, k, v, o, dout, lse, scale, causal, dk_acc, dv_acc):
+    def bwd_step(self, state, which, q, k, v, o, dout, lse, scale, causal, dk_acc, dv_acc,
+                 overwrite: bool = False):
         """Accumulate this block's dQ into the workspace ``which`` ('full' or 'half' query rows)
-        and its dK/dV into the travelling fp32 buffers."""
+        and its dK/dV into the fp32 buffers (``overwrite``: in place of what they hold)."""
         c = self.cabi
         flags = c.FMHA_BWD_SKIP_DQ_CONVERT | (c.FMHA_BWD_KEEP_WORKSPACE if state[which + "_used"] else 0)
+        if overwrite:
+            flags |= c.FMHA_BWD_ACCUM_OVERWRITE
         c.bwd(q, k, v, o, dout, lse, scale, causal, dq=None, dk_accum=dk_acc, dv_accum=dv_acc,
               workspace=state[which], flags=flags, status=self.status)
         state[which + "_used"] = True

@@ -251,13 +251,12 @@ class PeerRing:
                 if t >= 3:
                     cs.wait_event(ev_pushed[t % 2])  # the push of step t - 2 has read the buffer
             first_half_only = kv_rows.stop < rows
-            target[:, :, kv_rows].zero_()
             if t + 1 < world:
                 self._pull(side, "kv_b", t + 1, cur, causal, ev_free, ev_ready, exchange)
             whole_q = q_rows.start == 0
             be.bwd_step(state, "full" if whole_q else "half", q[:, q_rows], kb[:, kv_rows], vb[:, kv_rows],
                         out[:, q_rows], dout[:, q_rows], lse if whole_q else lse_half, scale, causal_block,
-                        target[0][:, kv_rows], target[1][:, kv_rows])
+                        target[0][:, kv_rows], target[1][:, kv_rows], overwrite=True)
             if t >= 1:
                 ev_free[t % 2].record(cs)
                 ev_part[t % 2].record(cs)

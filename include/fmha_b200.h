@@ -129,7 +129,8 @@ typedef struct {
   /* ring attention: 0 = normal (compute D, zero the fp32 dQ accumulator, convert dQ to fp16);
    * bit 0 set = do not zero the dQ accumulator nor recompute D (workspace carries both over
    * from an earlier call); bit 1 set = do not convert dQ (a later call will); bit 2 set = run
-   * the preprocess step only; bit 3 set = deterministic dQ (see FMHA_BWD_DETERMINISTIC). */
+   * the preprocess step only; bit 3 set = deterministic dQ (see FMHA_BWD_DETERMINISTIC); bit 4 set =
+   * dk_accum / dv_accum are overwritten, not added into (FMHA_BWD_ACCUM_OVERWRITE). */
   int32_t flags;
   int32_t* status;
   int32_t dtype; /* FMHA_DTYPE_FP16 (0) or FMHA_DTYPE_BF16 */
@@ -154,6 +155,11 @@ typedef struct {
  * such mode.  The order words live in the workspace (fmha_bwd_workspace_bytes accounts for
  * them) and are cleared by every call that carries the flag. */
 #define FMHA_BWD_DETERMINISTIC 8
+/* dk_accum / dv_accum are WRITTEN instead of added into: the fp32 dK / dV of this call replace
+ * what the buffers hold, every row of the seqlen_k rows included (zeros where no query row
+ * sees a key), so the caller need not clear them first (ring attention: the partial result of
+ * one step, sent to the block's owner). */
+#define FMHA_BWD_ACCUM_OVERWRITE 16
 
 /* Forward: O = softmax(scale * Q K^T [+ causal mask]) V and LSE.
  * Replaces fused_mha_forward (include/fused_mha.h:1-2, kernel/fused_mha_kernel.cu:891-902). */

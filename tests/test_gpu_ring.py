@@ -79,6 +79,29 @@ def test_backward_accumulates_over_key_blocks_into_fp32_buffers():
     helpers.check_against_oracle(got, ref, "blockwise backward")
 
 
+def test_backward_overwrites_the_fp32_buffers_when_asked():
+    """FMHA_BWD_ACCUM_OVERWRITE: dK / dV replace what dk_accum / dv_accum hold (NaN here), rows that
+    no query row sees are written as zeros, so the buffers of ring attention's partial results
+    need no clearing.  Rectangular causal case: the keys beyond the last query row are unseen."""
+    from flash_attn_v100 import cabi
+
+    for (Z, Nq, Nk, H, D, causal) in ((2, 128, 416, 2, 64, True), (1, 256, 256, 3, 128, False)):
+        q, k, v, dout = oracle.make_inputs(Z, Nq, H, D, seed=16, n_k=Nk)
+        ref = oracle.attention_fwd_bwd(q, k, v, dout, 0.12, causal)
+        qd, kd, vd, dod = q.cuda(), k.cuda(), v.cuda(), dout.cuda()
+        out, lse = cabi.fwd(qd, kd, vd, 0.12, causal)
+        # a row range of a larger buffer, like the half-block steps of the ring
+        big_k = torch.full((Z, Nk + 64, H, D), float("nan"), dtype=torch.float32, device="cuda")
+        big_v = torch.full_like(big_k, float("nan"))
+        dq, _, _ = cabi.bwd(qd, kd, vd, out, dod, lse, 0.12, causal, dk_accum=big_k[:, :Nk], dv_accum=big_v[:, :Nk],
+                            flags=cabi.FMHA_BWD_ACCUM_OVERWRITE)
+        assert torch.isnan(big_k[:, Nk:]).all() and torch.isnan(big_v[:, Nk:]).all()  # untouched beyond
+        got = (out.cpu(), lse.cpu(), dq.cpu(), big_k[:, :Nk].cpu(), big_v[:, :Nk].cpu())
+        helpers.check_against_oracle(got, ref, f"overwrite Nq{Nq} Nk{Nk} D{D} causal={causal}")
+        if causal:
+            assert not big_k[:, Nq:Nk].any() and not big_v[:, Nq:Nk].any()  # unseen keys: zeros
+
+
 def test_backward_in_three_separate_calls_matches_one_call():
     """Preprocess only, then the fused kernel on the kept workspace, then the dQ conversion: the
     same bits as one fmha_bwd call (dK/dV bitwise, dQ up to the order of its fp32 additions)."""
