@@ -386,7 +386,14 @@ def measure_ring(args, torch, dist, world, rank, dev, steps=None):
     from flash_attn_v100 import peer_ring
 
     be = fd.CudaBackend()
-    ring = peer_ring.PeerRing((Z, 2 * c, H, D), torch.float16, dev)
+    # the copy-engine transport needs CUDA IPC between the ranks; where that is not to be had the
+    # NCCL send/recv ring is measured instead (the set-up fails or succeeds on all ranks together)
+    try:
+        ring = peer_ring.PeerRing((Z, 2 * c, H, D), torch.float16, dev)
+        product = "peer"
+    except RuntimeError as exc:
+        print(f"copy-engine ring unavailable ({exc}); measuring the NCCL send/recv ring", file=sys.stderr)
+        ring, product = None, "nccl"
     res_holder = {}
 
     def make_step(comm, transport):
@@ -405,10 +412,10 @@ def measure_ring(args, torch, dist, world, rank, dev, steps=None):
     # be what is timed: the whole step (kernels, copies, flag kernels, events on three streams) is
     # captured in a CUDA graph once and replayed; the flags carry an iteration number that lives
     # on the device, so a replay is a new iteration.
-    step = make_step(True, "peer")
+    step = make_step(True, product)
     for _ in range(3):
         step()
-    graph = graph_of(step, torch) if args.graph != "off" else None
+    graph = graph_of(step, torch) if (args.graph != "off" and product == "peer") else None
     graphed = graph is not None
     t = torch.tensor([1 if graphed else 0], device=dev)
     if world > 1:
@@ -418,10 +425,11 @@ def measure_ring(args, torch, dist, world, rank, dev, steps=None):
     regs = timed_regions(timed, steps, 3, torch, dist, world, dev)
     ms = median(regs)
     got = res_holder["last"]
-    ring.check()
+    if ring is not None:
+        ring.check()
     ms_nocomm = ms_nccl = None
     if world > 1:
-        quiet = make_step(False, "peer")
+        quiet = make_step(False, product)
         quiet()
         qgraph = graph_of(quiet, torch) if graphed else None
         t = torch.tensor([1 if qgraph is not None else 0], device=dev)
@@ -429,9 +437,12 @@ def measure_ring(args, torch, dist, world, rank, dev, steps=None):
         quiet_timed = qgraph.replay if bool(t.item()) else quiet
         ms_nocomm = median(timed_regions(quiet_timed, steps, 3, torch, dist, world, dev))
         # for comparison: the same schedule with NCCL send/recv passing the blocks round
-        nccl = make_step(True, "nccl")
-        nccl()
-        ms_nccl = median(timed_regions(nccl, steps, 2, torch, dist, world, dev))
+        if product == "peer":
+            nccl = make_step(True, "nccl")
+            nccl()
+            ms_nccl = median(timed_regions(nccl, steps, 2, torch, dist, world, dev))
+        else:
+            ms_nccl = ms
 
     # parity on two sampled heads: gather them from every rank, rebuild the whole sequence, run
     # the oracle on it, compare this rank's shard
@@ -458,8 +469,9 @@ def measure_ring(args, torch, dist, world, rank, dev, steps=None):
            "causal": causal, "value": fl / (ms * 1e-3) / 1e12, "unit": "TFLOPS", "ms_per_step": ms,
            "regions": region_stats(regs), "steps": steps,
            "per_gpu_tflops": fl / (ms * 1e-3) / 1e12 / world,
-           "parallelism": f"zig-zag ring attention x{world} (K/V pulled from their owners and dK/dV pushed to "
-                          "theirs by the copy engines over NVLink; flags in peer memory)",
+           "parallelism": f"zig-zag ring attention x{world} (" + (
+               "K/V pulled from their owners and dK/dV pushed to theirs by the copy engines over NVLink; "
+               "flags in peer memory" if product == "peer" else "NCCL send/recv") + ")",
            "launch": "CUDA graph replay of one ring step" if graphed else "launches issued from Python",
            "rows_per_gpu": 2 * c, "kv_bytes_per_hop": kv_hop, "dkdv_bytes_per_hop": 2 * kv_hop,
            "parity": parity}
@@ -469,7 +481,8 @@ def measure_ring(args, torch, dist, world, rank, dev, steps=None):
         res["exposed_comm_ms_per_hop"] = max(0.0, ms - ms_nocomm) / hops
         res["exposed_comm_frac_of_step"] = max(0.0, ms - ms_nocomm) / ms
         res["ms_per_step_nccl_send_recv"] = ms_nccl  # launches issued from Python, not replayed
-    ring.close()
+    if ring is not None:
+        ring.close()
     return res
 
 
@@ -722,12 +735,17 @@ def run_ours(args):
                     "bwd_frac_of_measured_peak": f_bwd / (idle[1] + idle[2] + idle[3]) / 1e9 / peaks["tflops"],
                     "bwd_main_frac_of_measured_peak": f_bwd / idle[2] / 1e9 / peaks["tflops"]},
             },
-            "roofline": {"kernel": f"fmha_bwd_kernel<{D}> (fused dK/dV/dQ)",
-                         "bound": "tensor",
-                         "achieved": achieved, "peak": peaks["tflops"], "unit": "TFLOP/s",
-                         "frac": achieved / peaks["tflops"], "peak_source": peaks["source"] + " (burst)",
-                         "frac_of_sustained_peak": achieved / peaks["tflops_sustained"],
-                         "timed": "in place inside the step, steady state (the sustained peak is the like-for-like denominator)",
+            # the fused backward kernel is timed inside a long back-to-back loop, under the power
+            # cap: the like-for-like denominator is the SUSTAINED measured peak; the burst figure
+            # (and the kernel's own time from an idle GPU) are given beside it
+            "roofline": {"kernel": f"fmha_bwd_kernel<{D}> (fused dK/dV/dQ)", "bound": "tensor",
+                         "achieved": achieved, "peak": peaks["tflops_sustained"], "unit": "TFLOP/s",
+                         "frac": achieved / peaks["tflops_sustained"],
+                         "peak_source": peaks["source"] + " (sustained: the kernel is timed inside a long loop)",
+                         "frac_of_burst_peak": achieved / peaks["tflops"], "burst_peak": peaks["tflops"],
+                         "from_idle": {"achieved": f_bwd / idle[2] / 1e9,
+                                       "frac_of_burst_peak": f_bwd / idle[2] / 1e9 / peaks["tflops"]},
+                         "algorithmic_flops_per_launch": f_bwd,
                          "traffic": recorded_traffic(kernel_file, args.workload)},
             "e2e": {"value": world * (f_fwd + f_bwd) / (ms_e2e * 1e-3) / 1e12, "unit": "TFLOPS",
                     "ms_per_step": ms_e2e, "h2d_bytes_per_step": 4 * tensor_bytes,

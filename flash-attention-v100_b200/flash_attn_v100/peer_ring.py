@@ -80,28 +80,48 @@ class PeerRing:
             self.pull_stream = torch.cuda.Stream(device=self.device, priority=-1)
             self.push_stream = torch.cuda.Stream(device=self.device, priority=-1)
             torch.cuda.synchronize(self.device)
-        # ---- exchange the addresses (CUDA IPC): my export buffers, slots and flags for every peer
-        mine = {name: cabi.ipc_export(t) for name, t in (
-            ("kv_f", self.fwd_side.export), ("kv_b", self.bwd_side.export), ("slots", self.slots),
-            ("flags", self.flags))}
+        # ---- exchange the addresses (CUDA IPC): my export buffers, slots and flags for every peer.
+        # Every rank takes part in every collective of this set-up whether or not its own local
+        # steps worked, and all ranks agree on the outcome, so that a failure on one rank (IPC not
+        # permitted, no peer access) is an exception on all of them and never a hang.
+        def all_ok(ok: bool) -> bool:
+            t = torch.tensor([1 if ok else 0], dtype=torch.int32, device=self.device)
+            dist.all_reduce(t, op=dist.ReduceOp.MIN, group=group)
+            return bool(t.item())
+
+        self._opened = {}
+        mine, error = None, None
+        try:
+            mine = {name: cabi.ipc_export(t) for name, t in (
+                ("kv_f", self.fwd_side.export), ("kv_b", self.bwd_side.export), ("slots", self.slots),
+                ("flags", self.flags))}
+        except Exception as exc:  # noqa: BLE001 - reported on every rank below
+            error = exc
+        exported = all_ok(error is None)
         everyone = [None] * self.world
         dist.all_gather_object(everyone, mine, group=group)
-        self._opened = {}
         own = {"kv_f": self.fwd_side.export.data_ptr(), "kv_b": self.bwd_side.export.data_ptr(),
                "slots": self.slots.data_ptr(), "flags": self.flags.data_ptr()}
         self.peer = []
-        with torch.cuda.device(self.device):
-            for p in range(self.world):
-                if p == self.rank:
-                    self.peer.append(own)
-                    continue
-                entry = {}
-                for name, (handle, offset) in everyone[p].items():
-                    key = (p, handle)
-                    if key not in self._opened:
-                        self._opened[key] = cabi.ipc_open(handle, 0)
-                    entry[name] = self._opened[key] + offset
-                self.peer.append(entry)
+        if exported:
+            try:
+                with torch.cuda.device(self.device):
+                    for p in range(self.world):
+                        if p == self.rank:
+                            self.peer.append(own)
+                            continue
+                        entry = {}
+                        for name, (handle, offset) in everyone[p].items():
+                            key = (p, handle)
+                            if key not in self._opened:
+                                self._opened[key] = cabi.ipc_open(handle, 0)
+                            entry[name] = self._opened[key] + offset
+                        self.peer.append(entry)
+            except Exception as exc:  # noqa: BLE001
+                error = exc
+        if not all_ok(exported and error is None):
+            raise RuntimeError("PeerRing: CUDA IPC set-up failed on at least one rank"
+                               + (f" (here: {error})" if error is not None else ""))
         dist.barrier(group=group)
 
     # ---- addresses

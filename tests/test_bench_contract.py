@@ -38,7 +38,7 @@ def test_our_arm_line_has_roofline_baseline_e2e_and_clocks():
     assert d["n_gpus"] == 1 and d["steps"] == 3 and d["gpu_launches"] == 12
     r = d["roofline"]
     assert r["bound"] == "tensor" and r["unit"] == "TFLOP/s" and 0 < r["frac"] < 1.2
-    assert abs(r["frac"] - r["achieved"] / r["peak"]) < 1e-9
+    assert abs(r["frac"] - r["achieved"] / r["peak"]) < 1e-9 and r["frac_of_burst_peak"] <= r["frac"]
     assert d["cpu_baseline"]["kind"] == "port" and d["cpu_baseline"]["value"] > 0
     assert d["e2e"]["value"] > 0 and d["e2e"]["h2d_bytes_per_step"] > 0
     assert {"sm_mhz", "sm_max_mhz", "reasons"} <= set(d["clocks"])

@@ -24,6 +24,20 @@ def test_library_exports_every_declared_symbol(built_library):
         assert hasattr(lib, n), f"{n} declared in include/fmha_b200.h but not exported"
 
 
+def test_header_is_plain_c(tmp_path):
+    """The boundary is a C ABI: the header compiles as C99 (no C++ needed on the host side) and
+    the parameter structs can be zero-initialised, which selects every default."""
+    import subprocess
+
+    src = tmp_path / "use_header.c"
+    src.write_text('#include "fmha_b200.h"\n'
+                   "int main(void) { FmhaFwdParams f = {0}; FmhaBwdParams b = {0};\n"
+                   "  int (*fwd)(const FmhaFwdParams*, void*) = fmha_fwd; (void)fwd;\n"
+                   "  return f.dtype + b.flags; }\n")
+    subprocess.run(["gcc", "-std=c99", "-Wall", "-Wextra", "-pedantic", "-Werror", "-fsyntax-only",
+                    "-I", os.path.join(ROOT, "include"), str(src)], check=True)
+
+
 def test_binding_lists_the_same_symbols(built_library):
     from flash_attn_v100 import cabi
 
