@@ -426,7 +426,15 @@ def measure_ring(args, torch, dist, world, rank, dev, steps=None):
     ms = median(regs)
     got = res_holder["last"]
     if ring is not None:
-        ring.check()
+        # a bounded wait for a peer's flag that ran out leaves a code in the status word of the
+        # rank it happened on; all ranks agree on the outcome before any of them gives up
+        st = ring.status.clone()
+        if world > 1:
+            dist.all_reduce(st, op=dist.ReduceOp.MAX)
+        if int(st.item()) != 0:
+            ring.close()
+            return {"workload": "cfg5_ring_causal",
+                    "error": f"a bounded wait for a peer's flag gave up (status {int(st.item()):#x}); no number reported"}
     ms_nocomm = ms_nccl = None
     if world > 1:
         quiet = make_step(False, product)
@@ -666,7 +674,9 @@ def run_ours(args):
     torch.cuda.synchronize()
     if world > 1:
         dist.barrier()
-    e2e_iters = max(4, min(args.steps, 10))
+    # enough steps that filling and draining the three-stage pipeline (one step without an
+    # upload beside it, one without a download) is a few per cent of the region
+    e2e_iters = max(30, args.steps)
     ms_e2e = time_events(lambda: e2e_run(e2e_iters), 1, torch) / e2e_iters
     t = torch.tensor([ms_e2e], dtype=torch.float64, device=dev)
     if world > 1:

@@ -47,6 +47,9 @@ struct BwdKernelParams {
   int accum_overwrite;  // 1: dK / dV REPLACE what dk_accum / dv_accum hold (FMHA_BWD_ACCUM_OVERWRITE)
   int heads, seqlen_q, seqlen_k, seqlen_q_pad;
   int num_kv_blocks;    // ceil(seqlen_k / 128)
+  int num_heads_total;  // batch * heads
+  int head_group;       // heads whose CTAs are interleaved in the grid (>= 1)
+  int rotate_start;     // 1: CTA kb starts on its (kb mod count)-th query tile (no causal mask)
   float scale, scale_log2;
   int causal, causal_shift;
   int* status;
@@ -126,10 +129,18 @@ __global__ void __launch_bounds__(512, 1)
   const uint32_t stg_smem = ds_smem + T::kDsBytes;                  // dQ staging, 2 x 16 KB
   const uint32_t stat_smem = stg_smem + T::kStageBytes;             // statistics
 
-  // ---- coordinates: consecutive CTAs = same head; early KV tiles (most query tiles) first
+  // ---- coordinates.  Heads are taken in groups of head_group; within a group the CTAs are
+  // ordered by KV tile first (early KV tiles see the most query tiles under a causal mask and
+  // live longest), head second: the CTAs running at any time still belong to a handful of heads
+  // (their Q / dO tiles and dQ accumulators stay in L2), and what is dispatched last, at the end
+  // of a group and of the grid, are the short CTAs.  head_group = 1: all CTAs of a head in a row.
   const int nkb = p.num_kv_blocks;
-  const int zh = blockIdx.x / nkb;
-  const int kb = blockIdx.x % nkb;
+  const int per_group = p.head_group * nkb;
+  const int group = blockIdx.x / per_group;
+  const int within = blockIdx.x % per_group;
+  const int heads_here = min(p.head_group, p.num_heads_total - group * p.head_group);
+  const int zh = group * p.head_group + within % heads_here;
+  const int kb = within / heads_here;
   const int z = zh / p.heads;
   const int h = zh % p.heads;
   const int kv0 = kb * T::kBlock;
@@ -146,6 +157,16 @@ __global__ void __launch_bounds__(512, 1)
   }
   // query tiles this CTA walks (may be 0; a KV tile that is all padding walks none)
   const int cnt = kv0 < sk ? nq_tiles - i_begin : 0;
+  // The n-th query tile this CTA visits.  Under a causal mask the CTAs of a head start on
+  // different tiles by themselves (tile_begin grows with kb).  Without one they would all start
+  // on tile 0 and add into the same dQ tile at the same time, step after step; rotate_start lets
+  // CTA kb start on tile kb instead (wrapping round), so that the reduce-adds of a head's CTAs
+  // go to different lines of the L2.
+  const int rot = (p.rotate_start != 0 && cnt > 1) ? kb % cnt : 0;
+  auto tile_of = [&](int n) {
+    const int t = n + rot;
+    return i_begin + (t >= cnt ? t - cnt : t);
+  };
 
   if (threadIdx.x == 0) {
     mbar_init(smem_u32(&bar_kv_full), 1);
@@ -201,7 +222,7 @@ __global__ void __launch_bounds__(512, 1)
       for (int n = 0; n < cnt; ++n) {
         const int st = n % T::kQStages;
         const int round = n / T::kQStages;
-        const int row = (i_begin + n) * T::kBlock;
+        const int row = tile_of(n) * T::kBlock;
         if (round > 0 &&
             !mbar_wait_warp(smem_u32(&bar_q_empty[st]), (round - 1) & 1, &abort_word, 1))
           break;
@@ -334,15 +355,15 @@ __global__ void __launch_bounds__(512, 1)
       const uint32_t tDP = tmem_base + lane_addr + T::kColDP + cg * 64;
       // statistics: thread ct < 128 carries lse2[q0 + ct], the others delta[q0 + ct - 128]
       const float* stat_src = (ct < 128 ? p.lse2 : p.delta) + stat_base + (ct & 127);
-      float stat_next = (cnt > 0) ? __ldg(stat_src + (size_t)i_begin * T::kBlock) : 0.f;
+      float stat_next = (cnt > 0) ? __ldg(stat_src + (size_t)tile_of(0) * T::kBlock) : 0.f;
       const bool tl = (threadIdx.x == 0);
 
       for (int n = 0; n < cnt; ++n) {
-        const int qbase = (i_begin + n) * T::kBlock;
+        const int qbase = tile_of(n) * T::kBlock;
         const uint32_t sb = stat_smem;  // lse2 at [0, 512), delta at [512, 1024)
         named_bar_sync(3, 256);  // every thread is done reading the previous tile's values
         asm volatile("st.shared.f32 [%0], %1;" ::"r"(sb + ct * 4), "f"(stat_next) : "memory");
-        if (n + 1 < cnt) stat_next = __ldg(stat_src + (size_t)(i_begin + n + 1) * T::kBlock);
+        if (n + 1 < cnt) stat_next = __ldg(stat_src + (size_t)tile_of(n + 1) * T::kBlock);
         named_bar_sync(4, 256);  // this tile's values are visible
 
         // first visible query column of this thread's half (>= 64: none)
@@ -494,14 +515,14 @@ __global__ void __launch_bounds__(512, 1)
           if (r == 0) {
             int* order_word = p.dq_order == nullptr
                                   ? nullptr
-                                  : p.dq_order + (size_t)zh * (p.seqlen_q_pad / T::kBlock) + (i_begin + n);
+                                  : p.dq_order + (size_t)zh * (p.seqlen_q_pad / T::kBlock) + tile_of(n);
             if (order_word != nullptr && cc == 0) {
               // the KV tiles before this one have added their share of this query tile
               global_flag_wait(order_word, kb, &abort_word, p.status, 17);
               fence_proxy_async_all();
             }
             tma_reduce_add_4d(&tm_dqacc, stg_smem + (cc & 1) * 16384, cc * 32,
-                              (i_begin + n) * T::kBlock, h, z);
+                              tile_of(n) * T::kBlock, h, z);
             tma_commit_group();
             if (order_word != nullptr && cc == D / 32 - 1) {
               tma_wait_group<0>();  // the adds have been performed, not just read from shared memory

@@ -10,6 +10,7 @@
 #include <atomic>
 #include <cmath>
 #include <cstdint>
+#include <cstdlib>
 #include <cstring>
 #include <type_traits>
 
@@ -113,6 +114,29 @@ int check_common(int batch, int heads, int seqlen_q, int seqlen_k, int head_dim,
 fmha::Strides3 to3(const FmhaStrides& s) { return fmha::Strides3{s.batch, s.row, s.head}; }
 
 int round_up_128(int x) { return (x + 127) / 128 * 128; }
+
+// FMHA_BWD_ROTATE=0/1 overrides the default (tuning experiments)
+bool bwd_rotate_start() {
+  static const bool on = []() {
+    const char* e = std::getenv("FMHA_BWD_ROTATE");
+    return e != nullptr ? std::atoi(e) != 0 : false;
+  }();
+  return on;
+}
+
+// Heads whose CTAs are interleaved in the backward grid (see the coordinates in bwd_kernel.cuh).
+// 8 for up to 32 KV tiles per head: measured 3.3 % on the fused kernel at N = 2048 causal (0.809 ->
+// 0.782 ms; 4: 0.794, 16: 0.779), the last CTAs of a group and of the grid being the short ones.
+// Longer sequences keep one head at a time: their grids are long, and eight heads' query tiles
+// would not share the L2.  FMHA_BWD_HEAD_GROUP overrides (tuning experiments).
+int bwd_head_group(int num_kv_blocks) {
+  static const int forced = []() {
+    const char* e = std::getenv("FMHA_BWD_HEAD_GROUP");
+    return e != nullptr ? std::atoi(e) : 0;
+  }();
+  if (forced >= 1) return forced;
+  return num_kv_blocks <= 32 ? 8 : 1;
+}
 
 struct BwdWorkspace {
   float* dq_accum;
@@ -227,6 +251,10 @@ int launch_bwd(const FmhaBwdParams* p, const BwdWorkspace& w, cudaStream_t strea
     kp.seqlen_k = Nk;
     kp.seqlen_q_pad = Nq_pad;
     kp.num_kv_blocks = (Nk + 127) / 128;
+    kp.num_heads_total = Z * H;
+    kp.head_group = bwd_head_group(kp.num_kv_blocks);
+    // not with the ordered reduction, whose CTAs take their turns in the order of the KV tiles
+    kp.rotate_start = (!p->causal && !(p->flags & FMHA_BWD_DETERMINISTIC) && bwd_rotate_start()) ? 1 : 0;
     kp.scale = p->scale;
     kp.scale_log2 = p->scale * 1.4426950408889634f;
     kp.causal = p->causal ? 1 : 0;

@@ -162,3 +162,36 @@ def test_pull_push_schedule_adds_up_to_full_attention(world, causal):
     assert oracle.max_abs(fd.zigzag_merge(lses, dim=2), ref_lse) < 1e-5
     for got, ref in ((dqs, ref_dq), (dks, ref_dk), (dvs, ref_dv)):
         assert oracle.max_abs(fd.zigzag_merge(got), ref) < 1e-4
+
+
+def _missing_peer_worker(rank, world, port, out_dir):
+    """Rank 1 leaves between steps without ever joining the exchange; rank 0 must get an error on
+    the host within the process group's (short) time-out, not hang."""
+    import datetime
+    import time
+
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=5))
+    from flash_attn_v100 import distributed as fd
+
+    q, k, v, _ = oracle.make_inputs(1, 64, 1, 64, seed=1)
+    ql, kl, vl = (fd.zigzag_split(t, rank, world) for t in (q, k, v))
+    if rank == 1:
+        return  # the peer that never shows up (no collective of its in flight)
+    t0 = time.perf_counter()
+    try:
+        fd.ring_attention_forward(ql, kl, vl, 0.2, True, None, OracleBackend())
+        outcome = "no error"
+    except Exception as exc:  # noqa: BLE001 - any host-side error is the point
+        outcome = f"error after {time.perf_counter() - t0:.1f} s: {type(exc).__name__}"
+    with open(os.path.join(out_dir, "rank0.txt"), "w") as f:
+        f.write(outcome)
+
+
+def test_a_missing_peer_is_an_error_on_the_host_not_a_hang(tmp_path):
+    """Failure detection without a GPU: the exchange with a rank that has gone away ends with an
+    exception on the surviving rank once the process group's time-out (5 s here) has passed."""
+    mp.spawn(_missing_peer_worker, args=(2, _free_port(), str(tmp_path)), nprocs=2, join=True)
+    outcome = open(os.path.join(tmp_path, "rank0.txt")).read()
+    assert outcome.startswith("error after"), outcome
+    assert float(outcome.split()[2]) < 60.0, outcome
