@@ -49,7 +49,6 @@ struct BwdKernelParams {
   int num_kv_blocks;    // ceil(seqlen_k / 128)
   int num_heads_total;  // batch * heads
   int head_group;       // heads whose CTAs are interleaved in the grid (>= 1)
-  int rotate_start;     // 1: CTA kb starts on its (kb mod count)-th query tile (no causal mask)
   float scale, scale_log2;
   int causal, causal_shift;
   int* status;
@@ -157,34 +156,56 @@ __global__ void __launch_bounds__(512, 1)
   }
   // query tiles this CTA walks (may be 0; a KV tile that is all padding walks none)
   const int cnt = kv0 < sk ? nq_tiles - i_begin : 0;
-  // The n-th query tile this CTA visits.  Under a causal mask the CTAs of a head start on
-  // different tiles by themselves (tile_begin grows with kb).  Without one they would all start
-  // on tile 0 and add into the same dQ tile at the same time, step after step; rotate_start lets
-  // CTA kb start on tile kb instead (wrapping round), so that the reduce-adds of a head's CTAs
-  // go to different lines of the L2.
-  const int rot = (p.rotate_start != 0 && cnt > 1) ? kb % cnt : 0;
-  auto tile_of = [&](int n) {
-    const int t = n + rot;
-    return i_begin + (t >= cnt ? t - cnt : t);
-  };
+  // the n-th query tile this CTA visits
+  auto tile_of = [&](int n) { return i_begin + n; };
 
-  if (threadIdx.x == 0) {
-    mbar_init(smem_u32(&bar_kv_full), 1);
-    for (int s = 0; s < T::kQStages; ++s) {
-      mbar_init(smem_u32(&bar_q_full[s]), 1);
-      mbar_init(smem_u32(&bar_q_empty[s]), 1);
+  // The producer warp sets the barriers up itself and sends the loads of K, V and of the first
+  // Q / dO tile off at once, before the CTA-wide barrier below that waits for the tensor-memory
+  // allocation: the load latency at the head of a CTA runs beside the rest of the set-up.
+  if (warp == 12) {
+    if (lane == 0) {
+      mbar_init(smem_u32(&bar_kv_full), 1);
+      for (int s = 0; s < T::kQStages; ++s) {
+        mbar_init(smem_u32(&bar_q_full[s]), 1);
+        mbar_init(smem_u32(&bar_q_empty[s]), 1);
+      }
+      mbar_init(smem_u32(&bar_do_full), 1);
+      mbar_init(smem_u32(&bar_do_empty), 1);
+      mbar_init(smem_u32(&bar_s_full), 1);
+      mbar_init(smem_u32(&bar_dp_full), 1);
+      mbar_init(smem_u32(&bar_p_ready), 256);
+      mbar_init(smem_u32(&bar_ds_ready), 256);
+      mbar_init(smem_u32(&bar_dq_full), 1);
+      mbar_init(smem_u32(&bar_dq_empty), 128);
+      mbar_init(smem_u32(&bar_ds_free), 1);
+      mbar_init(smem_u32(&bar_done), 1);
+      fence_barrier_init();
     }
-    mbar_init(smem_u32(&bar_do_full), 1);
-    mbar_init(smem_u32(&bar_do_empty), 1);
-    mbar_init(smem_u32(&bar_s_full), 1);
-    mbar_init(smem_u32(&bar_dp_full), 1);
-    mbar_init(smem_u32(&bar_p_ready), 256);
-    mbar_init(smem_u32(&bar_ds_ready), 256);
-    mbar_init(smem_u32(&bar_dq_full), 1);
-    mbar_init(smem_u32(&bar_dq_empty), 128);
-    mbar_init(smem_u32(&bar_ds_free), 1);
-    mbar_init(smem_u32(&bar_done), 1);
-    fence_barrier_init();
+    __syncwarp();
+    if (cnt > 0 && elect_one()) {
+      tma_prefetch_desc(&tm_q);
+      tma_prefetch_desc(&tm_k);
+      tma_prefetch_desc(&tm_v);
+      tma_prefetch_desc(&tm_do);
+      const uint32_t kvbar = smem_u32(&bar_kv_full);
+      mbar_arrive_expect_tx(kvbar, 2 * T::kTileBytes);
+      const uint32_t qbar = smem_u32(&bar_q_full[0]);
+      mbar_arrive_expect_tx(qbar, T::kTileBytes);
+      const uint32_t dbar = smem_u32(&bar_do_full);
+      mbar_arrive_expect_tx(dbar, T::kTileBytes);
+      const int row0 = tile_of(0) * T::kBlock;
+#pragma unroll
+      for (int b = 0; b < T::kBoxes; ++b) {
+        tma_load_4d(k_smem + b * T::kBoxBytes, &tm_k, kvbar, b * 64, kv0, h, z);
+        tma_load_4d(q_smem + b * T::kBoxBytes, &tm_q, qbar, b * 64, row0, h, z);
+      }
+#pragma unroll
+      for (int b = 0; b < T::kBoxes; ++b) {
+        tma_load_4d(v_smem + b * T::kBoxBytes, &tm_v, kvbar, b * 64, kv0, h, z);
+        tma_load_4d(do_smem + b * T::kBoxBytes, &tm_do, dbar, b * 64, row0, h, z);
+      }
+    }
+    __syncwarp();
   }
   if (warp == 13) {
     tmem_alloc(smem_u32(&tmem_base_slot), T::kTmemCols);
@@ -205,21 +226,8 @@ __global__ void __launch_bounds__(512, 1)
   if (warp == 12) {
     // =========================== TMA producer ===========================
     if (cnt > 0) {
-      if (elect_one()) {
-        tma_prefetch_desc(&tm_q);
-        tma_prefetch_desc(&tm_k);
-        tma_prefetch_desc(&tm_v);
-        tma_prefetch_desc(&tm_do);
-        const uint32_t kvbar = smem_u32(&bar_kv_full);
-        mbar_arrive_expect_tx(kvbar, 2 * T::kTileBytes);
-#pragma unroll
-        for (int b = 0; b < T::kBoxes; ++b) {
-          tma_load_4d(k_smem + b * T::kBoxBytes, &tm_k, kvbar, b * 64, kv0, h, z);
-          tma_load_4d(v_smem + b * T::kBoxBytes, &tm_v, kvbar, b * 64, kv0, h, z);
-        }
-      }
-      __syncwarp();
-      for (int n = 0; n < cnt; ++n) {
+      // K, V and the first Q / dO tile were sent off during the set-up
+      for (int n = 1; n < cnt; ++n) {
         const int st = n % T::kQStages;
         const int round = n / T::kQStages;
         const int row = tile_of(n) * T::kBlock;
@@ -235,7 +243,7 @@ __global__ void __launch_bounds__(512, 1)
                         z);
         }
         __syncwarp();
-        if (n > 0 && !mbar_wait_warp(smem_u32(&bar_do_empty), (n - 1) & 1, &abort_word, 2)) break;
+        if (!mbar_wait_warp(smem_u32(&bar_do_empty), (n - 1) & 1, &abort_word, 2)) break;
         if (elect_one()) {
           const uint32_t dbar = smem_u32(&bar_do_full);
           mbar_arrive_expect_tx(dbar, T::kTileBytes);
@@ -535,12 +543,13 @@ __global__ void __launch_bounds__(512, 1)
         if (tl) FMHA_TL(1, n, 3);
       }
       if (r == 0) tma_wait_group<0>();
-      named_bar_sync(2, 128);  // the staging area is idle again (the dV epilogue reuses nothing of it,
-                               // but the group leaves its loop together)
+      named_bar_sync(2, 128);  // the group leaves its loop together
     }
 
-    // ============ epilogue: dK (warps 0-3), dV (warps 8-11); warps 4-7 are done ============
-    if (warp < 4 || warp >= 8) {
+    // ============ epilogue: dK (warps 0-3), dV (warps 4-7) ============
+    // The two compute groups, which are done with the last query tile before the dQ group is:
+    // dK and dV leave while the last dQ tile is still being staged and reduce-added.
+    if (warp < 8) {
       const bool is_dk = warp < 4;
       if (cnt > 0) mbar_wait(smem_u32(&bar_done), 0, &abort_word, 15);
       tc_fence_after();
@@ -603,7 +612,7 @@ __global__ void __launch_bounds__(512, 1)
           }
         }
         fence_proxy_async_smem();
-        named_bar_sync(is_dk ? 1 : 2, 128);
+        named_bar_sync(is_dk ? 1 : 5, 128);
         if (r == 0) {
           const CUtensorMap* tm = is_dk ? &tm_dk : &tm_dv;
 #pragma unroll

@@ -115,27 +115,22 @@ fmha::Strides3 to3(const FmhaStrides& s) { return fmha::Strides3{s.batch, s.row,
 
 int round_up_128(int x) { return (x + 127) / 128 * 128; }
 
-// FMHA_BWD_ROTATE=0/1 overrides the default (tuning experiments)
-bool bwd_rotate_start() {
-  static const bool on = []() {
-    const char* e = std::getenv("FMHA_BWD_ROTATE");
-    return e != nullptr ? std::atoi(e) != 0 : false;
-  }();
-  return on;
-}
-
-// Heads whose CTAs are interleaved in the backward grid (see the coordinates in bwd_kernel.cuh).
-// 8 for up to 32 KV tiles per head: measured 3.3 % on the fused kernel at N = 2048 causal (0.809 ->
-// 0.782 ms; 4: 0.794, 16: 0.779), the last CTAs of a group and of the grid being the short ones.
-// Longer sequences keep one head at a time: their grids are long, and eight heads' query tiles
-// would not share the L2.  FMHA_BWD_HEAD_GROUP overrides (tuning experiments).
-int bwd_head_group(int num_kv_blocks) {
+// Heads whose CTAs are interleaved in the backward grid (see the coordinates in bwd_kernel.cuh),
+// for up to 32 KV tiles per head.  Measured on the fused kernel at Z=8, H=32, N=2048, D=128,
+// alternating runs: causal 0.809 ms with one head at a time, 0.794 with groups of 4, 0.778 with 8,
+// 0.771 with 16, 0.770 with 24, 0.769 with 32, 0.773 with 37 (the last CTAs of a group and of the
+// grid being the short ones); without a mask, where all CTAs are equally long and only the L2
+// matters, 1.351 ms with 8 against 1.37-1.40 with 16 to 37.  Longer sequences keep one head at a
+// time: their grids are long, and many heads' query tiles would not share the L2.
+// FMHA_BWD_HEAD_GROUP overrides (tuning experiments).
+int bwd_head_group(int num_kv_blocks, bool causal) {
   static const int forced = []() {
     const char* e = std::getenv("FMHA_BWD_HEAD_GROUP");
     return e != nullptr ? std::atoi(e) : 0;
   }();
   if (forced >= 1) return forced;
-  return num_kv_blocks <= 32 ? 8 : 1;
+  if (num_kv_blocks > 32) return 1;
+  return causal ? 16 : 8;
 }
 
 struct BwdWorkspace {
@@ -252,9 +247,7 @@ int launch_bwd(const FmhaBwdParams* p, const BwdWorkspace& w, cudaStream_t strea
     kp.seqlen_q_pad = Nq_pad;
     kp.num_kv_blocks = (Nk + 127) / 128;
     kp.num_heads_total = Z * H;
-    kp.head_group = bwd_head_group(kp.num_kv_blocks);
-    // not with the ordered reduction, whose CTAs take their turns in the order of the KV tiles
-    kp.rotate_start = (!p->causal && !(p->flags & FMHA_BWD_DETERMINISTIC) && bwd_rotate_start()) ? 1 : 0;
+    kp.head_group = bwd_head_group(kp.num_kv_blocks, p->causal != 0);
     kp.scale = p->scale;
     kp.scale_log2 = p->scale * 1.4426950408889634f;
     kp.causal = p->causal ? 1 : 0;
