@@ -44,6 +44,8 @@ def test_our_arm_line_has_roofline_baseline_e2e_and_clocks():
     assert {"sm_mhz", "sm_max_mhz", "reasons"} <= set(d["clocks"])
     assert d["config"]["launch"].startswith("CUDA graph") or d["config"]["launch"].startswith("four")
     assert d["regions"]["count"] == 3 and d["regions"]["min_ms"] <= d["ms_per_step"] <= d["regions"]["max_ms"]
-    assert 0.8 < d["kernels"]["sum_of_parts_over_step"] < 1.6
+    # (a step of this small workload is replayed from a CUDA graph; the instrumented loop launches
+    # its kernels one by one with events between them, so the parts add up to well over the step)
+    assert 0.8 < d["kernels"]["sum_of_parts_over_step"] < 3.0
     assert d["kernels"]["from_idle"]["fwd_ms"] > 0 and d["kernels"]["plain_step_ms_right_after"] > 0
     assert "sharded" not in d  # only the default workload carries the sharded configs
