@@ -102,7 +102,7 @@ int check_strides(const FmhaStrides& s, int N, int H, int Z) {
 int check_common(int batch, int heads, int seqlen_q, int seqlen_k, int head_dim, float scale,
                  int dtype = FMHA_DTYPE_FP16) {
   if (dtype != FMHA_DTYPE_FP16 && dtype != FMHA_DTYPE_BF16) return FMHA_ERR_BAD_DTYPE;
-  if (head_dim != 64 && head_dim != 128) return FMHA_ERR_BAD_HEAD_DIM;
+  if (head_dim != 64 && head_dim != 96 && head_dim != 128) return FMHA_ERR_BAD_HEAD_DIM;
   if (batch <= 0 || heads <= 0 || seqlen_q <= 0 || seqlen_k <= 0) return FMHA_ERR_BAD_SHAPE;
   if (!std::isfinite(scale) || scale == 0.f) return FMHA_ERR_BAD_SHAPE;
   if ((long long)batch * heads * ((seqlen_q + 127) / 128 + 1) >= (1ll << 31) ||
@@ -156,21 +156,25 @@ BwdWorkspace carve_workspace(void* ws, int Z, int H, int Nq, int D) {
   return w;
 }
 
+// D is the head dimension the kernel runs at; the tensors have p->head_dim <= D elements per row
+// (96 runs at D = 128: the tensor maps describe 96 columns, the loads fill the rest of a
+// 128-wide tile with zeros and the stores clip it)
 template <int D, bool kBf16>
 int launch_fwd(const FmhaFwdParams* p, cudaStream_t stream) {
   using T = fmha::FwdTraits<D, kBf16>;
   CUtensorMap tq, tk, tv, to;
   int rc;
-  if ((rc = make_tensor_map(&tq, p->q, p->batch, p->seqlen_q, p->heads, D, p->q_strides, kBf16)))
+  const int Dr = p->head_dim;
+  if ((rc = make_tensor_map(&tq, p->q, p->batch, p->seqlen_q, p->heads, Dr, p->q_strides, kBf16)))
     return rc;
   // K and V are loaded in half tiles of kStepN rows
-  if ((rc = make_tensor_map(&tk, p->k, p->batch, p->seqlen_k, p->heads, D, p->k_strides, kBf16,
+  if ((rc = make_tensor_map(&tk, p->k, p->batch, p->seqlen_k, p->heads, Dr, p->k_strides, kBf16,
                             T::kStepN)))
     return rc;
-  if ((rc = make_tensor_map(&tv, p->v, p->batch, p->seqlen_k, p->heads, D, p->v_strides, kBf16,
+  if ((rc = make_tensor_map(&tv, p->v, p->batch, p->seqlen_k, p->heads, Dr, p->v_strides, kBf16,
                             T::kStepN)))
     return rc;
-  if ((rc = make_tensor_map(&to, p->o, p->batch, p->seqlen_q, p->heads, D, p->o_strides, kBf16)))
+  if ((rc = make_tensor_map(&to, p->o, p->batch, p->seqlen_q, p->heads, Dr, p->o_strides, kBf16)))
     return rc;
   fmha::FwdKernelParams kp;
   kp.lse = p->lse;
@@ -205,6 +209,7 @@ int launch_bwd(const FmhaBwdParams* p, const BwdWorkspace& w, cudaStream_t strea
   using E = typename std::conditional<kBf16, __nv_bfloat16, __half>::type;
   const int Z = p->batch, H = p->heads, Nq = p->seqlen_q, Nk = p->seqlen_k;
   const int Nq_pad = round_up_128(Nq);
+  const int Dr = p->head_dim;  // what the tensors have; D is what the kernels run at
 
   if (!(p->flags & FMHA_BWD_KEEP_WORKSPACE)) {
     const long long rows = (long long)Z * H * Nq_pad;
@@ -212,7 +217,7 @@ int launch_bwd(const FmhaBwdParams* p, const BwdWorkspace& w, cudaStream_t strea
     const unsigned grid = (unsigned)((rows + rows_per_block - 1) / rows_per_block);
     fmha::fmha_bwd_preprocess_kernel<D, E><<<grid, 256, 0, stream>>>(
         static_cast<const E*>(p->o), to3(p->o_strides), static_cast<const E*>(p->dout),
-        to3(p->dout_strides), p->lse, w.dq_accum, w.lse2, w.delta, H, Nq, Nq_pad, rows, p->seqused_q);
+        to3(p->dout_strides), p->lse, w.dq_accum, w.lse2, w.delta, H, Nq, Nq_pad, rows, p->seqused_q, Dr);
     if (cudaGetLastError() != cudaSuccess) return FMHA_ERR_LAUNCH;
   }
   if (p->flags & FMHA_BWD_PREPROCESS_ONLY) return FMHA_OK;
@@ -220,17 +225,17 @@ int launch_bwd(const FmhaBwdParams* p, const BwdWorkspace& w, cudaStream_t strea
   {
     CUtensorMap tq, tk, tv, tdo, tdk, tdv, tacc;
     int rc;
-    if ((rc = make_accum_map(&tacc, w.dq_accum, Z, Nq, H, D))) return rc;
-    if ((rc = make_tensor_map(&tq, p->q, Z, Nq, H, D, p->q_strides, kBf16))) return rc;
-    if ((rc = make_tensor_map(&tk, p->k, Z, Nk, H, D, p->k_strides, kBf16))) return rc;
-    if ((rc = make_tensor_map(&tv, p->v, Z, Nk, H, D, p->v_strides, kBf16))) return rc;
-    if ((rc = make_tensor_map(&tdo, p->dout, Z, Nq, H, D, p->dout_strides, kBf16))) return rc;
+    if ((rc = make_accum_map(&tacc, w.dq_accum, Z, Nq, H, Dr))) return rc;
+    if ((rc = make_tensor_map(&tq, p->q, Z, Nq, H, Dr, p->q_strides, kBf16))) return rc;
+    if ((rc = make_tensor_map(&tk, p->k, Z, Nk, H, Dr, p->k_strides, kBf16))) return rc;
+    if ((rc = make_tensor_map(&tv, p->v, Z, Nk, H, Dr, p->v_strides, kBf16))) return rc;
+    if ((rc = make_tensor_map(&tdo, p->dout, Z, Nq, H, Dr, p->dout_strides, kBf16))) return rc;
     // with fp32 accumulation the fp16 outputs are not touched: any valid map will do
     const bool acc_k = p->dk_accum != nullptr, acc_v = p->dv_accum != nullptr;
-    if ((rc = make_tensor_map(&tdk, acc_k ? p->k : p->dk, Z, Nk, H, D,
+    if ((rc = make_tensor_map(&tdk, acc_k ? p->k : p->dk, Z, Nk, H, Dr,
                               acc_k ? p->k_strides : p->dk_strides, kBf16)))
       return rc;
-    if ((rc = make_tensor_map(&tdv, acc_v ? p->v : p->dv, Z, Nk, H, D,
+    if ((rc = make_tensor_map(&tdv, acc_v ? p->v : p->dv, Z, Nk, H, Dr,
                               acc_v ? p->v_strides : p->dv_strides, kBf16)))
       return rc;
     fmha::BwdKernelParams kp;
@@ -239,9 +244,10 @@ int launch_bwd(const FmhaBwdParams* p, const BwdWorkspace& w, cudaStream_t strea
     kp.dk_accum = p->dk_accum;
     kp.dv_accum = p->dv_accum;
     kp.accum_batch_stride =
-        p->accum_batch_stride > 0 ? p->accum_batch_stride : (long long)Nk * H * D;
+        p->accum_batch_stride > 0 ? p->accum_batch_stride : (long long)Nk * H * Dr;
     kp.accum_overwrite = (p->flags & FMHA_BWD_ACCUM_OVERWRITE) ? 1 : 0;
     kp.heads = H;
+    kp.head_dim = Dr;
     kp.seqlen_q = Nq;
     kp.seqlen_k = Nk;
     kp.seqlen_q_pad = Nq_pad;
@@ -277,7 +283,7 @@ int launch_bwd(const FmhaBwdParams* p, const BwdWorkspace& w, cudaStream_t strea
     constexpr int rows_per_block = 256 / (D / 8);
     const unsigned grid = (unsigned)((rows + rows_per_block - 1) / rows_per_block);
     fmha::fmha_bwd_convert_dq_kernel<D, E><<<grid, 256, 0, stream>>>(
-        w.dq_accum, static_cast<E*>(p->dq), to3(p->dq_strides), H, Nq, p->scale, rows);
+        w.dq_accum, static_cast<E*>(p->dq), to3(p->dq_strides), H, Nq, p->scale, rows, Dr);
     if (cudaGetLastError() != cudaSuccess) return FMHA_ERR_LAUNCH;
   }
   return FMHA_OK;
@@ -341,8 +347,8 @@ int fmha_fwd(const FmhaFwdParams* p, void* stream) {
   if ((rc = check_strides(p->o_strides, p->seqlen_q, p->heads, p->batch))) return rc;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (p->dtype == FMHA_DTYPE_BF16)
-    return p->head_dim == 128 ? launch_fwd<128, true>(p, s) : launch_fwd<64, true>(p, s);
-  return p->head_dim == 128 ? launch_fwd<128, false>(p, s) : launch_fwd<64, false>(p, s);
+    return p->head_dim > 64 ? launch_fwd<128, true>(p, s) : launch_fwd<64, true>(p, s);
+  return p->head_dim > 64 ? launch_fwd<128, false>(p, s) : launch_fwd<64, false>(p, s);
 }
 
 size_t fmha_bwd_workspace_bytes(const FmhaBwdParams* p) {
@@ -393,8 +399,8 @@ int fmha_bwd(const FmhaBwdParams* p, void* workspace, size_t workspace_bytes, vo
   if (!aligned16(workspace)) return FMHA_ERR_BAD_ALIGNMENT;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (p->dtype == FMHA_DTYPE_BF16)
-    return p->head_dim == 128 ? launch_bwd<128, true>(p, w, s) : launch_bwd<64, true>(p, w, s);
-  return p->head_dim == 128 ? launch_bwd<128, false>(p, w, s) : launch_bwd<64, false>(p, w, s);
+    return p->head_dim > 64 ? launch_bwd<128, true>(p, w, s) : launch_bwd<64, true>(p, w, s);
+  return p->head_dim > 64 ? launch_bwd<128, false>(p, w, s) : launch_bwd<64, false>(p, w, s);
 }
 
 int fmha_bwd_static_scratch(const FmhaBwdParams* p, void* stream) {
@@ -419,29 +425,30 @@ int fmha_bwd_convert_dq(const void* workspace, void* dq, FmhaStrides dq_strides,
                         int32_t dtype, void* stream) {
   if (workspace == nullptr || dq == nullptr) return FMHA_ERR_NULL_POINTER;
   if (dtype != FMHA_DTYPE_FP16 && dtype != FMHA_DTYPE_BF16) return FMHA_ERR_BAD_DTYPE;
-  if (head_dim != 64 && head_dim != 128) return FMHA_ERR_BAD_HEAD_DIM;
+  if (head_dim != 64 && head_dim != 96 && head_dim != 128) return FMHA_ERR_BAD_HEAD_DIM;
   if (batch <= 0 || heads <= 0 || seqlen_q <= 0) return FMHA_ERR_BAD_SHAPE;
   if (!aligned16(workspace) || !aligned16(dq)) return FMHA_ERR_BAD_ALIGNMENT;
   int rc = check_strides(dq_strides, seqlen_q, heads, batch);
   if (rc) return rc;
   const long long rows = (long long)batch * seqlen_q * heads;
-  const int rows_per_block = 256 / (head_dim / 8);
+  const int Dp = head_dim > 64 ? 128 : 64;  // the thread layout the kernels run at
+  const int rows_per_block = 256 / (Dp / 8);
   const unsigned grid = (unsigned)((rows + rows_per_block - 1) / rows_per_block);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const float* acc = static_cast<const float*>(workspace);
   const fmha::Strides3 sd = to3(dq_strides);
   if (dtype == FMHA_DTYPE_BF16) {
     auto* out = static_cast<__nv_bfloat16*>(dq);
-    if (head_dim == 128)
-      fmha::fmha_bwd_convert_dq_kernel<128, __nv_bfloat16><<<grid, 256, 0, s>>>(acc, out, sd, heads, seqlen_q, scale, rows);
+    if (Dp == 128)
+      fmha::fmha_bwd_convert_dq_kernel<128, __nv_bfloat16><<<grid, 256, 0, s>>>(acc, out, sd, heads, seqlen_q, scale, rows, head_dim);
     else
-      fmha::fmha_bwd_convert_dq_kernel<64, __nv_bfloat16><<<grid, 256, 0, s>>>(acc, out, sd, heads, seqlen_q, scale, rows);
+      fmha::fmha_bwd_convert_dq_kernel<64, __nv_bfloat16><<<grid, 256, 0, s>>>(acc, out, sd, heads, seqlen_q, scale, rows, head_dim);
   } else {
     auto* out = static_cast<__half*>(dq);
-    if (head_dim == 128)
-      fmha::fmha_bwd_convert_dq_kernel<128, __half><<<grid, 256, 0, s>>>(acc, out, sd, heads, seqlen_q, scale, rows);
+    if (Dp == 128)
+      fmha::fmha_bwd_convert_dq_kernel<128, __half><<<grid, 256, 0, s>>>(acc, out, sd, heads, seqlen_q, scale, rows, head_dim);
     else
-      fmha::fmha_bwd_convert_dq_kernel<64, __half><<<grid, 256, 0, s>>>(acc, out, sd, heads, seqlen_q, scale, rows);
+      fmha::fmha_bwd_convert_dq_kernel<64, __half><<<grid, 256, 0, s>>>(acc, out, sd, heads, seqlen_q, scale, rows, head_dim);
   }
   return cudaGetLastError() == cudaSuccess ? FMHA_OK : FMHA_ERR_LAUNCH;
 }
@@ -453,7 +460,7 @@ int fmha_merge_rows(float* o_acc, float* lse_acc, const void* o_part, FmhaStride
   if (o_acc == nullptr || lse_acc == nullptr || o_part == nullptr || lse_part == nullptr)
     return FMHA_ERR_NULL_POINTER;
   if (dtype != FMHA_DTYPE_FP16 && dtype != FMHA_DTYPE_BF16) return FMHA_ERR_BAD_DTYPE;
-  if (head_dim != 64 && head_dim != 128) return FMHA_ERR_BAD_HEAD_DIM;
+  if (head_dim != 64 && head_dim != 96 && head_dim != 128) return FMHA_ERR_BAD_HEAD_DIM;
   if (batch <= 0 || heads <= 0 || rows <= 0 || row_offset < 0 ||
       (long long)row_offset + rows > (long long)acc_rows)
     return FMHA_ERR_BAD_SHAPE;
@@ -461,28 +468,29 @@ int fmha_merge_rows(float* o_acc, float* lse_acc, const void* o_part, FmhaStride
   int rc = check_strides(o_part_strides, rows, heads, batch);
   if (rc) return rc;
   const long long total = (long long)batch * rows * heads;
-  const int rows_per_block = 256 / (head_dim / 8);
+  const int Dp = head_dim > 64 ? 128 : 64;  // the thread layout the kernels run at
+  const int rows_per_block = 256 / (Dp / 8);
   const unsigned grid = (unsigned)((total + rows_per_block - 1) / rows_per_block);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const fmha::Strides3 sp = to3(o_part_strides);
   if (dtype == FMHA_DTYPE_BF16) {
     auto* part = static_cast<const __nv_bfloat16*>(o_part);
     auto* out = static_cast<__nv_bfloat16*>(o_out);
-    if (head_dim == 128)
+    if (Dp == 128)
       fmha::fmha_merge_kernel<128, __nv_bfloat16><<<grid, 256, 0, s>>>(
-          o_acc, lse_acc, part, sp, lse_part, out, heads, rows, acc_rows, row_offset, total);
+          o_acc, lse_acc, part, sp, lse_part, out, heads, rows, acc_rows, row_offset, total, head_dim);
     else
       fmha::fmha_merge_kernel<64, __nv_bfloat16><<<grid, 256, 0, s>>>(
-          o_acc, lse_acc, part, sp, lse_part, out, heads, rows, acc_rows, row_offset, total);
+          o_acc, lse_acc, part, sp, lse_part, out, heads, rows, acc_rows, row_offset, total, head_dim);
   } else {
     auto* part = static_cast<const __half*>(o_part);
     auto* out = static_cast<__half*>(o_out);
-    if (head_dim == 128)
+    if (Dp == 128)
       fmha::fmha_merge_kernel<128, __half><<<grid, 256, 0, s>>>(
-          o_acc, lse_acc, part, sp, lse_part, out, heads, rows, acc_rows, row_offset, total);
+          o_acc, lse_acc, part, sp, lse_part, out, heads, rows, acc_rows, row_offset, total, head_dim);
     else
       fmha::fmha_merge_kernel<64, __half><<<grid, 256, 0, s>>>(
-          o_acc, lse_acc, part, sp, lse_part, out, heads, rows, acc_rows, row_offset, total);
+          o_acc, lse_acc, part, sp, lse_part, out, heads, rows, acc_rows, row_offset, total, head_dim);
   }
   return cudaGetLastError() == cudaSuccess ? FMHA_OK : FMHA_ERR_LAUNCH;
 }
@@ -604,7 +612,7 @@ int fmha_sum_partials(const float* const* parts, const int32_t* rows_per_part, i
                       int32_t head_dim, int32_t dtype, void* stream) {
   if (parts == nullptr || rows_per_part == nullptr || out == nullptr) return FMHA_ERR_NULL_POINTER;
   if (dtype != FMHA_DTYPE_FP16 && dtype != FMHA_DTYPE_BF16) return FMHA_ERR_BAD_DTYPE;
-  if (head_dim != 64 && head_dim != 128) return FMHA_ERR_BAD_HEAD_DIM;
+  if (head_dim != 64 && head_dim != 96 && head_dim != 128) return FMHA_ERR_BAD_HEAD_DIM;
   if (batch <= 0 || heads <= 0 || rows <= 0 || n_parts <= 0) return FMHA_ERR_BAD_SHAPE;
   if (n_parts > fmha::kMaxPeers) return FMHA_ERR_TOO_LARGE;
   if (!aligned16(out)) return FMHA_ERR_BAD_ALIGNMENT;
@@ -620,22 +628,23 @@ int fmha_sum_partials(const float* const* parts, const int32_t* rows_per_part, i
     list.rows[i] = rows_per_part[i];
   }
   const long long total = (long long)batch * rows * heads;
-  const int rows_per_block = 256 / (head_dim / 8);
+  const int Dp = head_dim > 64 ? 128 : 64;  // the thread layout the kernels run at
+  const int rows_per_block = 256 / (Dp / 8);
   const unsigned grid = (unsigned)((total + rows_per_block - 1) / rows_per_block);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const fmha::Strides3 so = to3(out_strides);
   if (dtype == FMHA_DTYPE_BF16) {
     auto* o = static_cast<__nv_bfloat16*>(out);
-    if (head_dim == 128)
-      fmha::sum_partials_kernel<128, __nv_bfloat16><<<grid, 256, 0, s>>>(list, o, so, heads, rows, total);
+    if (Dp == 128)
+      fmha::sum_partials_kernel<128, __nv_bfloat16><<<grid, 256, 0, s>>>(list, o, so, heads, rows, total, head_dim);
     else
-      fmha::sum_partials_kernel<64, __nv_bfloat16><<<grid, 256, 0, s>>>(list, o, so, heads, rows, total);
+      fmha::sum_partials_kernel<64, __nv_bfloat16><<<grid, 256, 0, s>>>(list, o, so, heads, rows, total, head_dim);
   } else {
     auto* o = static_cast<__half*>(out);
-    if (head_dim == 128)
-      fmha::sum_partials_kernel<128, __half><<<grid, 256, 0, s>>>(list, o, so, heads, rows, total);
+    if (Dp == 128)
+      fmha::sum_partials_kernel<128, __half><<<grid, 256, 0, s>>>(list, o, so, heads, rows, total, head_dim);
     else
-      fmha::sum_partials_kernel<64, __half><<<grid, 256, 0, s>>>(list, o, so, heads, rows, total);
+      fmha::sum_partials_kernel<64, __half><<<grid, 256, 0, s>>>(list, o, so, heads, rows, total, head_dim);
   }
   return cudaGetLastError() == cudaSuccess ? FMHA_OK : FMHA_ERR_LAUNCH;
 }
@@ -694,7 +703,7 @@ const char* fmha_status_string(int status) {
   switch (status) {
     case FMHA_OK: return "ok";
     case FMHA_ERR_NULL_POINTER: return "a required pointer is NULL";
-    case FMHA_ERR_BAD_HEAD_DIM: return "head_dim must be 64 or 128";
+    case FMHA_ERR_BAD_HEAD_DIM: return "head_dim must be 64, 96 or 128";
     case FMHA_ERR_BAD_SHAPE: return "sizes must be positive and scale finite and non-zero";
     case FMHA_ERR_BAD_STRIDE: return "strides must be positive multiples of 8 elements";
     case FMHA_ERR_BAD_ALIGNMENT: return "pointers must be 16-byte aligned";

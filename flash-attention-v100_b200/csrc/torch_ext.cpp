@@ -7,7 +7,7 @@
 //
 // Differences from the reference extension, all widenings:
 //   - any sm_100 device instead of the sm_70 gate (kernel/fused_mha_api.cpp:21-23);
-//   - bf16 beside fp16 (reference: fp16 only, :25-29); head_dim 64 or 128 (reference: 128 only, :44); sequence length a multiple of 32 is
+//   - bf16 beside fp16 (reference: fp16 only, :25-29); head_dim 64, 96 or 128 (reference: 128 only, :44); sequence length a multiple of 32 is
 //     CHECKED (the reference only documents it, README.md:3);
 //   - q and k/v may differ in sequence length; row/head/batch strides are honoured;
 //   - `fwd` returns {out, softmax_max, softmax_sum} like the reference (:71), where
@@ -51,7 +51,7 @@ void check_shapes(const at::Tensor& q, const at::Tensor& k, const at::Tensor& v)
   const auto B = q.size(0), Nq = q.size(1), H = q.size(2), D = q.size(3);
   const auto Nk = k.size(1);
   TORCH_CHECK(B > 0, "batch size must be positive");
-  TORCH_CHECK(D == 64 || D == 128, "head dimension must be 64 or 128, got ", D);
+  TORCH_CHECK(D == 64 || D == 96 || D == 128, "head dimension must be 64, 96 or 128, got ", D);
   TORCH_CHECK(k.size(0) == B && k.size(2) == H && k.size(3) == D,
               "k must have shape (batch_size, seqlen_k, num_heads, head_size)");
   TORCH_CHECK(v.sizes() == k.sizes(), "v must have the shape of k");

@@ -147,7 +147,7 @@ def flash_attn_padded_func(q, k, v, seqused_q=None, seqused_k=None, softmax_scal
 def flash_attn_func(q, k, v, softmax_scale: Optional[float] = None, causal: bool = False):
     """softmax(q k^T * softmax_scale [+ causal mask]) v with autograd.
 
-    q, k, v: fp16 (or bf16) CUDA tensors (batch, seqlen, heads, head_dim), head_dim 64 or 128,
+    q, k, v: fp16 (or bf16) CUDA tensors (batch, seqlen, heads, head_dim), head_dim 64, 96 or 128,
     seqlen a multiple of 32.  softmax_scale defaults to head_dim ** -0.5.  Returns (batch,
     seqlen, heads, head_dim) in the inputs' type.
     """

@@ -16,6 +16,11 @@
  *    heads, head_dim) as in the reference (kernel/fused_mha_api.cpp:37-47).  Strides are in
  *    ELEMENTS and the head_dim stride must be 1.  Row/head/batch strides must be multiples
  *    of 8 elements and base pointers 16-byte aligned (TMA requirement).
+ *  - head_dim is 64, 96 or 128 (the reference: 128 only, kernel/fused_mha_api.cpp:44).  96 runs on
+ *    the 128-wide kernels: the tensor maps describe 96 columns, tile loads fill columns 96-127
+ *    with zeros and stores clip them, so the result is exact and the cost is that of 128.  The
+ *    fp32 buffers (workspace, dk_accum / dv_accum, o_acc, partial sums) have head_dim elements
+ *    per row like the 16-bit tensors.
  *  - `lse` is fp32 (Z, H, seqlen_q) contiguous: lse = max + ln(sum) of the scaled scores,
  *    i.e. the reference's `softmax_max` and `softmax_sum` (kernel/fused_mha_api.cpp:65-66)
  *    folded into one number per row.
@@ -50,7 +55,7 @@ extern "C" {
 enum {
   FMHA_OK = 0,
   FMHA_ERR_NULL_POINTER = 1,
-  FMHA_ERR_BAD_HEAD_DIM = 2,   /* head_dim not in {64, 128} */
+  FMHA_ERR_BAD_HEAD_DIM = 2,   /* head_dim not in {64, 96, 128} */
   FMHA_ERR_BAD_SHAPE = 3,      /* non-positive sizes */
   FMHA_ERR_BAD_STRIDE = 4,     /* stride not a multiple of 8 elements, or too small */
   FMHA_ERR_BAD_ALIGNMENT = 5,  /* pointer not 16-byte aligned */

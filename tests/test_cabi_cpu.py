@@ -69,7 +69,7 @@ def _fwd_params(cabi, **kw):
 
 
 @pytest.mark.parametrize("change,status", [
-    (dict(q=None), 1), (dict(lse=None), 1), (dict(head_dim=96), 2), (dict(head_dim=32), 2),
+    (dict(q=None), 1), (dict(lse=None), 1), (dict(head_dim=80), 2), (dict(head_dim=32), 2), (dict(head_dim=256), 2),
     (dict(batch=0), 3), (dict(seqlen_k=-5), 3), (dict(scale=0.0), 3), (dict(scale=float("nan")), 3),
     (dict(q=0x1008), 5), (dict(dtype=2), 11), (dict(dtype=-1), 11),
 ])
