@@ -7,9 +7,9 @@
 //   - merge: LSE-weighted merge of a partial attention result into running fp32
 //     accumulators (ring attention; no counterpart in the reference).
 // Each thread owns 8 consecutive head_dim elements (one 16-byte load of fp16 or bf16) of one row.
-// D is the head dimension the tensor-core kernels run at (64 or 128); d_real <= D is the one the
-// tensors have (96 runs at D = 128: the threads of a row beyond d_real have nothing to do, and the
-// fp32 accumulators are laid out with d_real elements per row).
+// D is the head dimension the tensor-core kernels run at (64 or 128); DR <= D is the one the
+// tensors have (96 runs at D = 128: the threads of a row beyond DR have nothing to do, and the
+// fp32 accumulators are laid out with DR elements per row).
 #pragma once
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
@@ -61,14 +61,14 @@ __device__ __forceinline__ uint4 pack8(const float (&f)[8]) {
 }
 
 // rows are indexed (zh, q) over the PADDED query length so that lse2 / delta are complete
-template <int D, typename E>
+template <int D, typename E, int DR = D>
 __global__ void __launch_bounds__(256)
     fmha_bwd_preprocess_kernel(const E* __restrict__ o, Strides3 so,
                                const E* __restrict__ dout, Strides3 sdo,
                                const float* __restrict__ lse, float* __restrict__ dq_accum,
                                float* __restrict__ lse2, float* __restrict__ delta, int heads,
                                int seqlen_q, int seqlen_q_pad, long long total_rows,
-                               const int* __restrict__ seqused_q, int d_real) {
+                               const int* __restrict__ seqused_q) {
   constexpr int kGroup = D / 8;  // threads per row
   constexpr int kRowsPerBlock = 256 / kGroup;
   const int part = threadIdx.x % kGroup;
@@ -88,7 +88,7 @@ __global__ void __launch_bounds__(256)
   // a padding row of a right-padded batch: P = exp2(s - inf) = 0 for it, it adds nothing to any
   // gradient, and its own dQ stays zero
   const bool padding = seqused_q != nullptr && q >= __ldg(seqused_q + z);
-  const bool mine = part * 8 < d_real;  // this thread's 8 elements exist
+  const bool mine = (DR == D) || part * 8 < DR;  // this thread's 8 elements exist
   float acc = 0.f;
   if (mine) {
     const uint4 uo =
@@ -109,45 +109,45 @@ __global__ void __launch_bounds__(256)
   }
   if (dq_accum != nullptr && mine) {
     float4* dst = reinterpret_cast<float4*>(
-        dq_accum + ((((long long)z * seqlen_q + q) * heads + h) * d_real + part * 8));
+        dq_accum + ((((long long)z * seqlen_q + q) * heads + h) * DR + part * 8));
     dst[0] = make_float4(0.f, 0.f, 0.f, 0.f);
     dst[1] = make_float4(0.f, 0.f, 0.f, 0.f);
   }
 }
 
-template <int D, typename E>
+template <int D, typename E, int DR = D>
 __global__ void __launch_bounds__(256)
     fmha_bwd_convert_dq_kernel(const float* __restrict__ dq_accum, E* __restrict__ dq,
                                Strides3 sdq, int heads, int seqlen_q, float scale,
-                               long long total_rows, int d_real) {
+                               long long total_rows) {
   constexpr int kGroup = D / 8;
   constexpr int kRowsPerBlock = 256 / kGroup;
   const int part = threadIdx.x % kGroup;
   const long long row_id = (long long)blockIdx.x * kRowsPerBlock + threadIdx.x / kGroup;
-  if (row_id >= total_rows || part * 8 >= d_real) return;
+  if (row_id >= total_rows || (DR != D && part * 8 >= DR)) return;
   // row_id enumerates (z, q, h): the accumulator's own order
   const int h = (int)(row_id % heads);
   const long long zq = row_id / heads;
   const int q = (int)(zq % seqlen_q);
   const int z = (int)(zq / seqlen_q);
-  const float4* src = reinterpret_cast<const float4*>(dq_accum + row_id * d_real + part * 8);
+  const float4* src = reinterpret_cast<const float4*>(dq_accum + row_id * DR + part * 8);
   const float4 a = src[0], b = src[1];
   float f[8] = {a.x * scale, a.y * scale, a.z * scale, a.w * scale,
                 b.x * scale, b.y * scale, b.z * scale, b.w * scale};
   *reinterpret_cast<uint4*>(dq + z * sdq.batch + q * sdq.row + h * sdq.head + part * 8) = pack8<E>(f);
 }
 
-template <int D, typename E>
+template <int D, typename E, int DR = D>
 __global__ void __launch_bounds__(256)
     fmha_merge_kernel(float* __restrict__ o_acc, float* __restrict__ lse_acc,
                       const E* __restrict__ o_part, Strides3 sp,
                       const float* __restrict__ lse_part, E* __restrict__ o_out, int heads,
-                      int rows, int acc_rows, int row_offset, long long total_rows, int d_real) {
+                      int rows, int acc_rows, int row_offset, long long total_rows) {
   constexpr int kGroup = D / 8;
   constexpr int kRowsPerBlock = 256 / kGroup;
   const int part = threadIdx.x % kGroup;
   const long long row_id = (long long)blockIdx.x * kRowsPerBlock + threadIdx.x / kGroup;
-  const bool active = row_id < total_rows && part * 8 < d_real;
+  const bool active = row_id < total_rows && (DR == D || part * 8 < DR);
   float la = 0.f, lb = 0.f, ln = 0.f;
   long long stat_idx = 0;
   if (active) {
@@ -171,7 +171,7 @@ __global__ void __launch_bounds__(256)
       wb = eb * inv;
       ln = mx + __logf(ea + eb);
     }
-    float4* acc = reinterpret_cast<float4*>(o_acc + acc_row * d_real + part * 8);
+    float4* acc = reinterpret_cast<float4*>(o_acc + acc_row * DR + part * 8);
     const float4 a0 = acc[0], a1 = acc[1];
     const uint4 up =
         *reinterpret_cast<const uint4*>(o_part + z * sp.batch + q * sp.row + h * sp.head + part * 8);
@@ -183,7 +183,7 @@ __global__ void __launch_bounds__(256)
     acc[0] = make_float4(f[0], f[1], f[2], f[3]);
     acc[1] = make_float4(f[4], f[5], f[6], f[7]);
     if (o_out != nullptr)
-      *reinterpret_cast<uint4*>(o_out + acc_row * d_real + part * 8) = pack8<E>(f);
+      *reinterpret_cast<uint4*>(o_out + acc_row * DR + part * 8) = pack8<E>(f);
   }
   // every thread of a row has read lse_acc before its first thread overwrites it
   __syncwarp();

@@ -46,8 +46,6 @@ struct BwdKernelParams {
   long long accum_batch_stride;  // elements between batch entries of dk_accum / dv_accum
   int accum_overwrite;  // 1: dK / dV REPLACE what dk_accum / dv_accum hold (FMHA_BWD_ACCUM_OVERWRITE)
   int heads, seqlen_q, seqlen_k, seqlen_q_pad;
-  int head_dim;         // elements per row of the tensors (<= D: 96 runs at D = 128, the columns
-                        // beyond it are zero in every tile and are never written out)
   int num_kv_blocks;    // ceil(seqlen_k / 128)
   int num_heads_total;  // batch * heads
   int head_group;       // heads whose CTAs are interleaved in the grid (>= 1)
@@ -94,7 +92,10 @@ struct BwdTraits {
   static constexpr uint32_t kIdescDQ = umma_idesc_f16(128, D, 1, 1, kBf16);    // dQ
 };
 
-template <int D, bool kBf16 = false>
+// DR <= D: elements per row of the tensors.  96 runs at D = 128: the tile loads fill columns
+// 96-127 with zeros, so those columns of dQ, dK and dV are zeros that are never written out, and
+// the fp32 buffers have DR elements per row.
+template <int D, bool kBf16 = false, int DR = D>
 __global__ void __launch_bounds__(512, 1)
     fmha_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                     const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_do,
@@ -492,8 +493,10 @@ __global__ void __launch_bounds__(512, 1)
       reg_alloc<kBwdRegsDq>();
       const uint32_t tDQ = tmem_base + lane_addr + T::kColDQ;
       const bool tl = (r == 0);
-      const int n_chunks = min(D / 32, (p.head_dim + 31) / 32);  // 32-column chunks of a dQ row
-      uint32_t chunk_no = 0;  // chunks staged so far: picks the staging buffer (n_chunks may be odd)
+      constexpr int kChunks = (DR + 31) / 32;  // 32-column chunks of a dQ row
+      // an odd number of chunks per tile breaks the alternation of the two staging buffers by
+      // chunk index: count the chunks staged so far instead
+      [[maybe_unused]] uint32_t chunk_no = 0;
       for (int n = 0; n < cnt; ++n) {
         if (tl) FMHA_TL(1, n, 0);
         // on a time-out keep going (like the compute groups): every later wait returns at once,
@@ -511,13 +514,17 @@ __global__ void __launch_bounds__(512, 1)
         mbar_arrive(smem_u32(&bar_dq_empty));
         if (tl) FMHA_TL(1, n, 2);
 #pragma unroll
-        for (int cc = 0; cc < D / 32; ++cc) {
-          if (cc >= n_chunks) break;  // columns the tensors do not have (uniform over the CTA)
+        for (int cc = 0; cc < kChunks; ++cc) {
           // One reduce-add per 32-column chunk for the whole 128-row tile (16 KB): few large
           // bulk operations instead of many small ones.  The buffer was last used two
           // reduce-adds ago: at most one group may still be reading.
-          const uint32_t stg_buf = stg_smem + (chunk_no & 1u) * 16384;
-          ++chunk_no;
+          uint32_t stg_buf;
+          if constexpr (kChunks % 2 == 0) {
+            stg_buf = stg_smem + (cc & 1) * 16384;
+          } else {
+            stg_buf = stg_smem + (chunk_no & 1u) * 16384;
+            ++chunk_no;
+          }
           if (r == 0) tma_wait_group_read<1>();
           named_bar_sync(2, 128);
           const uint32_t buf_row = stg_buf + r * 128;
@@ -539,7 +546,7 @@ __global__ void __launch_bounds__(512, 1)
             tma_reduce_add_4d(&tm_dqacc, stg_buf, cc * 32,
                               tile_of(n) * T::kBlock, h, z);
             tma_commit_group();
-            if (order_word != nullptr && cc == n_chunks - 1) {
+            if (order_word != nullptr && cc == kChunks - 1) {
               tma_wait_group<0>();  // the adds have been performed, not just read from shared memory
               fence_proxy_async_all();
               __threadfence();
@@ -571,7 +578,7 @@ __global__ void __launch_bounds__(512, 1)
         const bool have = cnt > 0 && kvi < sk;                  // this thread's row has a result
         const bool touch = kvi < p.seqlen_k && (have || p.accum_overwrite != 0);
         float* dst =
-            accum + (size_t)z * p.accum_batch_stride + ((size_t)kvi * p.heads + h) * p.head_dim;
+            accum + (size_t)z * p.accum_batch_stride + ((size_t)kvi * p.heads + h) * DR;
 #pragma unroll
         for (int cc = 0; cc < D / 32; ++cc) {
           uint32_t a[32];
@@ -579,7 +586,7 @@ __global__ void __launch_bounds__(512, 1)
             tmem_ld32(tAcc + cc * 32, a);
             tmem_wait_ld();
           }
-          if (touch && cc * 32 < p.head_dim) {
+          if (touch && cc * 32 < DR) {
 #pragma unroll
             for (int i = 0; i < 32; i += 4) {
               float4 cur = make_float4(0.f, 0.f, 0.f, 0.f);

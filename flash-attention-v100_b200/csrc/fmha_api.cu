@@ -111,6 +111,20 @@ int check_common(int batch, int heads, int seqlen_q, int seqlen_k, int head_dim,
   return FMHA_OK;
 }
 
+// head_dim -> (D, DR) = (width the kernels run at, elements per row of the tensors):
+// 64 -> (64, 64), 96 -> (128, 96), 128 -> (128, 128)
+#define FMHA_DISPATCH_DIMS(head_dim, ...)       \
+  if ((head_dim) == 128) {                      \
+    constexpr int D = 128, DR = 128;            \
+    __VA_ARGS__                                 \
+  } else if ((head_dim) == 96) {                \
+    constexpr int D = 128, DR = 96;             \
+    __VA_ARGS__                                 \
+  } else {                                      \
+    constexpr int D = 64, DR = 64;              \
+    __VA_ARGS__                                 \
+  }
+
 fmha::Strides3 to3(const FmhaStrides& s) { return fmha::Strides3{s.batch, s.row, s.head}; }
 
 int round_up_128(int x) { return (x + 127) / 128 * 128; }
@@ -203,21 +217,22 @@ int launch_fwd(const FmhaFwdParams* p, cudaStream_t stream) {
   return cudaGetLastError() == cudaSuccess ? FMHA_OK : FMHA_ERR_LAUNCH;
 }
 
-template <int D, bool kBf16>
+// D: the head dimension the kernels run at; DR <= D: what the tensors have (p->head_dim)
+template <int D, bool kBf16, int DR = D>
 int launch_bwd(const FmhaBwdParams* p, const BwdWorkspace& w, cudaStream_t stream) {
   using T = fmha::BwdTraits<D, kBf16>;
   using E = typename std::conditional<kBf16, __nv_bfloat16, __half>::type;
   const int Z = p->batch, H = p->heads, Nq = p->seqlen_q, Nk = p->seqlen_k;
   const int Nq_pad = round_up_128(Nq);
-  const int Dr = p->head_dim;  // what the tensors have; D is what the kernels run at
+  constexpr int Dr = DR;
 
   if (!(p->flags & FMHA_BWD_KEEP_WORKSPACE)) {
     const long long rows = (long long)Z * H * Nq_pad;
     constexpr int rows_per_block = 256 / (D / 8);
     const unsigned grid = (unsigned)((rows + rows_per_block - 1) / rows_per_block);
-    fmha::fmha_bwd_preprocess_kernel<D, E><<<grid, 256, 0, stream>>>(
+    fmha::fmha_bwd_preprocess_kernel<D, E, DR><<<grid, 256, 0, stream>>>(
         static_cast<const E*>(p->o), to3(p->o_strides), static_cast<const E*>(p->dout),
-        to3(p->dout_strides), p->lse, w.dq_accum, w.lse2, w.delta, H, Nq, Nq_pad, rows, p->seqused_q, Dr);
+        to3(p->dout_strides), p->lse, w.dq_accum, w.lse2, w.delta, H, Nq, Nq_pad, rows, p->seqused_q);
     if (cudaGetLastError() != cudaSuccess) return FMHA_ERR_LAUNCH;
   }
   if (p->flags & FMHA_BWD_PREPROCESS_ONLY) return FMHA_OK;
@@ -247,7 +262,6 @@ int launch_bwd(const FmhaBwdParams* p, const BwdWorkspace& w, cudaStream_t strea
         p->accum_batch_stride > 0 ? p->accum_batch_stride : (long long)Nk * H * Dr;
     kp.accum_overwrite = (p->flags & FMHA_BWD_ACCUM_OVERWRITE) ? 1 : 0;
     kp.heads = H;
-    kp.head_dim = Dr;
     kp.seqlen_q = Nq;
     kp.seqlen_k = Nk;
     kp.seqlen_q_pad = Nq_pad;
@@ -269,7 +283,7 @@ int launch_bwd(const FmhaBwdParams* p, const BwdWorkspace& w, cudaStream_t strea
     }
     kp.timeline = g_timeline;
     kp.timeline_block = g_timeline_block;
-    auto kernel = fmha::fmha_bwd_kernel<D, kBf16>;
+    auto kernel = fmha::fmha_bwd_kernel<D, kBf16, DR>;
     if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, T::kSmemBytes) !=
         cudaSuccess)
       return FMHA_ERR_LAUNCH;
@@ -282,8 +296,8 @@ int launch_bwd(const FmhaBwdParams* p, const BwdWorkspace& w, cudaStream_t strea
     const long long rows = (long long)Z * Nq * H;
     constexpr int rows_per_block = 256 / (D / 8);
     const unsigned grid = (unsigned)((rows + rows_per_block - 1) / rows_per_block);
-    fmha::fmha_bwd_convert_dq_kernel<D, E><<<grid, 256, 0, stream>>>(
-        w.dq_accum, static_cast<E*>(p->dq), to3(p->dq_strides), H, Nq, p->scale, rows, Dr);
+    fmha::fmha_bwd_convert_dq_kernel<D, E, DR><<<grid, 256, 0, stream>>>(
+        w.dq_accum, static_cast<E*>(p->dq), to3(p->dq_strides), H, Nq, p->scale, rows);
     if (cudaGetLastError() != cudaSuccess) return FMHA_ERR_LAUNCH;
   }
   return FMHA_OK;
@@ -399,8 +413,12 @@ int fmha_bwd(const FmhaBwdParams* p, void* workspace, size_t workspace_bytes, vo
   if (!aligned16(workspace)) return FMHA_ERR_BAD_ALIGNMENT;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (p->dtype == FMHA_DTYPE_BF16)
-    return p->head_dim > 64 ? launch_bwd<128, true>(p, w, s) : launch_bwd<64, true>(p, w, s);
-  return p->head_dim > 64 ? launch_bwd<128, false>(p, w, s) : launch_bwd<64, false>(p, w, s);
+    return p->head_dim == 128 ? launch_bwd<128, true>(p, w, s)
+           : p->head_dim == 96 ? launch_bwd<128, true, 96>(p, w, s)
+                               : launch_bwd<64, true>(p, w, s);
+  return p->head_dim == 128 ? launch_bwd<128, false>(p, w, s)
+         : p->head_dim == 96 ? launch_bwd<128, false, 96>(p, w, s)
+                             : launch_bwd<64, false>(p, w, s);
 }
 
 int fmha_bwd_static_scratch(const FmhaBwdParams* p, void* stream) {
@@ -431,24 +449,21 @@ int fmha_bwd_convert_dq(const void* workspace, void* dq, FmhaStrides dq_strides,
   int rc = check_strides(dq_strides, seqlen_q, heads, batch);
   if (rc) return rc;
   const long long rows = (long long)batch * seqlen_q * heads;
-  const int Dp = head_dim > 64 ? 128 : 64;  // the thread layout the kernels run at
-  const int rows_per_block = 256 / (Dp / 8);
+  const int rows_per_block = 256 / ((head_dim > 64 ? 128 : 64) / 8);  // 16 or 8 threads per row
   const unsigned grid = (unsigned)((rows + rows_per_block - 1) / rows_per_block);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const float* acc = static_cast<const float*>(workspace);
   const fmha::Strides3 sd = to3(dq_strides);
   if (dtype == FMHA_DTYPE_BF16) {
     auto* out = static_cast<__nv_bfloat16*>(dq);
-    if (Dp == 128)
-      fmha::fmha_bwd_convert_dq_kernel<128, __nv_bfloat16><<<grid, 256, 0, s>>>(acc, out, sd, heads, seqlen_q, scale, rows, head_dim);
-    else
-      fmha::fmha_bwd_convert_dq_kernel<64, __nv_bfloat16><<<grid, 256, 0, s>>>(acc, out, sd, heads, seqlen_q, scale, rows, head_dim);
+    FMHA_DISPATCH_DIMS(head_dim,
+                       fmha::fmha_bwd_convert_dq_kernel<D, __nv_bfloat16, DR><<<grid, 256, 0, s>>>(
+                           acc, out, sd, heads, seqlen_q, scale, rows);)
   } else {
     auto* out = static_cast<__half*>(dq);
-    if (Dp == 128)
-      fmha::fmha_bwd_convert_dq_kernel<128, __half><<<grid, 256, 0, s>>>(acc, out, sd, heads, seqlen_q, scale, rows, head_dim);
-    else
-      fmha::fmha_bwd_convert_dq_kernel<64, __half><<<grid, 256, 0, s>>>(acc, out, sd, heads, seqlen_q, scale, rows, head_dim);
+    FMHA_DISPATCH_DIMS(head_dim,
+                       fmha::fmha_bwd_convert_dq_kernel<D, __half, DR><<<grid, 256, 0, s>>>(
+                           acc, out, sd, heads, seqlen_q, scale, rows);)
   }
   return cudaGetLastError() == cudaSuccess ? FMHA_OK : FMHA_ERR_LAUNCH;
 }
@@ -468,29 +483,22 @@ int fmha_merge_rows(float* o_acc, float* lse_acc, const void* o_part, FmhaStride
   int rc = check_strides(o_part_strides, rows, heads, batch);
   if (rc) return rc;
   const long long total = (long long)batch * rows * heads;
-  const int Dp = head_dim > 64 ? 128 : 64;  // the thread layout the kernels run at
-  const int rows_per_block = 256 / (Dp / 8);
+  const int rows_per_block = 256 / ((head_dim > 64 ? 128 : 64) / 8);  // 16 or 8 threads per row
   const unsigned grid = (unsigned)((total + rows_per_block - 1) / rows_per_block);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const fmha::Strides3 sp = to3(o_part_strides);
   if (dtype == FMHA_DTYPE_BF16) {
     auto* part = static_cast<const __nv_bfloat16*>(o_part);
     auto* out = static_cast<__nv_bfloat16*>(o_out);
-    if (Dp == 128)
-      fmha::fmha_merge_kernel<128, __nv_bfloat16><<<grid, 256, 0, s>>>(
-          o_acc, lse_acc, part, sp, lse_part, out, heads, rows, acc_rows, row_offset, total, head_dim);
-    else
-      fmha::fmha_merge_kernel<64, __nv_bfloat16><<<grid, 256, 0, s>>>(
-          o_acc, lse_acc, part, sp, lse_part, out, heads, rows, acc_rows, row_offset, total, head_dim);
+    FMHA_DISPATCH_DIMS(head_dim,
+                       fmha::fmha_merge_kernel<D, __nv_bfloat16, DR><<<grid, 256, 0, s>>>(
+                           o_acc, lse_acc, part, sp, lse_part, out, heads, rows, acc_rows, row_offset, total);)
   } else {
     auto* part = static_cast<const __half*>(o_part);
     auto* out = static_cast<__half*>(o_out);
-    if (Dp == 128)
-      fmha::fmha_merge_kernel<128, __half><<<grid, 256, 0, s>>>(
-          o_acc, lse_acc, part, sp, lse_part, out, heads, rows, acc_rows, row_offset, total, head_dim);
-    else
-      fmha::fmha_merge_kernel<64, __half><<<grid, 256, 0, s>>>(
-          o_acc, lse_acc, part, sp, lse_part, out, heads, rows, acc_rows, row_offset, total, head_dim);
+    FMHA_DISPATCH_DIMS(head_dim,
+                       fmha::fmha_merge_kernel<D, __half, DR><<<grid, 256, 0, s>>>(
+                           o_acc, lse_acc, part, sp, lse_part, out, heads, rows, acc_rows, row_offset, total);)
   }
   return cudaGetLastError() == cudaSuccess ? FMHA_OK : FMHA_ERR_LAUNCH;
 }
@@ -628,23 +636,20 @@ int fmha_sum_partials(const float* const* parts, const int32_t* rows_per_part, i
     list.rows[i] = rows_per_part[i];
   }
   const long long total = (long long)batch * rows * heads;
-  const int Dp = head_dim > 64 ? 128 : 64;  // the thread layout the kernels run at
-  const int rows_per_block = 256 / (Dp / 8);
+  const int rows_per_block = 256 / ((head_dim > 64 ? 128 : 64) / 8);  // 16 or 8 threads per row
   const unsigned grid = (unsigned)((total + rows_per_block - 1) / rows_per_block);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const fmha::Strides3 so = to3(out_strides);
   if (dtype == FMHA_DTYPE_BF16) {
     auto* o = static_cast<__nv_bfloat16*>(out);
-    if (Dp == 128)
-      fmha::sum_partials_kernel<128, __nv_bfloat16><<<grid, 256, 0, s>>>(list, o, so, heads, rows, total, head_dim);
-    else
-      fmha::sum_partials_kernel<64, __nv_bfloat16><<<grid, 256, 0, s>>>(list, o, so, heads, rows, total, head_dim);
+    FMHA_DISPATCH_DIMS(head_dim,
+                       fmha::sum_partials_kernel<D, __nv_bfloat16, DR><<<grid, 256, 0, s>>>(
+                           list, o, so, heads, rows, total);)
   } else {
     auto* o = static_cast<__half*>(out);
-    if (Dp == 128)
-      fmha::sum_partials_kernel<128, __half><<<grid, 256, 0, s>>>(list, o, so, heads, rows, total, head_dim);
-    else
-      fmha::sum_partials_kernel<64, __half><<<grid, 256, 0, s>>>(list, o, so, heads, rows, total, head_dim);
+    FMHA_DISPATCH_DIMS(head_dim,
+                       fmha::sum_partials_kernel<D, __half, DR><<<grid, 256, 0, s>>>(
+                           list, o, so, heads, rows, total);)
   }
   return cudaGetLastError() == cudaSuccess ? FMHA_OK : FMHA_ERR_LAUNCH;
 }

@@ -67,16 +67,16 @@ struct PartList {
 
 // out (16-bit, strided) = sum over parts of fp32 (Z, rows, H, D) buffers, each dense with
 // `rows` rows per batch entry although only its first rows[s] rows count.  D = 64 or 128 sets the
-// threads per row; the tensors have d_real <= D elements per row (96 runs at D = 128).
-template <int D, typename E>
+// threads per row; the tensors have DR <= D elements per row (96 runs at D = 128).
+template <int D, typename E, int DR = D>
 __global__ void __launch_bounds__(256)
     sum_partials_kernel(PartList parts, E* __restrict__ out, Strides3 so, int heads, int rows,
-                        long long total_rows, int d_real) {
+                        long long total_rows) {
   constexpr int kGroup = D / 8;
   constexpr int kRowsPerBlock = 256 / kGroup;
   const int part = threadIdx.x % kGroup;
   const long long row_id = (long long)blockIdx.x * kRowsPerBlock + threadIdx.x / kGroup;
-  if (row_id >= total_rows || part * 8 >= d_real) return;
+  if (row_id >= total_rows || (DR != D && part * 8 >= DR)) return;
   // row_id enumerates (z, n, h)
   const int h = (int)(row_id % heads);
   const long long zn = row_id / heads;
@@ -86,7 +86,7 @@ __global__ void __launch_bounds__(256)
 #pragma unroll 4
   for (int s = 0; s < parts.n; ++s) {
     if (n < parts.rows[s]) {
-      const float4* src = reinterpret_cast<const float4*>(parts.ptr[s] + row_id * d_real + part * 8);
+      const float4* src = reinterpret_cast<const float4*>(parts.ptr[s] + row_id * DR + part * 8);
       const float4 a = src[0], b = src[1];
       f[0] += a.x, f[1] += a.y, f[2] += a.z, f[3] += a.w;
       f[4] += b.x, f[5] += b.y, f[6] += b.z, f[7] += b.w;
