@@ -172,7 +172,10 @@ __global__ void __launch_bounds__(256)
       ln = mx + __logf(ea + eb);
     }
     float4* acc = reinterpret_cast<float4*>(o_acc + acc_row * DR + part * 8);
-    const float4 a0 = acc[0], a1 = acc[1];
+    // a row whose accumulated LSE is -inf holds nothing yet: its o_acc is not read (it may be
+    // uninitialised memory), so the first merge of a row initialises it
+    float4 a0 = make_float4(0.f, 0.f, 0.f, 0.f), a1 = a0;
+    if (la > -CUDART_INF_F) a0 = acc[0], a1 = acc[1];
     const uint4 up =
         *reinterpret_cast<const uint4*>(o_part + z * sp.batch + q * sp.row + h * sp.head + part * 8);
     float fp[8];

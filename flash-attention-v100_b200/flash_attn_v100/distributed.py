@@ -121,7 +121,8 @@ class CudaBackend:
 
     def new_accumulators(self, q):
         Z, N, H, D = q.shape
-        o_acc = torch.zeros((Z, N, H, D), dtype=torch.float32, device=q.device)
+        # rows start with LSE = -inf, for which the merge does not read o_acc: no zero fill
+        o_acc = torch.empty((Z, N, H, D), dtype=torch.float32, device=q.device)
         lse_acc = torch.full((Z, H, N), float("-inf"), dtype=torch.float32, device=q.device)
         return o_acc, lse_acc
 

@@ -236,6 +236,8 @@ int fmha_bwd_convert_dq(const void* workspace, void* dq, FmhaStrides dq_strides,
  * o_acc fp32 (Z, N, H, D) contiguous, lse_acc fp32 (Z, H, N) contiguous; o_part 16-bit (`dtype`)
  * with strides, lse_part fp32 (Z, H, N).  rows = N.  When `o_out` is not NULL the merged result
  * is also written in `dtype` as (Z, N, H, D) contiguous (used on the last ring step).
+ * A row with lse_acc = -inf holds nothing yet: its o_acc is not read, so accumulators start as
+ * lse_acc = -inf and o_acc uninitialised.
  * No counterpart in the reference (it has no multi-GPU path). */
 int fmha_merge(float* o_acc, float* lse_acc, const void* o_part, FmhaStrides o_part_strides,
                const float* lse_part, void* o_out, int32_t batch, int32_t heads, int32_t rows,

@@ -26,7 +26,8 @@ def _intact(buf, fill):
 
 @pytest.mark.parametrize("Z,Nq,Nk,H,D,causal,shift", [
     (2, 96, 96, 3, 64, True, 0), (1, 160, 416, 2, 128, False, 0), (3, 288, 32, 2, 128, True, -64),
-    (1, 2016, 2016, 2, 128, True, 0), (2, 32, 544, 1, 64, True, 512),
+    (1, 2016, 2016, 2, 128, True, 0), (2, 32, 544, 1, 64, True, 512), (2, 160, 288, 3, 96, True, 0),
+    (1, 416, 160, 2, 96, False, 0),
 ])
 def test_outputs_do_not_write_outside_their_tensors(Z, Nq, Nk, H, D, causal, shift):
     from flash_attn_v100 import cabi

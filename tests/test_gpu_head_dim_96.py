@@ -127,7 +127,7 @@ def test_ring_building_blocks():
     qd, kd, vd, dod = q.cuda(), k.cuda(), v.cuda(), dout.cuda()
     half = N // 2
     # forward: two key halves merged through LSE
-    o_acc = torch.zeros((Z, N, H, D), dtype=torch.float32, device="cuda")
+    o_acc = torch.full((Z, N, H, D), float("nan"), dtype=torch.float32, device="cuda")  # never read while LSE = -inf
     lse_acc = torch.full((Z, H, N), float("-inf"), device="cuda")
     out16 = torch.empty((Z, N, H, D), dtype=torch.float16, device="cuda")
     for i, lo in enumerate((0, half)):

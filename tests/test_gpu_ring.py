@@ -19,12 +19,13 @@ sys.path.insert(0, PKG)
 
 def test_merge_kernel_matches_oracle_merge():
     """fmha_merge: two partial results over disjoint key halves merged through LSE equal the
-    attention over all keys."""
+    attention over all keys.  The accumulators start as LSE = -inf and an o_acc that is never
+    read for such rows (NaN here): the first merge initialises them."""
     from flash_attn_v100 import cabi
 
     q, k, v, _ = oracle.make_inputs(2, 256, 3, 128, seed=5, n_k=512)
     qd, kd, vd = q.cuda(), k.cuda(), v.cuda()
-    o_acc = torch.zeros((2, 256, 3, 128), dtype=torch.float32, device="cuda")
+    o_acc = torch.full((2, 256, 3, 128), float("nan"), dtype=torch.float32, device="cuda")
     lse_acc = torch.full((2, 3, 256), float("-inf"), device="cuda")
     for lo in (0, 256):
         o_p, l_p = cabi.fwd(qd, kd[:, lo:lo + 256], vd[:, lo:lo + 256], 0.1, False)
