@@ -207,6 +207,49 @@ def run_reference(args):
     print(json.dumps(line), flush=True)
 
 
+def cpus_near_gpu(torch, dev):
+    """The CPUs of the NUMA node the GPU hangs off (its PCI device's local_cpulist in sysfs),
+    restricted to those this process may run on; None when that cannot be told."""
+    try:
+        props = torch.cuda.get_device_properties(dev)
+        path = "/sys/bus/pci/devices/%04x:%02x:%02x.0/local_cpulist" % (
+            props.pci_domain_id, props.pci_bus_id, props.pci_device_id)
+        with open(path) as f:
+            text = f.read().strip()
+        cpus = set()
+        for part in text.split(","):
+            lo, _, hi = part.partition("-")
+            cpus.update(range(int(lo), int(hi or lo) + 1))
+        cpus &= os.sched_getaffinity(0)
+        return cpus or None
+    except (AttributeError, OSError, ValueError, RuntimeError):
+        return None
+
+
+class near_gpu:
+    """Context: the calling thread runs on the GPU's own NUMA node, so that pinned host buffers
+    allocated inside are placed in the memory the GPU's PCIe root port reaches without crossing
+    sockets.  The previous affinity is put back on exit.  Does nothing when the node is unknown."""
+
+    def __init__(self, torch, dev):
+        self.cpus = cpus_near_gpu(torch, dev)
+        self.old = None
+
+    def __enter__(self):
+        if self.cpus:
+            try:
+                self.old = os.sched_getaffinity(0)
+                os.sched_setaffinity(0, self.cpus)
+            except OSError:
+                self.old = None
+        return self
+
+    def __exit__(self, *exc):
+        if self.old is not None:
+            os.sched_setaffinity(0, self.old)
+        return False
+
+
 def time_events(fn, iters, torch):
     """Average device milliseconds of fn() over `iters` back-to-back calls (CUDA events on the
     current stream, synchronised on both sides)."""
@@ -559,7 +602,9 @@ def run_ours(args):
     if strong:
         Z //= world
     # every rank draws its own batch (seed = rank): no communication
-    hq, hk, hv, hdo = (t.pin_memory() for t in oracle.make_inputs(Z, N, H, D, seed=rank))
+    host_inputs = oracle.make_inputs(Z, N, H, D, seed=rank)
+    with near_gpu(torch, dev) as placement:
+        hq, hk, hv, hdo = (t.pin_memory() for t in host_inputs)
     q, k, v, dout = (t.to(dev) for t in (hq, hk, hv, hdo))
     out = torch.empty_like(q)
     lse = torch.empty((Z, H, N), dtype=torch.float32, device=dev)
@@ -642,7 +687,8 @@ def run_ours(args):
     # from pinned host memory and its own results back; the copies of neighbouring steps overlap
     # with each other and with the kernels (PCIe is full duplex): inputs of step i+1 go up while
     # step i computes and the results of step i-1 come down, through two sets of device buffers.
-    h_out, h_dq, h_dk, h_dv = (torch.empty_like(hq).pin_memory() for _ in range(4))
+    with near_gpu(torch, dev):
+        h_out, h_dq, h_dk, h_dv = (torch.empty_like(hq).pin_memory() for _ in range(4))
     s_up, s_down = torch.cuda.Stream(), torch.cuda.Stream()
     sets = [{"in": [torch.empty_like(q) for _ in range(4)], "res": None,
              "up": torch.cuda.Event(), "done": torch.cuda.Event(), "down": torch.cuda.Event()}
@@ -762,7 +808,10 @@ def run_ours(args):
             "e2e": {"value": world * (f_fwd + f_bwd) / (ms_e2e * 1e-3) / 1e12, "unit": "TFLOPS",
                     "ms_per_step": ms_e2e, "h2d_bytes_per_step": 4 * tensor_bytes,
                     "d2h_bytes_per_step": 4 * tensor_bytes, "api": "flash_attn_v100.flash_attn_func + backward",
-                    "overlap": "copies of neighbouring steps overlap (two buffer sets, three streams)"},
+                    "overlap": "copies of neighbouring steps overlap (two buffer sets, three streams)",
+                    "pcie_gbs_each_way": 4 * tensor_bytes / (ms_e2e * 1e-3) / 1e9,
+                    "host_buffers": ("pinned, allocated from the GPU's NUMA node (%d CPUs)" % len(placement.cpus))
+                    if placement.cpus else "pinned, placement left to the OS"},
             "gpu_launches": 4 * args.steps,  # fwd, bwd preprocess, bwd main, bwd convert per step of a region
             "clocks": clocks_kernels,
         }
