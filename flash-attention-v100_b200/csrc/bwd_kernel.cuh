@@ -49,6 +49,7 @@ struct BwdKernelParams {
   int num_kv_blocks;    // ceil(seqlen_k / 128)
   int num_heads_total;  // batch * heads
   int head_group;       // heads whose CTAs are interleaved in the grid (>= 1)
+  int q_tile_begin;     // query tiles before this one take no part (FmhaBwdParams.q_row_begin / 128)
   float scale, scale_log2;
   int causal, causal_shift;
   int* status;
@@ -157,8 +158,9 @@ __global__ void __launch_bounds__(512, 1)
     const long long first_row = (long long)kv0 - p.causal_shift;
     i_begin = first_row <= 0 ? 0 : (int)min((long long)nq_tiles, first_row / T::kBlock);
   }
+  i_begin = max(i_begin, p.q_tile_begin);
   // query tiles this CTA walks (may be 0; a KV tile that is all padding walks none)
-  const int cnt = kv0 < sk ? nq_tiles - i_begin : 0;
+  const int cnt = kv0 < sk ? max(0, nq_tiles - i_begin) : 0;
   // the n-th query tile this CTA visits
   auto tile_of = [&](int n) { return i_begin + n; };
 

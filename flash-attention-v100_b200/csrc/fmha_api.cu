@@ -268,6 +268,7 @@ int launch_bwd(const FmhaBwdParams* p, const BwdWorkspace& w, cudaStream_t strea
     kp.num_kv_blocks = (Nk + 127) / 128;
     kp.num_heads_total = Z * H;
     kp.head_group = bwd_head_group(kp.num_kv_blocks, p->causal != 0);
+    kp.q_tile_begin = p->q_row_begin / 128;
     kp.scale = p->scale;
     kp.scale_log2 = p->scale * 1.4426950408889634f;
     kp.causal = p->causal ? 1 : 0;
@@ -401,6 +402,9 @@ int fmha_bwd(const FmhaBwdParams* p, void* workspace, size_t workspace_bytes, vo
     return rc;
   if (p->dv_accum == nullptr && (rc = check_strides(p->dv_strides, p->seqlen_k, p->heads, p->batch)))
     return rc;
+  if (p->q_row_begin < 0 || p->q_row_begin % 128 != 0 ||
+      (p->q_row_begin != 0 && p->q_row_begin >= p->seqlen_q))
+    return FMHA_ERR_BAD_SHAPE;
   if (p->dk_accum != nullptr || p->dv_accum != nullptr) {
     // the epilogue adds with 16-byte accesses at accum + z * stride: the stride must keep them
     // aligned, and batch entries must not overlap

@@ -69,6 +69,7 @@ class FmhaBwdParams(ctypes.Structure):
         ("scale", ctypes.c_float), ("causal", ctypes.c_int32), ("causal_shift", ctypes.c_int32),
         ("flags", ctypes.c_int32), ("status", ctypes.c_void_p), ("dtype", ctypes.c_int32),
         ("seqused_q", ctypes.c_void_p), ("seqused_k", ctypes.c_void_p),
+        ("q_row_begin", ctypes.c_int32),
     ]
 
 
@@ -220,7 +221,8 @@ def fwd(q, k, v, scale: float, causal: bool = False, causal_shift: int = 0,
 
 
 def bwd_params(q, k, v, o, dout, lse, dq, dk, dv, scale, causal, causal_shift=0, dk_accum=None,
-               dv_accum=None, flags=0, status=None, seqused_q=None, seqused_k=None) -> FmhaBwdParams:
+               dv_accum=None, flags=0, status=None, seqused_q=None, seqused_k=None,
+               q_row_begin=0) -> FmhaBwdParams:
     p = FmhaBwdParams()
     p.q, p.k, p.v, p.dout, p.lse = q.data_ptr(), k.data_ptr(), v.data_ptr(), dout.data_ptr(), lse.data_ptr()
     p.o = None if o is None else o.data_ptr()
@@ -256,6 +258,7 @@ def bwd_params(q, k, v, o, dout, lse, dq, dk, dv, scale, causal, causal_shift=0,
     p.dtype = _dtype_code(q)
     p.seqused_q = _seqused_ptr(seqused_q, q.shape[0])
     p.seqused_k = _seqused_ptr(seqused_k, q.shape[0])
+    p.q_row_begin = int(q_row_begin)
     return p
 
 
@@ -267,9 +270,10 @@ def bwd_workspace_bytes(Z: int, Nq: int, H: int, D: int) -> int:
 
 def bwd(q, k, v, o, dout, lse, scale: float, causal: bool = False, causal_shift: int = 0,
         dq=None, dk=None, dv=None, dk_accum=None, dv_accum=None, workspace=None, flags: int = 0,
-        status=None, stream=None, seqused_q=None, seqused_k=None):
+        status=None, stream=None, seqused_q=None, seqused_k=None, q_row_begin: int = 0):
     """dQ, dK, dV through ``fmha_bwd``.  Outputs and workspace are allocated with torch unless
-    passed in; with ``dk_accum`` / ``dv_accum`` (fp32) the fp16 dK / dV are not produced."""
+    passed in; with ``dk_accum`` / ``dv_accum`` (fp32) the fp16 dK / dV are not produced.
+    ``q_row_begin`` (a multiple of 128): query rows before it take no part in the call."""
     _require_cuda_half(q, k, v, o, dout, dq, dk, dv)
     Z, Nq, H, D = q.shape
     if dq is None and not (flags & (FMHA_BWD_SKIP_DQ_CONVERT | FMHA_BWD_PREPROCESS_ONLY)):
@@ -281,7 +285,7 @@ def bwd(q, k, v, o, dout, lse, scale: float, causal: bool = False, causal_shift:
     if workspace is None:
         workspace = torch.empty(bwd_workspace_bytes(Z, Nq, H, D), dtype=torch.uint8, device=q.device)
     p = bwd_params(q, k, v, o, dout, lse, dq, dk, dv, scale, causal, causal_shift, dk_accum,
-                   dv_accum, flags, status, seqused_q, seqused_k)
+                   dv_accum, flags, status, seqused_q, seqused_k, q_row_begin)
     with torch.cuda.device(q.device):
         _check(load_library().fmha_bwd(ctypes.byref(p), ctypes.c_void_p(workspace.data_ptr()),
                                        workspace.numel() * workspace.element_size(),

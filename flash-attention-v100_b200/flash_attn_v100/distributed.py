@@ -134,26 +134,30 @@ class CudaBackend:
     def finish(self, o_acc, lse_acc, dtype):
         return o_acc.to(dtype), lse_acc
 
-    def new_bwd_state(self, q, device=None):
+    def new_bwd_state(self, q, device=None, half: bool = True):
+        """Workspaces of a ring backward: one for steps over all query rows and (``half``) one
+        for steps over the second half of them given as a tensor of its own."""
         Z, N, H, D = q.shape
         device = q.device if device is None else device
         nbytes = self.cabi.bwd_workspace_bytes
         return {
             "full": torch.empty(nbytes(Z, N, H, D), dtype=torch.uint8, device=device),
-            "half": torch.empty(nbytes(Z, N // 2, H, D), dtype=torch.uint8, device=device),
+            "half": torch.empty(nbytes(Z, N // 2, H, D) if half else 0, dtype=torch.uint8, device=device),
             "full_used": False, "half_used": False,
         }
 
     def bwd_step(self, state, which, q, k, v, o, dout, lse, scale, causal, dk_acc, dv_acc,
-                 overwrite: bool = False):
+                 overwrite: bool = False, causal_shift: int = 0, q_row_begin: int = 0):
         """Accumulate this block's dQ into the workspace ``which`` ('full' or 'half' query rows)
-        and its dK/dV into the fp32 buffers (``overwrite``: in place of what they hold)."""
+        and its dK/dV into the fp32 buffers (``overwrite``: in place of what they hold).
+        ``q_row_begin``: the query rows before it take no part (q, o, dout, lse are those of all
+        rows, the workspace is 'full')."""
         c = self.cabi
         flags = c.FMHA_BWD_SKIP_DQ_CONVERT | (c.FMHA_BWD_KEEP_WORKSPACE if state[which + "_used"] else 0)
         if overwrite:
             flags |= c.FMHA_BWD_ACCUM_OVERWRITE
-        c.bwd(q, k, v, o, dout, lse, scale, causal, dq=None, dk_accum=dk_acc, dv_accum=dv_acc,
-              workspace=state[which], flags=flags, status=self.status)
+        c.bwd(q, k, v, o, dout, lse, scale, causal, causal_shift, dq=None, dk_accum=dk_acc, dv_accum=dv_acc,
+              workspace=state[which], flags=flags, status=self.status, q_row_begin=q_row_begin)
         state[which + "_used"] = True
 
     def bwd_finish(self, state, q, k, v, o, dout, lse, scale):
@@ -161,7 +165,8 @@ class CudaBackend:
         c = self.cabi
         Z, N, H, D = q.shape
         half = N // 2
-        dq = torch.zeros_like(q)
+        # the conversion of the 'full' workspace writes every row of dq
+        dq = torch.empty_like(q) if state["full_used"] else torch.zeros_like(q)
         if state["full_used"]:
             self._convert(state["full"], dq, scale, q.shape)
         if state["half_used"]:

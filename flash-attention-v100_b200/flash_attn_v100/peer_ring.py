@@ -75,8 +75,12 @@ class PeerRing:
             self.part = [torch.empty((2,) + self.shape, dtype=torch.float32, device=self.device) for _ in range(2)]
             self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
             self.backend.status = self.status
+            # Steps in which only the second half of the queries sees a block run on all rows'
+            # tensors with q_row_begin (a multiple of the 128-row tile) and share the one
+            # workspace; shards too short for that fall back to a workspace of their own.
+            self.row_begin_ok = (rows // 2) % 128 == 0
             self.bwd_state = self.backend.new_bwd_state(torch.empty(self.shape, dtype=dtype, device="meta"),
-                                                        device=self.device)
+                                                        device=self.device, half=not self.row_begin_ok)
             self.pull_stream = torch.cuda.Stream(device=self.device, priority=-1)
             self.push_stream = torch.cuda.Stream(device=self.device, priority=-1)
             torch.cuda.synchronize(self.device)
@@ -254,44 +258,77 @@ class PeerRing:
         ev_free = [torch.cuda.Event(), torch.cuda.Event()]
         ev_part = [torch.cuda.Event(), torch.cuda.Event()]
         ev_pushed = [torch.cuda.Event(), torch.cuda.Event()]
-        lse_half = lse[:, :, half:].contiguous()
+        begin_ok = self.row_begin_ok
+        lse_half = None if begin_ok else lse[:, :, half:].contiguous()
         if world > 1:
             self.pull_stream.wait_stream(cs)
             self._pull(side, "kv_b", 1, cur, causal, ev_free, ev_ready, exchange)
         slot_bytes = 2 * Z * rows * H * D * 4
         entry = rows * H * D * 4
+        mine = self.slots[rank]  # my own contribution goes straight into my slot
+
+        def second_half_step(kb, vb, kv_rows, causal_block, target, shift=0):
+            """dQ of the second half of the query rows, dK / dV of key rows ``kv_rows``."""
+            if begin_ok:
+                be.bwd_step(state, "full", q, kb[:, kv_rows], vb[:, kv_rows], out, dout, lse, scale,
+                            causal_block, target[0][:, kv_rows], target[1][:, kv_rows], overwrite=True,
+                            causal_shift=shift, q_row_begin=half)
+            else:
+                be.bwd_step(state, "half", q[:, half:], kb[:, kv_rows], vb[:, kv_rows], out[:, half:],
+                            dout[:, half:], lse_half, scale, causal_block, target[0][:, kv_rows],
+                            target[1][:, kv_rows], overwrite=True, causal_shift=shift + (half if causal_block else 0))
+
+        # The local block is done in two parts, a short one first and the long one last, so that
+        # the first pull of a visiting block and the last push of a partial result both have a
+        # kernel running beside them: (second half of the queries) x (second half of the keys)
+        # now, all queries x (first half of the keys) after the last visiting block.  Each part
+        # overwrites its own key rows of my slot.  With a causal mask the local block is causal
+        # over the local row numbers (the second chunk of a zig-zag shard is later in the
+        # sequence than the first); without one the two parts are simply two key halves.
+        split_local = world > 1
+        lo, hi = slice(0, half), slice(half, rows)
+        if not split_local:
+            be.bwd_step(state, "full", q, k, v, out, dout, lse, scale, causal, mine[0], mine[1], overwrite=True)
+        elif causal:
+            # key j (local number) is visible to query i iff j <= i: with the keys given from
+            # row `half` on that is j' <= i - half
+            second_half_step(k, v, hi, True, mine, shift=-half)
+        else:
+            be.bwd_step(state, "full", q, k[:, hi], v[:, hi], out, dout, lse, scale, False,
+                        mine[0][:, hi], mine[1][:, hi], overwrite=True)
         for t, (src, q_rows, kv_rows, causal_block) in enumerate(self.fd.ring_step_shapes(rank, world, causal, rows)):
             if t == 0:
-                kb, vb = k, v
-                target = self.slots[rank]  # my own contribution goes straight into my slot
-            else:
-                cs.wait_event(ev_ready[t % 2])
-                kb, vb = side.recv[t % 2][0], side.recv[t % 2][1]
-                target = self.part[t % 2]
-                if t >= 3:
-                    cs.wait_event(ev_pushed[t % 2])  # the push of step t - 2 has read the buffer
+                continue
+            cs.wait_event(ev_ready[t % 2])
+            kb, vb = side.recv[t % 2][0], side.recv[t % 2][1]
+            target = self.part[t % 2]
+            if t >= 3:
+                cs.wait_event(ev_pushed[t % 2])  # the push of step t - 2 has read the buffer
             first_half_only = kv_rows.stop < rows
             if t + 1 < world:
                 self._pull(side, "kv_b", t + 1, cur, causal, ev_free, ev_ready, exchange)
-            whole_q = q_rows.start == 0
-            be.bwd_step(state, "full" if whole_q else "half", q[:, q_rows], kb[:, kv_rows], vb[:, kv_rows],
-                        out[:, q_rows], dout[:, q_rows], lse if whole_q else lse_half, scale, causal_block,
-                        target[0][:, kv_rows], target[1][:, kv_rows], overwrite=True)
-            if t >= 1:
-                ev_free[t % 2].record(cs)
-                ev_part[t % 2].record(cs)
-                if exchange:
-                    with torch.cuda.stream(self.push_stream):
-                        ps = self.push_stream
-                        ps.wait_event(ev_part[t % 2])
-                        c.peer_wait([self._flag(rank, _GRAD_FREE, src)], gcur, self.status, self.timeout_ms, ps)
-                        dst = self.peer[src]["slots"] + rank * slot_bytes
-                        if first_half_only:
-                            c.peer_copy_2d(dst, entry, target.data_ptr(), entry, entry // 2, 2 * Z, ps)
-                        else:
-                            c.peer_copy(dst, target.data_ptr(), slot_bytes, ps)
-                        c.peer_signal([self._flag(src, _GRAD_READY, rank)], gcur, ps)
-                        ev_pushed[t % 2].record(ps)
+            if q_rows.start == 0:
+                be.bwd_step(state, "full", q, kb[:, kv_rows], vb[:, kv_rows], out, dout, lse, scale,
+                            causal_block, target[0][:, kv_rows], target[1][:, kv_rows], overwrite=True)
+            else:
+                second_half_step(kb, vb, kv_rows, causal_block, target)
+            ev_free[t % 2].record(cs)
+            ev_part[t % 2].record(cs)
+            if exchange:
+                with torch.cuda.stream(self.push_stream):
+                    ps = self.push_stream
+                    ps.wait_event(ev_part[t % 2])
+                    c.peer_wait([self._flag(rank, _GRAD_FREE, src)], gcur, self.status, self.timeout_ms, ps)
+                    dst = self.peer[src]["slots"] + rank * slot_bytes
+                    if first_half_only:
+                        c.peer_copy_2d(dst, entry, target.data_ptr(), entry, entry // 2, 2 * Z, ps)
+                    else:
+                        c.peer_copy(dst, target.data_ptr(), slot_bytes, ps)
+                    c.peer_signal([self._flag(src, _GRAD_READY, rank)], gcur, ps)
+                    ev_pushed[t % 2].record(ps)
+        if split_local:
+            be.bwd_step(state, "full", q, k[:, lo], v[:, lo], out, dout, lse, scale, causal,
+                        mine[0][:, lo], mine[1][:, lo], overwrite=True)
         # every other rank's contribution to my block has arrived; add them up
         c.peer_wait([self._flag(rank, _GRAD_READY, p) for p in others], gcur, self.status, self.timeout_ms, cs)
         sources = list(range(world)) if exchange else [rank]

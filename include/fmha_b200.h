@@ -143,6 +143,13 @@ typedef struct {
    * the padding rows of dq, dk and dv are written as zeros. */
   const int32_t* seqused_q;
   const int32_t* seqused_k;
+  /* Query rows before this index take no part in the call: nothing is added to their dQ, and
+   * they contribute nothing to dK / dV.  0 = all rows; otherwise a multiple of 128 below
+   * seqlen_q (FMHA_ERR_BAD_SHAPE if not).  q, o, dout, lse and the workspace stay those of ALL
+   * seqlen_q rows, so calls over different row ranges share one workspace (ring attention: a
+   * step in which only the second half of the local queries sees the visiting block).  The
+   * causal mask keeps counting rows from 0. */
+  int32_t q_row_begin;
 } FmhaBwdParams;
 
 #define FMHA_BWD_KEEP_WORKSPACE 1

@@ -114,6 +114,15 @@ def test_backward_workspace_size_and_validation(built_library):
     p.flags = cabi.FMHA_BWD_KEEP_WORKSPACE | cabi.FMHA_BWD_PREPROCESS_ONLY
     assert lib.fmha_bwd(ctypes.byref(p), 0x2000, 1 << 30, None) == 6
     p.flags = 0
+    # q_row_begin: a multiple of the 128-row tile below seqlen_q, or 0
+    p.seqlen_q = 512
+    for bad in (64, 512, 640, -128):
+        p.q_row_begin = bad
+        assert lib.fmha_bwd(ctypes.byref(p), 0x2000, 16, None) == 3, bad
+    for good in (0, 128, 384):
+        p.q_row_begin = good
+        assert lib.fmha_bwd(ctypes.byref(p), 0x2000, 16, None) == 6, good  # passes on to the workspace check
+    p.q_row_begin, p.seqlen_q = 0, 32
     p.head_dim = 100
     assert lib.fmha_bwd(ctypes.byref(p), 0x2000, 1 << 30, None) == 2
 

@@ -103,6 +103,50 @@ def test_backward_overwrites_the_fp32_buffers_when_asked():
             assert not big_k[:, Nq:Nk].any() and not big_v[:, Nq:Nk].any()  # unseen keys: zeros
 
 
+def test_backward_over_a_row_range_of_the_queries_shares_the_workspace():
+    """q_row_begin: query rows before it take no part.  (a) Alone: dQ of the excluded rows stays
+    zero, dQ of the others and dK / dV equal those of an attention over the included rows only.
+    (b) The way ring attention splits its local causal block: (second half of the queries) x
+    (second half of the keys) first, all queries x (first half of the keys) second, one
+    workspace, equals the causal backward in one call."""
+    from flash_attn_v100 import cabi
+
+    Z, N, H, D = 2, 512, 3, 128
+    half = N // 2
+    q, k, v, dout = oracle.make_inputs(Z, N, H, D, seed=23)
+    qd, kd, vd, dod = q.cuda(), k.cuda(), v.cuda(), dout.cuda()
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    # (a) non-causal, rows [half, N) only
+    out, lse = cabi.fwd(qd, kd, vd, 0.1, False, status=status)
+    dq, dk, dv = cabi.bwd(qd, kd, vd, out, dod, lse, 0.1, False, q_row_begin=half, status=status)
+    ref = oracle.attention_fwd_bwd(q[:, half:], k, v, dout[:, half:], 0.1, False)
+    assert not dq[:, :half].any()
+    for got, want in ((dq[:, half:], ref[2]), (dk, ref[3]), (dv, ref[4])):
+        assert oracle.rel_l2(got.float().cpu(), want) <= helpers.TOL_GRAD_REL_L2
+    # (b) the local causal block in two parts
+    out, lse = cabi.fwd(qd, kd, vd, 0.1, True, status=status)
+    ws = torch.empty(cabi.bwd_workspace_bytes(Z, N, H, D), dtype=torch.uint8, device="cuda")
+    dk32 = torch.full((Z, N, H, D), float("nan"), device="cuda")
+    dv32 = torch.full((Z, N, H, D), float("nan"), device="cuda")
+    base = cabi.FMHA_BWD_SKIP_DQ_CONVERT | cabi.FMHA_BWD_ACCUM_OVERWRITE
+    cabi.bwd(qd, kd[:, half:], vd[:, half:], out, dod, lse, 0.1, True, -half, dq=None,
+             dk_accum=dk32[:, half:], dv_accum=dv32[:, half:], workspace=ws, flags=base, status=status,
+             q_row_begin=half)
+    cabi.bwd(qd, kd[:, :half], vd[:, :half], out, dod, lse, 0.1, True, 0, dq=None,
+             dk_accum=dk32[:, :half], dv_accum=dv32[:, :half], workspace=ws,
+             flags=base | cabi.FMHA_BWD_KEEP_WORKSPACE, status=status)
+    dq = torch.empty_like(qd)
+    cabi.bwd_convert_dq(ws, dq, 0.1)
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0
+    ref = oracle.attention_fwd_bwd(q, k, v, dout, 0.1, True)
+    helpers.check_against_oracle((out.cpu(), lse.cpu(), dq.cpu(), dk32.cpu(), dv32.cpu()), ref, "local block in two parts")
+    # a begin that is no multiple of the tile, or beyond the rows, is refused
+    for bad in (64, N, -128):
+        with pytest.raises(RuntimeError):
+            cabi.bwd(qd, kd, vd, out, dod, lse, 0.1, True, q_row_begin=bad)
+
+
 def test_backward_in_three_separate_calls_matches_one_call():
     """Preprocess only, then the fused kernel on the kept workspace, then the dQ conversion: the
     same bits as one fmha_bwd call (dK/dV bitwise, dQ up to the order of its fp32 additions)."""
@@ -261,6 +305,14 @@ def test_ring_attention_on_gpus(transport, causal, tmp_path):
     pushed to theirs ("peer").  World size = visible GPUs (2, 4 or 8); world size 1 exercises the
     same code path without a peer.  Two passes in a row: the second reuses every buffer and flag."""
     _run_ring(tmp_path, causal, transport, Z=2, rows_per_rank=512, H=4, D=128, repeats=2)
+
+
+@pytest.mark.parametrize("causal", [True, False])
+def test_ring_attention_shards_whose_half_is_no_multiple_of_the_tile(causal, tmp_path):
+    """320 rows per rank: half a shard (160 rows) is no multiple of the 128-row tile, so the steps
+    over the second half of the queries run on sliced tensors with a workspace of their own
+    instead of q_row_begin."""
+    _run_ring(tmp_path, causal, "peer", Z=2, rows_per_rank=320, H=2, D=64, repeats=2)
 
 
 @pytest.mark.parametrize("transport", ["nccl", "peer"])
