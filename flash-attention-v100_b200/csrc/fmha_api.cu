@@ -658,6 +658,49 @@ int fmha_sum_partials(const float* const* parts, const int32_t* rows_per_part, i
   return cudaGetLastError() == cudaSuccess ? FMHA_OK : FMHA_ERR_LAUNCH;
 }
 
+int fmha_merge_parts(const void* const* o_parts, const float* const* lse_parts,
+                     const int32_t* row_offset, const int32_t* rows_per_part, int32_t n_parts,
+                     void* o_out, float* lse_out, int32_t batch, int32_t heads, int32_t rows,
+                     int32_t head_dim, int32_t dtype, void* stream) {
+  if (o_parts == nullptr || lse_parts == nullptr || row_offset == nullptr || rows_per_part == nullptr ||
+      o_out == nullptr || lse_out == nullptr)
+    return FMHA_ERR_NULL_POINTER;
+  if (dtype != FMHA_DTYPE_FP16 && dtype != FMHA_DTYPE_BF16) return FMHA_ERR_BAD_DTYPE;
+  if (head_dim != 64 && head_dim != 96 && head_dim != 128) return FMHA_ERR_BAD_HEAD_DIM;
+  if (batch <= 0 || heads <= 0 || rows <= 0 || n_parts <= 0) return FMHA_ERR_BAD_SHAPE;
+  if (n_parts > fmha::kMaxPeers) return FMHA_ERR_TOO_LARGE;
+  if (!aligned16(o_out)) return FMHA_ERR_BAD_ALIGNMENT;
+  fmha::MergeList list;
+  list.n = n_parts;
+  for (int i = 0; i < n_parts; ++i) {
+    if (o_parts[i] == nullptr || lse_parts[i] == nullptr) return FMHA_ERR_NULL_POINTER;
+    if (!aligned16(o_parts[i])) return FMHA_ERR_BAD_ALIGNMENT;
+    if (rows_per_part[i] <= 0 || row_offset[i] < 0 ||
+        (long long)row_offset[i] + rows_per_part[i] > (long long)rows)
+      return FMHA_ERR_BAD_SHAPE;
+    list.o[i] = o_parts[i];
+    list.lse[i] = lse_parts[i];
+    list.row0[i] = row_offset[i];
+    list.rows[i] = rows_per_part[i];
+  }
+  const long long total = (long long)batch * rows * heads;
+  const int rows_per_block = 256 / ((head_dim > 64 ? 128 : 64) / 8);  // 16 or 8 threads per row
+  const unsigned grid = (unsigned)((total + rows_per_block - 1) / rows_per_block);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (dtype == FMHA_DTYPE_BF16) {
+    auto* o = static_cast<__nv_bfloat16*>(o_out);
+    FMHA_DISPATCH_DIMS(head_dim,
+                       fmha::merge_parts_kernel<D, __nv_bfloat16, DR><<<grid, 256, 0, s>>>(
+                           list, o, lse_out, heads, rows, total);)
+  } else {
+    auto* o = static_cast<__half*>(o_out);
+    FMHA_DISPATCH_DIMS(head_dim,
+                       fmha::merge_parts_kernel<D, __half, DR><<<grid, 256, 0, s>>>(
+                           list, o, lse_out, heads, rows, total);)
+  }
+  return cudaGetLastError() == cudaSuccess ? FMHA_OK : FMHA_ERR_LAUNCH;
+}
+
 int fmha_b200_forward(const void* query_ptr, const void* key_ptr, const void* value_ptr,
                       void* output_ptr, void* lse_ptr, int batch, int head, int m, int n, int k,
                       float scale, int causal, void* stream) {

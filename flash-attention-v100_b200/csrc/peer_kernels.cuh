@@ -95,4 +95,61 @@ __global__ void __launch_bounds__(256)
   *reinterpret_cast<uint4*>(out + z * so.batch + n * so.row + h * so.head + part * 8) = pack8<E>(f);
 }
 
+struct MergeList {
+  const void* o[kMaxPeers];     // 16-bit (Z, rows[s], H, DR) contiguous
+  const float* lse[kMaxPeers];  // fp32 (Z, H, rows[s]) contiguous
+  int row0[kMaxPeers];          // part s covers output rows [row0[s], row0[s] + rows[s])
+  int rows[kMaxPeers];
+  int n;
+};
+
+// All partial attention results of a ring forward merged in ONE pass (instead of one
+// read-modify-write pass over fp32 accumulators per step): for every output row
+//   lse = log sum_s e^lse_s,   o = sum_s e^(lse_s - lse) o_s      over the parts that cover the row.
+// out 16-bit (Z, rows, H, DR) contiguous, lse_out fp32 (Z, H, rows).
+template <int D, typename E, int DR = D>
+__global__ void __launch_bounds__(256)
+    merge_parts_kernel(MergeList parts, E* __restrict__ out, float* __restrict__ lse_out, int heads,
+                       int rows, long long total_rows) {
+  constexpr int kGroup = D / 8;
+  constexpr int kRowsPerBlock = 256 / kGroup;
+  const int part = threadIdx.x % kGroup;
+  const long long row_id = (long long)blockIdx.x * kRowsPerBlock + threadIdx.x / kGroup;
+  if (row_id >= total_rows || (DR != D && part * 8 >= DR)) return;
+  // row_id enumerates (z, n, h) of the output
+  const int h = (int)(row_id % heads);
+  const long long zn = row_id / heads;
+  const int n = (int)(zn % rows);
+  const int z = (int)(zn / rows);
+  float mx = -CUDART_INF_F;
+  for (int s = 0; s < parts.n; ++s) {
+    const int r = n - parts.row0[s];
+    if (r >= 0 && r < parts.rows[s])
+      mx = fmaxf(mx, parts.lse[s][((long long)z * heads + h) * parts.rows[s] + r]);
+  }
+  float f[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+  float sum = 0.f;
+  if (mx > -CUDART_INF_F) {
+    for (int s = 0; s < parts.n; ++s) {
+      const int r = n - parts.row0[s];
+      if (r < 0 || r >= parts.rows[s]) continue;
+      const float w = __expf(parts.lse[s][((long long)z * heads + h) * parts.rows[s] + r] - mx);
+      if (w == 0.f) continue;
+      sum += w;
+      const uint4 u = *reinterpret_cast<const uint4*>(
+          static_cast<const E*>(parts.o[s]) + (((long long)z * parts.rows[s] + r) * heads + h) * DR + part * 8);
+      float fp[8];
+      unpack8<E>(u, fp);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) f[i] = fmaf(w, fp[i], f[i]);
+    }
+    const float inv = 1.f / sum;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) f[i] *= inv;
+  }
+  *reinterpret_cast<uint4*>(out + row_id * DR + part * 8) = pack8<E>(f);
+  if (part == 0)
+    lse_out[((long long)z * heads + h) * rows + n] = mx > -CUDART_INF_F ? mx + __logf(sum) : -CUDART_INF_F;
+}
+
 }  // namespace fmha

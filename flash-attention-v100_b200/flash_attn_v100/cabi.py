@@ -32,7 +32,7 @@ EXPORTED_SYMBOLS = (
     "fmha_fwd", "fmha_bwd_workspace_bytes", "fmha_bwd", "fmha_bwd_static_scratch", "fmha_bwd_convert_dq", "fmha_merge", "fmha_merge_rows", "fmha_b200_forward",
     "fmha_b200_backward", "fmha_status_string", "fmha_version",
     "fmha_ipc_export", "fmha_ipc_open", "fmha_ipc_close", "fmha_peer_copy", "fmha_peer_copy_2d",
-    "fmha_counter_bump", "fmha_peer_signal", "fmha_peer_wait", "fmha_sum_partials",
+    "fmha_counter_bump", "fmha_peer_signal", "fmha_peer_wait", "fmha_sum_partials", "fmha_merge_parts",
 )
 
 
@@ -124,7 +124,9 @@ def load_library() -> ctypes.CDLL:
             ("fmha_peer_signal", [ctypes.POINTER(vp), i32, vp, vp]),
             ("fmha_peer_wait", [ctypes.POINTER(vp), i32, vp, vp, i32, vp]),
             ("fmha_sum_partials", [ctypes.POINTER(vp), ctypes.POINTER(i32), i32, vp, FmhaStrides, i32, i32,
-                                   i32, i32, i32, vp])):
+                                   i32, i32, i32, vp]),
+            ("fmha_merge_parts", [ctypes.POINTER(vp), ctypes.POINTER(vp), ctypes.POINTER(i32),
+                                  ctypes.POINTER(i32), i32, vp, vp, i32, i32, i32, i32, i32, vp])):
         getattr(lib, name).restype = ctypes.c_int
         getattr(lib, name).argtypes = args
     lib.fmha_status_string.restype = ctypes.c_char_p
@@ -402,3 +404,24 @@ def sum_partials(part_addrs, rows_per_part, out: torch.Tensor, stream=None):
                                                 _strides(out), Z, H, rows, D, _dtype_code(out),
                                                 _stream(stream)), "fmha_sum_partials")
     return out
+
+
+def merge_parts(o_parts, lse_parts, row_offsets, o_out, lse_out, stream=None):
+    """``fmha_merge_parts``: o_out (Z, rows, H, D) 16-bit, lse_out (Z, H, rows) fp32 = the LSE merge
+    of the partial results (o_parts[s] (Z, rows_s, H, D), lse_parts[s] (Z, H, rows_s), both
+    contiguous), part s covering the output rows from row_offsets[s] on."""
+    Z, rows, H, D = o_out.shape
+    for o, l in zip(o_parts, lse_parts):
+        if not (o.is_contiguous() and l.is_contiguous()) or o.dtype != o_out.dtype:
+            raise RuntimeError("partial results must be contiguous and of the output's type")
+    if not (o_out.is_contiguous() and lse_out.is_contiguous()):
+        raise RuntimeError("o_out and lse_out must be contiguous")
+    n = len(o_parts)
+    ro = (ctypes.c_int32 * n)(*[int(x) for x in row_offsets])
+    rp = (ctypes.c_int32 * n)(*[int(o.shape[1]) for o in o_parts])
+    with torch.cuda.device(o_out.device):
+        _check(load_library().fmha_merge_parts(_addr_array([o.data_ptr() for o in o_parts]),
+                                               _addr_array([l.data_ptr() for l in lse_parts]), ro, rp, n,
+                                               _ptr(o_out), _ptr(lse_out), Z, H, rows, D,
+                                               _dtype_code(o_out), _stream(stream)), "fmha_merge_parts")
+    return o_out, lse_out

@@ -204,17 +204,18 @@ class PeerRing:
         be, world, rank = self.backend, self.world, self.rank
         cs = torch.cuda.current_stream(self.device)
         side = self.fwd_side
-        half = self.shape[1] // 2
         self.pull_stream.wait_stream(cs)  # earlier work on the receive buffers is behind us
         cur = self._publish(side, k, v, cs, exchange)
         ev_ready = [torch.cuda.Event(), torch.cuda.Event()]
         ev_free = [torch.cuda.Event(), torch.cuda.Event()]
-        o_acc, lse_acc = be.new_accumulators(q)
-        out = torch.empty_like(q)
         if world > 1:
             self.pull_stream.wait_stream(cs)
             self._pull(side, "kv_f", 1, cur, causal, ev_free, ev_ready, exchange)
-        rows = self.shape[1]
+        Z, rows, H, D = self.shape
+        # every step leaves its partial (O, LSE) in buffers of its own; ONE pass merges them all
+        # at the end (fmha_merge_parts) instead of a read-modify-write pass over fp32
+        # accumulators after every step
+        parts_o, parts_l, offsets = [], [], []
         for t, (src, q_rows, kv_rows, causal_block) in enumerate(self.fd.ring_step_shapes(rank, world, causal, rows)):
             if t == 0:
                 kb, vb = k, v
@@ -223,16 +224,24 @@ class PeerRing:
                 kb, vb = side.recv[t % 2][0], side.recv[t % 2][1]
             if t + 1 < world:
                 self._pull(side, "kv_f", t + 1, cur, causal, ev_free, ev_ready, exchange)
-            last = t + 1 == world
-            whole_q = q_rows.start == 0
-            o_p, l_p = be.fwd(q[:, q_rows], kb[:, kv_rows], vb[:, kv_rows], scale, causal_block, not last)
-            be.merge(o_acc, lse_acc, o_p, l_p, q_rows, out if (last and whole_q) else None)
-            if last and not whole_q:
-                out.copy_(o_acc)
+            n_q = q_rows.stop - q_rows.start
+            o_p = torch.empty((Z, n_q, H, D), dtype=q.dtype, device=self.device)
+            l_p = torch.empty((Z, H, n_q), dtype=torch.float32, device=self.device)
+            self.cabi.fwd(q[:, q_rows], kb[:, kv_rows], vb[:, kv_rows], scale, causal_block, out=o_p, lse=l_p,
+                          status=self.status, sm_margin=be.sm_margin if t + 1 < world else 0)
+            parts_o.append(o_p)
+            parts_l.append(l_p)
+            offsets.append(q_rows.start)
             if t >= 1:
                 ev_free[t % 2].record(cs)
+        if world == 1:
+            out, lse = parts_o[0], parts_l[0]
+        else:
+            out = torch.empty_like(q)
+            lse = torch.empty((Z, H, rows), dtype=torch.float32, device=self.device)
+            self.cabi.merge_parts(parts_o, parts_l, offsets, out, lse, cs)
         cs.wait_stream(self.pull_stream)  # nothing of this call is left on the side stream
-        return out, lse_acc
+        return out, lse
 
     # ---- backward
     def backward(self, q, k, v, out, lse, dout, scale: float, causal: bool, exchange: bool = True):

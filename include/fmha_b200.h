@@ -303,6 +303,19 @@ int fmha_sum_partials(const float* const* parts, const int32_t* rows_per_part, i
                       void* out, FmhaStrides out_strides, int32_t batch, int32_t heads, int32_t rows,
                       int32_t head_dim, int32_t dtype, void* stream);
 
+/* All partial results of a ring-attention forward merged in one pass: for every output row
+ *   lse = log sum_s e^(lse_s),  o = sum_s e^(lse_s - lse) o_s     over the parts that cover it.
+ * Part s (s < n_parts <= 16): o_parts[s] 16-bit (Z, rows_per_part[s], H, D) contiguous,
+ * lse_parts[s] fp32 (Z, H, rows_per_part[s]) contiguous, covering the output rows
+ * [row_offset[s], row_offset[s] + rows_per_part[s]).  o_out 16-bit (Z, rows, H, D) contiguous,
+ * lse_out fp32 (Z, H, rows); a row no part covers (or whose parts are all empty, LSE = -inf)
+ * gets o = 0, lse = -inf.  Replaces n_parts calls of fmha_merge_rows on fp32 accumulators and
+ * the final conversion.  No counterpart in the reference. */
+int fmha_merge_parts(const void* const* o_parts, const float* const* lse_parts,
+                     const int32_t* row_offset, const int32_t* rows_per_part, int32_t n_parts,
+                     void* o_out, float* lse_out, int32_t batch, int32_t heads, int32_t rows,
+                     int32_t head_dim, int32_t dtype, void* stream);
+
 /* Reference-shaped launchers: same argument meaning as include/fused_mha.h:1-6, dense fp16
  * (batch, m|n, head, k) tensors, except that the `max`/`sum` pair becomes one `lse` buffer,
  * the backward's `d_ptr` (fp16 D) is dropped in favour of a caller workspace, and a status

@@ -35,6 +35,48 @@ def test_merge_kernel_matches_oracle_merge():
     assert oracle.max_abs(lse_acc.cpu(), ref_lse) <= helpers.TOL_LSE_MAX_ABS
 
 
+@pytest.mark.parametrize("dtype,D", [(torch.float16, 128), (torch.bfloat16, 64), (torch.float16, 96)])
+def test_merge_of_all_parts_in_one_pass(dtype, D):
+    """fmha_merge_parts: three partial results (two over all query rows, one over the second half
+    only, as in zig-zag ring attention) merged in one pass equal the attention over all keys the
+    rows saw, and equal the step-by-step merge into fp32 accumulators."""
+    from flash_attn_v100 import cabi
+
+    Z, N, H = 2, 256, 3
+    half = N // 2
+    q, k, v, _ = oracle.make_inputs(Z, N, H, D, seed=41, n_k=3 * 128, dtype=dtype)
+    qd, kd, vd = q.cuda(), k.cuda(), v.cuda()
+    blocks = [(slice(0, N), slice(0, 128)), (slice(half, N), slice(128, 256)), (slice(0, N), slice(256, 384))]
+    parts_o, parts_l, offs = [], [], []
+    o_acc = torch.empty((Z, N, H, D), dtype=torch.float32, device="cuda")
+    lse_acc = torch.full((Z, H, N), float("-inf"), device="cuda")
+    for qr, kr in blocks:
+        o_p, l_p = cabi.fwd(qd[:, qr], kd[:, kr], vd[:, kr], 0.1, False)
+        parts_o.append(o_p.contiguous())
+        parts_l.append(l_p)
+        offs.append(qr.start)
+        cabi.merge(o_acc, lse_acc, o_p, l_p, row_offset=qr.start)
+    out = torch.empty((Z, N, H, D), dtype=dtype, device="cuda")
+    lse = torch.empty((Z, H, N), device="cuda")
+    cabi.merge_parts(parts_o, parts_l, offs, out, lse)
+    assert oracle.max_abs(lse.cpu(), lse_acc.cpu()) <= 1e-5
+    tol = helpers.TOL_O_MAX_ABS_BF16 if dtype == torch.bfloat16 else helpers.TOL_O_MAX_ABS
+    assert oracle.max_abs(out.float().cpu(), o_acc.cpu()) <= tol
+    # against the oracle: the first half of the rows saw key blocks 0 and 2, the second half all
+    keys_first = torch.cat([k[:, :128], k[:, 256:]], dim=1), torch.cat([v[:, :128], v[:, 256:]], dim=1)
+    ref_a, lse_a = oracle.attention_forward(q[:, :half], keys_first[0], keys_first[1], 0.1, False)
+    ref_b, lse_b = oracle.attention_forward(q[:, half:], k, v, 0.1, False)
+    assert oracle.max_abs(out[:, :half].float().cpu(), ref_a) <= tol
+    assert oracle.max_abs(out[:, half:].float().cpu(), ref_b) <= tol
+    assert oracle.max_abs(lse[:, :, :half].cpu(), lse_a) <= helpers.TOL_LSE_MAX_ABS
+    assert oracle.max_abs(lse[:, :, half:].cpu(), lse_b) <= helpers.TOL_LSE_MAX_ABS
+    # rows whose parts are all empty (LSE = -inf): zeros and -inf, no NaN
+    for l in parts_l:
+        l[:, :, -1] = float("-inf")
+    cabi.merge_parts(parts_o, parts_l, offs, out, lse)
+    assert not out[:, -1].any() and bool(torch.isinf(lse[:, :, -1]).all()) and not torch.isnan(out.float()).any()
+
+
 def test_merge_of_a_row_range_into_larger_accumulators():
     """fmha_merge_rows: a partial result for the second half of the query rows merged in place
     into full-height accumulators equals the merge of a compact copy of that row range."""
