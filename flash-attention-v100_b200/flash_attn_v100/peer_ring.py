@@ -6,7 +6,7 @@ GPU reaches every other at full bandwidth, so nothing has to be *passed round*: 
 shards the same way (zig-zag, see ``distributed.py``) but
 
 * every rank PULLS the K/V block it needs next straight from the rank that owns it, with the
-  copy engines (``cudaMemcpyAsync`` from an address mapped through CUDA IPC), one step ahead,
+  copy engines (``cudaMemcpyAsync`` from an address mapped through CUDA IPC), two steps ahead,
   on a stream of its own, while the attention kernel of the current step runs on all SMs;
 * in the backward pass every rank PUSHES its fp32 dK/dV contribution for a visiting block to
   a slot at the block's owner, again with the copy engines while the next step computes; the
@@ -30,14 +30,16 @@ import torch.distributed as dist
 
 # rows of the flag matrix (one column per peer)
 _READY_F, _ACK_F, _READY_B, _ACK_B, _GRAD_READY, _GRAD_FREE, _N_FLAGS = 0, 1, 2, 3, 4, 5, 6
+# receive buffers per direction: a block is fetched _DEPTH - 1 steps before the step that uses it
+_DEPTH = 3
 
 
 class _KVSide:
-    """Export buffer, two receive buffers and the iteration words of one direction (fwd or bwd)."""
+    """Export buffer, the receive buffers and the iteration words of one direction (fwd or bwd)."""
 
     def __init__(self, shape, dtype, device, ready_row, ack_row):
         self.export = torch.empty((2,) + shape, dtype=dtype, device=device)
-        self.recv = [torch.empty((2,) + shape, dtype=dtype, device=device) for _ in range(2)]
+        self.recv = [torch.empty((2,) + shape, dtype=dtype, device=device) for _ in range(_DEPTH)]
         self.it = torch.zeros(2, dtype=torch.int32, device=device)  # [this iteration, the previous]
         self.ready_row, self.ack_row = ready_row, ack_row
 
@@ -171,15 +173,16 @@ class PeerRing:
 
     def _pull(self, side: _KVSide, kv_name: str, t: int, cur: int, causal: bool, ev_free, ev_ready,
               exchange: bool):
-        """Fetch the block of step t (t >= 1) into receive buffer t % 2 on the pull stream."""
+        """Fetch the block of step t (t >= 1) into receive buffer t % _DEPTH on the pull stream."""
         c = self.cabi
         Z, rows, H, D = self.shape
         src = (self.rank - t) % self.world
-        buf = side.recv[t % 2]
+        buf = side.recv[t % _DEPTH]
         esize = buf.element_size()
         with torch.cuda.stream(self.pull_stream):
-            if t >= 3:
-                self.pull_stream.wait_event(ev_free[t % 2])  # the kernels of step t - 2 are done with it
+            if t >= _DEPTH + 1:
+                # the kernels of step t - _DEPTH are done with the buffer
+                self.pull_stream.wait_event(ev_free[t % _DEPTH])
             if exchange:
                 c.peer_wait([self._flag(self.rank, side.ready_row, src)], cur, self.status,
                             self.timeout_ms, self.pull_stream)
@@ -195,7 +198,7 @@ class PeerRing:
                 c.peer_copy(buf.data_ptr(), src_addr, 2 * Z * entry, self.pull_stream)
             if exchange:
                 c.peer_signal([self._flag(src, side.ack_row, self.rank)], cur, self.pull_stream)
-            ev_ready[t % 2].record(self.pull_stream)
+            ev_ready[t % _DEPTH].record(self.pull_stream)
 
     # ---- forward
     def forward(self, q, k, v, scale: float, causal: bool, exchange: bool = True
@@ -206,11 +209,12 @@ class PeerRing:
         side = self.fwd_side
         self.pull_stream.wait_stream(cs)  # earlier work on the receive buffers is behind us
         cur = self._publish(side, k, v, cs, exchange)
-        ev_ready = [torch.cuda.Event(), torch.cuda.Event()]
-        ev_free = [torch.cuda.Event(), torch.cuda.Event()]
+        ev_ready = [torch.cuda.Event() for _ in range(_DEPTH)]
+        ev_free = [torch.cuda.Event() for _ in range(_DEPTH)]
         if world > 1:
             self.pull_stream.wait_stream(cs)
-            self._pull(side, "kv_f", 1, cur, causal, ev_free, ev_ready, exchange)
+            for t in range(1, min(_DEPTH, world)):
+                self._pull(side, "kv_f", t, cur, causal, ev_free, ev_ready, exchange)
         Z, rows, H, D = self.shape
         # every step leaves its partial (O, LSE) in buffers of its own; ONE pass merges them all
         # at the end (fmha_merge_parts) instead of a read-modify-write pass over fp32
@@ -220,10 +224,10 @@ class PeerRing:
             if t == 0:
                 kb, vb = k, v
             else:
-                cs.wait_event(ev_ready[t % 2])
-                kb, vb = side.recv[t % 2][0], side.recv[t % 2][1]
-            if t + 1 < world:
-                self._pull(side, "kv_f", t + 1, cur, causal, ev_free, ev_ready, exchange)
+                cs.wait_event(ev_ready[t % _DEPTH])
+                kb, vb = side.recv[t % _DEPTH][0], side.recv[t % _DEPTH][1]
+            if t >= 1 and t + _DEPTH - 1 < world:
+                self._pull(side, "kv_f", t + _DEPTH - 1, cur, causal, ev_free, ev_ready, exchange)
             n_q = q_rows.stop - q_rows.start
             o_p = torch.empty((Z, n_q, H, D), dtype=q.dtype, device=self.device)
             l_p = torch.empty((Z, H, n_q), dtype=torch.float32, device=self.device)
@@ -233,7 +237,7 @@ class PeerRing:
             parts_l.append(l_p)
             offsets.append(q_rows.start)
             if t >= 1:
-                ev_free[t % 2].record(cs)
+                ev_free[t % _DEPTH].record(cs)
         if world == 1:
             out, lse = parts_o[0], parts_l[0]
         else:
@@ -263,15 +267,16 @@ class PeerRing:
             c.peer_signal([self._flag(p, _GRAD_FREE, rank) for p in others], gcur, cs)
         state = self.bwd_state
         state["full_used"] = state["half_used"] = False
-        ev_ready = [torch.cuda.Event(), torch.cuda.Event()]
-        ev_free = [torch.cuda.Event(), torch.cuda.Event()]
+        ev_ready = [torch.cuda.Event() for _ in range(_DEPTH)]
+        ev_free = [torch.cuda.Event() for _ in range(_DEPTH)]
         ev_part = [torch.cuda.Event(), torch.cuda.Event()]
         ev_pushed = [torch.cuda.Event(), torch.cuda.Event()]
         begin_ok = self.row_begin_ok
         lse_half = None if begin_ok else lse[:, :, half:].contiguous()
         if world > 1:
             self.pull_stream.wait_stream(cs)
-            self._pull(side, "kv_b", 1, cur, causal, ev_free, ev_ready, exchange)
+            for t in range(1, min(_DEPTH, world)):
+                self._pull(side, "kv_b", t, cur, causal, ev_free, ev_ready, exchange)
         slot_bytes = 2 * Z * rows * H * D * 4
         entry = rows * H * D * 4
         mine = self.slots[rank]  # my own contribution goes straight into my slot
@@ -308,20 +313,20 @@ class PeerRing:
         for t, (src, q_rows, kv_rows, causal_block) in enumerate(self.fd.ring_step_shapes(rank, world, causal, rows)):
             if t == 0:
                 continue
-            cs.wait_event(ev_ready[t % 2])
-            kb, vb = side.recv[t % 2][0], side.recv[t % 2][1]
+            cs.wait_event(ev_ready[t % _DEPTH])
+            kb, vb = side.recv[t % _DEPTH][0], side.recv[t % _DEPTH][1]
             target = self.part[t % 2]
             if t >= 3:
                 cs.wait_event(ev_pushed[t % 2])  # the push of step t - 2 has read the buffer
             first_half_only = kv_rows.stop < rows
-            if t + 1 < world:
-                self._pull(side, "kv_b", t + 1, cur, causal, ev_free, ev_ready, exchange)
+            if t + _DEPTH - 1 < world:
+                self._pull(side, "kv_b", t + _DEPTH - 1, cur, causal, ev_free, ev_ready, exchange)
             if q_rows.start == 0:
                 be.bwd_step(state, "full", q, kb[:, kv_rows], vb[:, kv_rows], out, dout, lse, scale,
                             causal_block, target[0][:, kv_rows], target[1][:, kv_rows], overwrite=True)
             else:
                 second_half_step(kb, vb, kv_rows, causal_block, target)
-            ev_free[t % 2].record(cs)
+            ev_free[t % _DEPTH].record(cs)
             ev_part[t % 2].record(cs)
             if exchange:
                 with torch.cuda.stream(self.push_stream):
