@@ -27,7 +27,7 @@ path in the product.
 """
 from __future__ import annotations
 
-from typing import List, Optional, Tuple
+from typing import NamedTuple, List, Optional, Tuple
 
 import torch
 import torch.distributed as dist
@@ -84,6 +84,37 @@ def ring_step_shapes(rank: int, world: int, causal: bool, rows: int):
         else:
             steps.append((src, slice(half, rows), full, False))  # second half of local Q x whole block
     return steps
+
+
+class RingCall(NamedTuple):
+    """One kernel call of the copy-engine ring: the blocks it works on and the dense shape."""
+    parts: tuple        # of (step t, src rank, rows of the src's block needed, first row in the local buffer)
+    q_rows: slice       # local query rows that take part
+    kv_stop: int        # rows [0, kv_stop) of the local buffer hold the keys / values of the call
+    causal_block: bool
+
+
+def ring_calls(rank: int, world: int, causal: bool, rows: int, pair: bool = True):
+    """``ring_step_shapes`` grouped into kernel calls.  Two consecutive steps that need only the
+    first half of their block (under a causal mask: blocks of ranks before this one) share one
+    call: the two half blocks sit behind each other in one buffer, which is then as long as a
+    whole block, and all local queries see all of it.  A step's grid of 128-row tiles then fills
+    the SMs in twice as many rounds, i.e. more evenly, and there are fewer launches and partial
+    results.  Every other step is a call of its own."""
+    half = rows // 2
+    steps = ring_step_shapes(rank, world, causal, rows)
+    calls, t = [], 0
+    while t < len(steps):
+        src, q_rows, kv_rows, causal_block = steps[t]
+        halved = t >= 1 and kv_rows.stop == half and q_rows.start == 0
+        if pair and halved and t + 1 < len(steps) and steps[t + 1][2].stop == half and steps[t + 1][1].start == 0:
+            calls.append(RingCall(((t, src, kv_rows, 0), (t + 1, steps[t + 1][0], steps[t + 1][2], half)),
+                                  q_rows, rows, False))
+            t += 2
+        else:
+            calls.append(RingCall(((t, src, kv_rows, 0),), q_rows, kv_rows.stop, causal_block))
+            t += 1
+    return calls
 
 
 def ring_grad_rows(owner: int, world: int, causal: bool, rows: int):

@@ -51,7 +51,8 @@ class PeerRing:
     handles are exchanged here), then call ``forward`` / ``backward`` any number of times, all
     ranks in the same order."""
 
-    def __init__(self, shard_shape, dtype, device, group=None, timeout_ms: int = 10000, sm_margin: int = 2):
+    def __init__(self, shard_shape, dtype, device, group=None, timeout_ms: int = 10000, sm_margin: int = 2,
+                 pair_steps: bool = True):
         from flash_attn_v100 import cabi, distributed as fd
 
         self.cabi = cabi
@@ -67,6 +68,8 @@ class PeerRing:
         if rows % 2:
             raise ValueError("a zig-zag shard has an even number of rows")
         self.timeout_ms = int(timeout_ms)
+        # two steps over first halves of blocks in one kernel call (distributed.ring_calls)
+        self.pair_steps = bool(pair_steps)
         self.backend = fd.CudaBackend(sm_margin=sm_margin if self.world > 1 else 0)
         with torch.cuda.device(self.device):
             self.fwd_side = _KVSide(self.shape, dtype, self.device, _READY_F, _ACK_F)
@@ -171,34 +174,34 @@ class PeerRing:
             c.peer_signal([self._flag(p, side.ready_row, self.rank) for p in others], cur, cs)
         return cur
 
-    def _pull(self, side: _KVSide, kv_name: str, t: int, cur: int, causal: bool, ev_free, ev_ready,
-              exchange: bool):
-        """Fetch the block of step t (t >= 1) into receive buffer t % _DEPTH on the pull stream."""
+    def _pull(self, side: _KVSide, kv_name: str, ci: int, call, cur: int, ev_free, ev_ready, exchange: bool):
+        """Fetch the block(s) of call ``ci`` (>= 1) into receive buffer ci % _DEPTH on the pull
+        stream: a whole block, or the first halves of one or two blocks behind each other."""
         c = self.cabi
         Z, rows, H, D = self.shape
-        src = (self.rank - t) % self.world
-        buf = side.recv[t % _DEPTH]
+        buf = side.recv[ci % _DEPTH]
         esize = buf.element_size()
+        entry = rows * H * D * esize  # one tensor of one batch entry
         with torch.cuda.stream(self.pull_stream):
-            if t >= _DEPTH + 1:
-                # the kernels of step t - _DEPTH are done with the buffer
-                self.pull_stream.wait_event(ev_free[t % _DEPTH])
-            if exchange:
-                c.peer_wait([self._flag(self.rank, side.ready_row, src)], cur, self.status,
-                            self.timeout_ms, self.pull_stream)
-                src_addr = self.peer[src][kv_name]
-            else:
-                src_addr = side.export.data_ptr()  # measurements: same bytes, local source
-            entry = rows * H * D * esize
-            kv_rows = self.fd.ring_step_shapes(self.rank, self.world, causal, rows)[t][2]
-            if kv_rows.stop < rows:
-                # only the first half of the block is needed
-                c.peer_copy_2d(buf.data_ptr(), entry, src_addr, entry, entry // 2, 2 * Z, self.pull_stream)
-            else:
-                c.peer_copy(buf.data_ptr(), src_addr, 2 * Z * entry, self.pull_stream)
-            if exchange:
-                c.peer_signal([self._flag(src, side.ack_row, self.rank)], cur, self.pull_stream)
-            ev_ready[t % _DEPTH].record(self.pull_stream)
+            if ci >= _DEPTH + 1:
+                # the kernels of call ci - _DEPTH are done with the buffer
+                self.pull_stream.wait_event(ev_free[ci % _DEPTH])
+            for (_t, src, kv_rows, first_row) in call.parts:
+                if exchange:
+                    c.peer_wait([self._flag(self.rank, side.ready_row, src)], cur, self.status,
+                                self.timeout_ms, self.pull_stream)
+                    src_addr = self.peer[src][kv_name]
+                else:
+                    src_addr = side.export.data_ptr()  # measurements: same bytes, local source
+                if kv_rows.stop < rows:
+                    # only the first half of the block is needed; it goes to rows first_row.. here
+                    c.peer_copy_2d(buf.data_ptr() + first_row * H * D * esize, entry, src_addr, entry,
+                                   entry // 2, 2 * Z, self.pull_stream)
+                else:
+                    c.peer_copy(buf.data_ptr(), src_addr, 2 * Z * entry, self.pull_stream)
+                if exchange:
+                    c.peer_signal([self._flag(src, side.ack_row, self.rank)], cur, self.pull_stream)
+            ev_ready[ci % _DEPTH].record(self.pull_stream)
 
     # ---- forward
     def forward(self, q, k, v, scale: float, causal: bool, exchange: bool = True
@@ -211,33 +214,36 @@ class PeerRing:
         cur = self._publish(side, k, v, cs, exchange)
         ev_ready = [torch.cuda.Event() for _ in range(_DEPTH)]
         ev_free = [torch.cuda.Event() for _ in range(_DEPTH)]
+        Z, rows, H, D = self.shape
+        calls = self.fd.ring_calls(rank, world, causal, rows, self.pair_steps)
         if world > 1:
             self.pull_stream.wait_stream(cs)
-            for t in range(1, min(_DEPTH, world)):
-                self._pull(side, "kv_f", t, cur, causal, ev_free, ev_ready, exchange)
-        Z, rows, H, D = self.shape
-        # every step leaves its partial (O, LSE) in buffers of its own; ONE pass merges them all
+            for ci in range(1, min(_DEPTH, len(calls))):
+                self._pull(side, "kv_f", ci, calls[ci], cur, ev_free, ev_ready, exchange)
+        # every call leaves its partial (O, LSE) in buffers of its own; ONE pass merges them all
         # at the end (fmha_merge_parts) instead of a read-modify-write pass over fp32
         # accumulators after every step
         parts_o, parts_l, offsets = [], [], []
-        for t, (src, q_rows, kv_rows, causal_block) in enumerate(self.fd.ring_step_shapes(rank, world, causal, rows)):
-            if t == 0:
+        for ci, call in enumerate(calls):
+            if ci == 0:
                 kb, vb = k, v
             else:
-                cs.wait_event(ev_ready[t % _DEPTH])
-                kb, vb = side.recv[t % _DEPTH][0], side.recv[t % _DEPTH][1]
-            if t >= 1 and t + _DEPTH - 1 < world:
-                self._pull(side, "kv_f", t + _DEPTH - 1, cur, causal, ev_free, ev_ready, exchange)
+                cs.wait_event(ev_ready[ci % _DEPTH])
+                kb, vb = side.recv[ci % _DEPTH][0], side.recv[ci % _DEPTH][1]
+            if ci >= 1 and ci + _DEPTH - 1 < len(calls):
+                self._pull(side, "kv_f", ci + _DEPTH - 1, calls[ci + _DEPTH - 1], cur, ev_free, ev_ready, exchange)
+            q_rows = call.q_rows
             n_q = q_rows.stop - q_rows.start
             o_p = torch.empty((Z, n_q, H, D), dtype=q.dtype, device=self.device)
             l_p = torch.empty((Z, H, n_q), dtype=torch.float32, device=self.device)
-            self.cabi.fwd(q[:, q_rows], kb[:, kv_rows], vb[:, kv_rows], scale, causal_block, out=o_p, lse=l_p,
-                          status=self.status, sm_margin=be.sm_margin if t + 1 < world else 0)
+            self.cabi.fwd(q[:, q_rows], kb[:, :call.kv_stop], vb[:, :call.kv_stop], scale, call.causal_block,
+                          out=o_p, lse=l_p, status=self.status,
+                          sm_margin=be.sm_margin if ci + 1 < len(calls) else 0)
             parts_o.append(o_p)
             parts_l.append(l_p)
             offsets.append(q_rows.start)
-            if t >= 1:
-                ev_free[t % _DEPTH].record(cs)
+            if ci >= 1:
+                ev_free[ci % _DEPTH].record(cs)
         if world == 1:
             out, lse = parts_o[0], parts_l[0]
         else:
@@ -273,10 +279,11 @@ class PeerRing:
         ev_pushed = [torch.cuda.Event(), torch.cuda.Event()]
         begin_ok = self.row_begin_ok
         lse_half = None if begin_ok else lse[:, :, half:].contiguous()
+        calls = self.fd.ring_calls(rank, world, causal, rows, self.pair_steps)
         if world > 1:
             self.pull_stream.wait_stream(cs)
-            for t in range(1, min(_DEPTH, world)):
-                self._pull(side, "kv_b", t, cur, causal, ev_free, ev_ready, exchange)
+            for ci in range(1, min(_DEPTH, len(calls))):
+                self._pull(side, "kv_b", ci, calls[ci], cur, ev_free, ev_ready, exchange)
         slot_bytes = 2 * Z * rows * H * D * 4
         entry = rows * H * D * 4
         mine = self.slots[rank]  # my own contribution goes straight into my slot
@@ -310,36 +317,39 @@ class PeerRing:
         else:
             be.bwd_step(state, "full", q, k[:, hi], v[:, hi], out, dout, lse, scale, False,
                         mine[0][:, hi], mine[1][:, hi], overwrite=True)
-        for t, (src, q_rows, kv_rows, causal_block) in enumerate(self.fd.ring_step_shapes(rank, world, causal, rows)):
-            if t == 0:
+        for ci, call in enumerate(calls):
+            if ci == 0:
                 continue
-            cs.wait_event(ev_ready[t % _DEPTH])
-            kb, vb = side.recv[t % _DEPTH][0], side.recv[t % _DEPTH][1]
-            target = self.part[t % 2]
-            if t >= 3:
-                cs.wait_event(ev_pushed[t % 2])  # the push of step t - 2 has read the buffer
-            first_half_only = kv_rows.stop < rows
-            if t + _DEPTH - 1 < world:
-                self._pull(side, "kv_b", t + _DEPTH - 1, cur, causal, ev_free, ev_ready, exchange)
-            if q_rows.start == 0:
+            cs.wait_event(ev_ready[ci % _DEPTH])
+            kb, vb = side.recv[ci % _DEPTH][0], side.recv[ci % _DEPTH][1]
+            target = self.part[ci % 2]
+            if ci >= 3:
+                cs.wait_event(ev_pushed[ci % 2])  # the pushes of call ci - 2 have read the buffer
+            if ci + _DEPTH - 1 < len(calls):
+                self._pull(side, "kv_b", ci + _DEPTH - 1, calls[ci + _DEPTH - 1], cur, ev_free, ev_ready, exchange)
+            kv_rows = slice(0, call.kv_stop)
+            if call.q_rows.start == 0:
                 be.bwd_step(state, "full", q, kb[:, kv_rows], vb[:, kv_rows], out, dout, lse, scale,
-                            causal_block, target[0][:, kv_rows], target[1][:, kv_rows], overwrite=True)
+                            call.causal_block, target[0][:, kv_rows], target[1][:, kv_rows], overwrite=True)
             else:
-                second_half_step(kb, vb, kv_rows, causal_block, target)
-            ev_free[t % _DEPTH].record(cs)
-            ev_part[t % 2].record(cs)
+                second_half_step(kb, vb, kv_rows, call.causal_block, target)
+            ev_free[ci % _DEPTH].record(cs)
+            ev_part[ci % 2].record(cs)
             if exchange:
                 with torch.cuda.stream(self.push_stream):
                     ps = self.push_stream
-                    ps.wait_event(ev_part[t % 2])
-                    c.peer_wait([self._flag(rank, _GRAD_FREE, src)], gcur, self.status, self.timeout_ms, ps)
-                    dst = self.peer[src]["slots"] + rank * slot_bytes
-                    if first_half_only:
-                        c.peer_copy_2d(dst, entry, target.data_ptr(), entry, entry // 2, 2 * Z, ps)
-                    else:
-                        c.peer_copy(dst, target.data_ptr(), slot_bytes, ps)
-                    c.peer_signal([self._flag(src, _GRAD_READY, rank)], gcur, ps)
-                    ev_pushed[t % 2].record(ps)
+                    ps.wait_event(ev_part[ci % 2])
+                    for (_t, src, src_rows, first_row) in call.parts:
+                        c.peer_wait([self._flag(rank, _GRAD_FREE, src)], gcur, self.status, self.timeout_ms, ps)
+                        dst = self.peer[src]["slots"] + rank * slot_bytes
+                        if src_rows.stop < rows:
+                            # the first half of src's block: rows first_row.. of my buffer
+                            c.peer_copy_2d(dst, entry, target.data_ptr() + first_row * H * D * 4, entry,
+                                           entry // 2, 2 * Z, ps)
+                        else:
+                            c.peer_copy(dst, target.data_ptr(), slot_bytes, ps)
+                        c.peer_signal([self._flag(src, _GRAD_READY, rank)], gcur, ps)
+                    ev_pushed[ci % 2].record(ps)
         if split_local:
             be.bwd_step(state, "full", q, k[:, lo], v[:, lo], out, dout, lse, scale, causal,
                         mine[0][:, lo], mine[1][:, lo], overwrite=True)

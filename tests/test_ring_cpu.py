@@ -164,6 +164,68 @@ def test_pull_push_schedule_adds_up_to_full_attention(world, causal):
         assert oracle.max_abs(fd.zigzag_merge(got), ref) < 1e-4
 
 
+@pytest.mark.parametrize("world", [1, 2, 3, 4, 8])
+def test_paired_calls_add_up_to_full_attention(world):
+    """``ring_calls``: the steps grouped into kernel calls, two first halves of blocks behind each
+    other in one buffer where the causal schedule allows it.  Played through for all ranks with
+    the oracle as the kernel: outputs merged through LSE over the calls and gradients split back
+    to the blocks' owners must equal attention over the whole sequence, every step must appear in
+    exactly one call, and a pair must be two first halves seen by all local queries."""
+    from flash_attn_v100 import distributed as fd
+
+    Z, H, D = 1, 2, 64
+    rows = 32
+    half = rows // 2
+    N = rows * world
+    q, k, v, dout = oracle.make_inputs(Z, N, H, D, seed=9)
+    ref_out, ref_lse, ref_dq, ref_dk, ref_dv = oracle.attention_fwd_bwd(q, k, v, dout, 0.2, True)
+    shard = lambda t, r: fd.zigzag_split(t, r, world)
+    outs, dqs = [], []
+    dks = [torch.zeros((Z, rows, H, D)) for _ in range(world)]
+    dvs = [torch.zeros((Z, rows, H, D)) for _ in range(world)]
+    pairs = 0
+    for r in range(world):
+        calls = fd.ring_calls(r, world, True, rows)
+        steps = fd.ring_step_shapes(r, world, True, rows)
+        assert sorted(t for c in calls for (t, _, _, _) in c.parts) == list(range(world))
+        ql, dol = shard(q, r).float(), shard(dout, r).float()
+        o_acc, lse_acc = torch.zeros((Z, rows, H, D)), torch.full((Z, H, rows), float("-inf"))
+        buffers = []
+        for c in calls:
+            kb, vb = torch.zeros((Z, rows, H, D)), torch.zeros((Z, rows, H, D))
+            for (t, src, src_rows, first_row) in c.parts:
+                assert (src, c.q_rows if len(c.parts) == 1 else steps[t][1], src_rows) == \
+                       (steps[t][0], steps[t][1], steps[t][2])
+                n = src_rows.stop
+                kb[:, first_row:first_row + n] = shard(k, src)[:, src_rows].float()
+                vb[:, first_row:first_row + n] = shard(v, src)[:, src_rows].float()
+            if len(c.parts) == 2:
+                pairs += 1
+                assert c.kv_stop == rows and c.q_rows == slice(0, rows) and not c.causal_block
+                assert [p[2].stop for p in c.parts] == [half, half] and [p[3] for p in c.parts] == [0, half]
+            buffers.append((kb[:, :c.kv_stop], vb[:, :c.kv_stop]))
+            o_p, l_p = oracle.attention_forward(ql[:, c.q_rows], *buffers[-1], 0.2, c.causal_block)
+            o, l = oracle.merge_partials(o_acc[:, c.q_rows], lse_acc[:, :, c.q_rows], o_p, l_p)
+            o_acc[:, c.q_rows], lse_acc[:, :, c.q_rows] = o, l
+        outs.append(o_acc)
+        dq = torch.zeros((Z, rows, H, D))
+        for c, (kb, vb) in zip(calls, buffers):
+            g = oracle.attention_backward(ql[:, c.q_rows], kb, vb, o_acc[:, c.q_rows], lse_acc[:, :, c.q_rows],
+                                          dol[:, c.q_rows], 0.2, c.causal_block)
+            dq[:, c.q_rows] += g[0]
+            for (t, src, src_rows, first_row) in c.parts:
+                n = src_rows.stop
+                dks[src][:, :n] += g[1][:, first_row:first_row + n]
+                dvs[src][:, :n] += g[2][:, first_row:first_row + n]
+        dqs.append(dq)
+    assert pairs == sum(r // 2 for r in range(world))  # rank r has r blocks of earlier ranks
+    assert oracle.max_abs(fd.zigzag_merge(outs), ref_out) < 1e-5
+    for got, ref in ((dqs, ref_dq), (dks, ref_dk), (dvs, ref_dv)):
+        assert oracle.max_abs(fd.zigzag_merge(got), ref) < 1e-4
+    # without a causal mask every step needs a whole block: no pairs
+    assert all(len(c.parts) == 1 for c in fd.ring_calls(world - 1, world, False, rows))
+
+
 def _missing_peer_worker(rank, world, port, out_dir):
     """Rank 1 leaves between steps without ever joining the exchange; rank 0 must get an error on
     the host within the process group's (short) time-out, not hang."""
