@@ -23,6 +23,7 @@ buffer first.  torch.distributed is used once, to exchange the IPC handles.
 """
 from __future__ import annotations
 
+import os
 from typing import List, Optional, Tuple
 
 import torch
@@ -30,8 +31,9 @@ import torch.distributed as dist
 
 # rows of the flag matrix (one column per peer)
 _READY_F, _ACK_F, _READY_B, _ACK_B, _GRAD_READY, _GRAD_FREE, _N_FLAGS = 0, 1, 2, 3, 4, 5, 6
-# receive buffers per direction: a block is fetched _DEPTH - 1 steps before the step that uses it
-_DEPTH = 3
+# receive buffers per direction: a block is fetched _DEPTH - 1 calls before the call that uses it
+# (FMHA_RING_DEPTH, 2..6, overrides for tuning experiments)
+_DEPTH = min(6, max(2, int(os.environ.get("FMHA_RING_DEPTH", "3"))))
 
 
 class _KVSide:
@@ -52,7 +54,7 @@ class PeerRing:
     ranks in the same order."""
 
     def __init__(self, shard_shape, dtype, device, group=None, timeout_ms: int = 10000, sm_margin: int = 2,
-                 pair_steps: bool = True):
+                 pair_steps: Optional[bool] = None):
         from flash_attn_v100 import cabi, distributed as fd
 
         self.cabi = cabi
@@ -69,6 +71,9 @@ class PeerRing:
             raise ValueError("a zig-zag shard has an even number of rows")
         self.timeout_ms = int(timeout_ms)
         # two steps over first halves of blocks in one kernel call (distributed.ring_calls)
+        # (default on; FMHA_RING_PAIR=0 switches it off for tuning experiments)
+        if pair_steps is None:
+            pair_steps = os.environ.get("FMHA_RING_PAIR", "1") != "0"
         self.pair_steps = bool(pair_steps)
         self.backend = fd.CudaBackend(sm_margin=sm_margin if self.world > 1 else 0)
         with torch.cuda.device(self.device):
