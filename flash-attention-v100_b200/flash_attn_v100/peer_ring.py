@@ -71,9 +71,13 @@ class PeerRing:
             raise ValueError("a zig-zag shard has an even number of rows")
         self.timeout_ms = int(timeout_ms)
         # two steps over first halves of blocks in one kernel call (distributed.ring_calls)
-        # (default on; FMHA_RING_PAIR=0 switches it off for tuning experiments)
+        # Off by default: at 8 GPUs the kernels of a step get 3-4 % faster (a paired call fills
+        # the SMs in 6.9 rounds of tiles instead of 3.46) but the step does not, its time then
+        # being set by the hand-shakes, and it varies more from step to step (same box, three
+        # regions of five steps: 4.85-5.28 ms without, 4.86-5.43 ms with).  FMHA_RING_PAIR=1
+        # switches it on for experiments.
         if pair_steps is None:
-            pair_steps = os.environ.get("FMHA_RING_PAIR", "1") != "0"
+            pair_steps = os.environ.get("FMHA_RING_PAIR", "0") != "0"
         self.pair_steps = bool(pair_steps)
         self.backend = fd.CudaBackend(sm_margin=sm_margin if self.world > 1 else 0)
         with torch.cuda.device(self.device):

@@ -281,7 +281,7 @@ def _free_port():
         return s.getsockname()[1]
 
 
-def _ring_worker(rank, world, port, causal, out_dir, transport, Z, rows_per_rank, H, D, repeats):
+def _ring_worker(rank, world, port, causal, out_dir, transport, Z, rows_per_rank, H, D, repeats, pair=False):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
     torch.cuda.set_device(rank)
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
@@ -295,7 +295,8 @@ def _ring_worker(rank, world, port, causal, out_dir, transport, Z, rows_per_rank
                          for _ in range(4))
         ring = None
         if transport == "peer":
-            ring = peer_ring.PeerRing((Z, rows_per_rank, H, D), torch.float16, torch.device("cuda", rank))
+            ring = peer_ring.PeerRing((Z, rows_per_rank, H, D), torch.float16, torch.device("cuda", rank),
+                                      pair_steps=pair)
         for _ in range(repeats):  # more than once: buffers, flags and iteration numbers are reused
             ql, kl, vl, dol = (fd.zigzag_split(t, rank, world).requires_grad_(i < 3)
                                for i, t in enumerate((q, k, v, dout)))
@@ -319,13 +320,13 @@ def _visible_world():
     return 8 if n >= 8 else 4 if n >= 4 else 2 if n >= 2 else 1
 
 
-def _run_ring(tmp_path, causal, transport, Z, rows_per_rank, H, D, repeats=1):
+def _run_ring(tmp_path, causal, transport, Z, rows_per_rank, H, D, repeats=1, pair=False):
     from flash_attn_v100 import distributed as fd
     from oracle import attention_oracle_blockwise as blockwise
 
     world = _visible_world()
     mp.spawn(_ring_worker, args=(world, _free_port(), causal, str(tmp_path), transport, Z, rows_per_rank, H, D,
-                                 repeats), nprocs=world, join=True)
+                                 repeats, pair), nprocs=world, join=True)
     parts = [torch.load(os.path.join(tmp_path, f"rank{r}.pt")) for r in range(world)]
     N = rows_per_rank * world
     g = torch.Generator(device="cuda").manual_seed(9)
@@ -355,6 +356,13 @@ def test_ring_attention_shards_whose_half_is_no_multiple_of_the_tile(causal, tmp
     over the second half of the queries run on sliced tensors with a workspace of their own
     instead of q_row_begin."""
     _run_ring(tmp_path, causal, "peer", Z=2, rows_per_rank=320, H=2, D=64, repeats=2)
+
+
+def test_ring_attention_with_paired_steps(tmp_path):
+    """``pair_steps``: two steps over first halves of blocks in one kernel call (ranks 2 and up
+    have such pairs, so this takes 3 or more GPUs to mean anything; with fewer it is the plain
+    schedule).  Two passes in a row."""
+    _run_ring(tmp_path, True, "peer", Z=2, rows_per_rank=512, H=4, D=128, repeats=2, pair=True)
 
 
 @pytest.mark.parametrize("transport", ["nccl", "peer"])
