@@ -13,8 +13,8 @@ Prints ONE JSON line (rank 0):
   value        whole-job fwd+bwd TFLOP/s with inputs resident in HBM, algorithmic FLOPs
                (fwd 4*Z*H*N^2*D, halved when causal; bwd 2.5x), CUDA-event time, max over ranks
   e2e          the same metric through the public API flash_attn_func (+ autograd backward)
-               with pinned HOST buffers: H2D of q, k, v, dout and D2H of out, dq, dk, dv inside
-               the timed region
+               with pinned HOST buffers (placed on the GPU's NUMA node where sysfs tells it):
+               H2D of q, k, v, dout and D2H of out, dq, dk, dv inside the timed region
   roofline     the dominant kernel (fused dK/dV/dQ backward) against the measured dense 16-bit
                tensor peak from MEASURED_PEAKS.json (fallback 1590 TF/s), timed in place with CUDA
                events; `traffic` is DRAM bytes per launch from the committed ncu capture (null
