@@ -31,6 +31,45 @@ def test_reference_arm_line_on_host_cores():
     assert d["gpu_launches"] == 0
 
 
+def test_host_buffer_placement_helper(monkeypatch, tmp_path):
+    """``cpus_near_gpu``: the GPU's PCI address -> sysfs local_cpulist -> CPU set, cut down to the
+    CPUs this process may use; anything missing means "unknown" (None), never an exception, and
+    ``near_gpu`` puts the previous affinity back."""
+    import builtins
+    import types
+
+    sys.path.insert(0, ROOT)
+    import bench
+
+    fake_torch = types.SimpleNamespace(cuda=types.SimpleNamespace(get_device_properties=lambda dev: types.SimpleNamespace(
+        pci_domain_id=0, pci_bus_id=0x1b, pci_device_id=0)))
+    listing = tmp_path / "local_cpulist"
+    real_open = builtins.open
+    allowed = sorted(os.sched_getaffinity(0))
+
+    def fake_open(path, *a, **k):
+        if str(path) == "/sys/bus/pci/devices/0000:1b:00.0/local_cpulist":
+            return real_open(listing, *a, **k)
+        return real_open(path, *a, **k)
+
+    monkeypatch.setattr(builtins, "open", fake_open)
+    listing.write_text(f"{allowed[0]},{allowed[-1]}-{allowed[-1] + 3}\n")
+    assert bench.cpus_near_gpu(fake_torch, 0) == {allowed[0], allowed[-1]}
+    before = os.sched_getaffinity(0)
+    with bench.near_gpu(fake_torch, 0) as placement:
+        assert placement.cpus == {allowed[0], allowed[-1]}
+        assert os.sched_getaffinity(0) == placement.cpus
+    assert os.sched_getaffinity(0) == before
+    listing.write_text("100000-100003\n")          # none of them usable here
+    assert bench.cpus_near_gpu(fake_torch, 0) is None
+    listing.write_text("not a list\n")
+    assert bench.cpus_near_gpu(fake_torch, 0) is None
+    no_pci = types.SimpleNamespace(cuda=types.SimpleNamespace(get_device_properties=lambda dev: object()))
+    assert bench.cpus_near_gpu(no_pci, 0) is None
+    with bench.near_gpu(no_pci, 0) as placement:
+        assert placement.cpus is None and os.sched_getaffinity(0) == before
+
+
 @pytest.mark.gpu
 def test_our_arm_line_has_roofline_baseline_e2e_and_clocks():
     d = _run("--steps", "3", "--warmup", "3", "--regions", "3", "--workload", "cfg2_causal")
